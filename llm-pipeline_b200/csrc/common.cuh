@@ -1,0 +1,79 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions and the
+// error reporting of the C entry points.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLMP_API extern "C" __attribute__((visibility("default")))
+
+// Element type codes used by the C entry points.
+enum LlmpDtype : int { LLMP_F32 = 0, LLMP_BF16 = 1 };
+
+// Every entry point returns 0 on success. A non-zero return means nothing useful was computed;
+// llmp_last_error() then gives the reason as text.
+void llmp_set_error(const char* fmt, ...);
+int llmp_check_launch(const char* what);
+
+#define LLMP_REQUIRE(cond, ...)            \
+    do {                                   \
+        if (!(cond)) {                     \
+            llmp_set_error(__VA_ARGS__);   \
+            return 1;                      \
+        }                                  \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Reads element i of a vector whose element type is chosen at run time (norm weights and
+// biases keep the type they were stored in).
+__device__ __forceinline__ float load_as_float(const void* p, int is_bf16, size_t i) {
+    return is_bf16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i])
+                   : reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a thread block; every thread gets the result. scratch holds 32 floats.
+// The order of the additions is fixed by the block size alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}

@@ -1,0 +1,237 @@
+// Memory-bound kernels of the forward pass: embedding gather, rotary tables, fused
+// residual-add + RMSNorm, fused per-head q/k RMSNorm + rotary + paged K/V write, SwiGLU.
+// All statistics (mean square, rsqrt, angles, sigmoid) are computed in float32.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// Embedding: residual[n, :] = float(table[ids[n], :]).  The residual stream is float32.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+    const int n = blockIdx.x;
+    const int id = ids[n];
+    const bool ok = id >= 0 && id < V;
+    const T* row = table + (size_t)(ok ? id : 0) * H;
+    float* dst = out + (size_t)n * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = ok ? to_float(row[c]) : 0.f;
+}
+
+LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float* out, int N, int H, int V,
+                            cudaStream_t stream) {
+    if (N <= 0) return 0;
+    LLMP_REQUIRE(H > 0 && V > 0, "embedding: bad sizes H=%d V=%d", H, V);
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == LLMP_F32)
+        embedding_kernel<float><<<N, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+    else
+        embedding_kernel<bf16><<<N, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
+    return llmp_check_launch("embedding");
+}
+
+// ------------------------------------------------------------------------------------------
+// Rotary tables: cos/sin[n, j] = cos/sin(float(pos[n]) * inv_freq[j]) * scaling, float32.
+// ------------------------------------------------------------------------------------------
+__global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float scaling,
+                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int N, int half) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)N * half) return;
+    const int n = (int)(i / half), j = (int)(i % half);
+    const float angle = (float)pos[n] * inv_freq[j];
+    float s, c;
+    sincosf(angle, &s, &c);
+    cos_out[i] = c * scaling;
+    sin_out[i] = s * scaling;
+}
+
+LLMP_API int llmp_rope_tables(const int* pos, const float* inv_freq, float scaling, float* cos_out, float* sin_out,
+                              int N, int half, cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return 0;
+    const size_t total = (size_t)N * half;
+    rope_tables_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(pos, inv_freq, scaling, cos_out, sin_out,
+                                                                           N, half);
+    return llmp_check_launch("rope_tables");
+}
+
+// ------------------------------------------------------------------------------------------
+// Fused residual add + RMSNorm.  For output row m (input row r = rows ? rows[m] : m):
+//   x = residual[r] + delta[r] + delta_bias          (delta, delta_bias optional)
+//   if (!rows) residual[r] = x
+//   out[m] = weight * (x * rsqrt(mean(x^2) + eps))   rounded once to the output type
+// One block per row; the row is staged in shared memory between the two passes.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const void* __restrict__ delta_bias, int bias_bf16,
+                                   const void* __restrict__ weight, int weight_bf16, float eps,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H) {
+    extern __shared__ float row_smem[];
+    __shared__ float scratch[32];
+    const int m = blockIdx.x;
+    const int r = rows ? rows[m] : m;
+    float* res = residual + (size_t)r * H;
+    const T* del = delta ? delta + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float x = res[c];
+        if (del) x += to_float(del[c]);
+        if (delta_bias) x += load_as_float(delta_bias, bias_bf16, c);
+        row_smem[c] = x;
+        ss += x * x;
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    T* dst = out + (size_t)m * H;
+    const bool write_back = (rows == nullptr) && (del != nullptr || delta_bias != nullptr);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = row_smem[c];
+        if (write_back) res[c] = x;
+        dst[c] = from_float<T>(load_as_float(weight, weight_bf16, c) * (x * rstd));
+    }
+}
+
+LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* delta_bias, int bias_dtype,
+                              const void* weight, int weight_dtype, float eps, void* out, int dtype,
+                              const int* rows, int M, int H, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    LLMP_REQUIRE(H > 0, "add_rmsnorm: bad width %d", H);
+    const size_t smem = (size_t)H * sizeof(float);
+    LLMP_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", H, smem);
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (dtype == LLMP_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<M, threads, smem, stream>>>(residual, (const float*)delta, delta_bias,
+                                                                bias_dtype == LLMP_BF16, weight,
+                                                                weight_dtype == LLMP_BF16, eps, (float*)out, rows, H);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<bf16><<<M, threads, smem, stream>>>(residual, (const bf16*)delta, delta_bias,
+                                                               bias_dtype == LLMP_BF16, weight,
+                                                               weight_dtype == LLMP_BF16, eps, (bf16*)out, rows, H);
+    }
+    return llmp_check_launch("add_rmsnorm");
+}
+
+// ------------------------------------------------------------------------------------------
+// Fused projection bias + per-head RMSNorm + rotary + paged K/V write.
+// qkv is [N, (nq + 2*nkv) * d] with columns [q heads | k heads | v heads].  For token n:
+//   q head: (+bias) -> RMSNorm over d (optional) -> rotate the first rotary_dim entries -> written in place
+//   k head: same, then stored to the page slot of the token
+//   v head: (+bias) -> stored to the page slot
+// Rotation pairs entry j with j + rotary_dim/2:  y[j] = x[j]*cos - x[j+h]*sin,  y[j+h] = x[j+h]*cos + x[j]*sin.
+// Pages are [num_pages, 2 (K,V), nkv, page_size, d];  slot = page * page_size + offset, or -1 to skip.
+// One warp per (token, head); 4 warps per block.
+// ------------------------------------------------------------------------------------------
+#define QKV_WARPS 4
+template <typename T>
+__global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bias, int bias_bf16,
+                                const void* __restrict__ q_w, const void* __restrict__ k_w, int w_bf16,
+                                float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                int rotary_dim, const int* __restrict__ slots, T* __restrict__ pages,
+                                int nq, int nkv, int d, int page_size) {
+    extern __shared__ float head_smem[];           // [QKV_WARPS][d]
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* x = head_smem + (size_t)warp * d;
+    const int heads = nq + 2 * nkv;
+    const size_t row_width = (size_t)heads * d;
+    T* row = qkv + (size_t)n * row_width;
+    const int half = rotary_dim / 2;
+    const int slot = slots ? slots[n] : -1;
+    for (int h = warp; h < heads; h += QKV_WARPS) {
+        const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+        T* src = row + (size_t)h * d;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            float v = to_float(src[i]);
+            if (bias) v += load_as_float(bias, bias_bf16, (size_t)h * d + i);
+            x[i] = v;
+            ss += v * v;
+        }
+        __syncwarp();
+        const void* w = is_q ? q_w : k_w;
+        if ((is_q || is_k) && w) {
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / (float)d + eps);
+            for (int i = lane; i < d; i += 32) x[i] = load_as_float(w, w_bf16, i) * (x[i] * rstd);
+            __syncwarp();
+        }
+        if ((is_q || is_k) && half > 0) {
+            const float* c = cos_t + (size_t)n * half;
+            const float* s = sin_t + (size_t)n * half;
+            for (int j = lane; j < half; j += 32) {
+                const float a = x[j], b = x[j + half];
+                x[j] = a * c[j] - b * s[j];
+                x[j + half] = b * c[j] + a * s[j];
+            }
+            __syncwarp();
+        }
+        if (is_q) {
+            for (int i = lane; i < d; i += 32) src[i] = from_float<T>(x[i]);
+        } else if (pages && slot >= 0) {
+            const int kvh = is_k ? h - nq : h - nq - nkv;
+            const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+            T* dst = pages + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * d;
+            for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
+        }
+        __syncwarp();
+    }
+}
+
+LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtype, const void* q_w, const void* k_w,
+                           int w_dtype, float eps, const float* cos_t, const float* sin_t, int rotary_dim,
+                           const int* slots, void* pages, int N, int nq, int nkv, int d, int page_size,
+                           cudaStream_t stream) {
+    if (N <= 0) return 0;
+    LLMP_REQUIRE(nq > 0 && nkv >= 0 && d > 0, "qkv_post: bad sizes nq=%d nkv=%d d=%d", nq, nkv, d);
+    LLMP_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
+                 "qkv_post: rotary_dim %d must be even and at most head_dim %d", rotary_dim, d);
+    LLMP_REQUIRE(rotary_dim == 0 || (cos_t && sin_t), "qkv_post: rotary tables missing");
+    LLMP_REQUIRE(!pages || page_size > 0, "qkv_post: bad page size %d", page_size);
+    const size_t smem = (size_t)QKV_WARPS * d * sizeof(float);
+    LLMP_REQUIRE(smem <= 48 * 1024, "qkv_post: head_dim %d too large", d);
+    if (dtype == LLMP_F32)
+        qkv_post_kernel<float><<<N, QKV_WARPS * 32, smem, stream>>>(
+            (float*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
+            slots, (float*)pages, nq, nkv, d, page_size);
+    else
+        qkv_post_kernel<bf16><<<N, QKV_WARPS * 32, smem, stream>>>(
+            (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
+            slots, (bf16*)pages, nq, nkv, d, page_size);
+    return llmp_check_launch("qkv_post");
+}
+
+// ------------------------------------------------------------------------------------------
+// SwiGLU: out[n, i] = silu(gu[n, i]) * gu[n, I + i],  silu(z) = z / (1 + exp(-z)), float32 inside.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+    const int n = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const T* row = gu + (size_t)n * 2 * I;
+    const float g = to_float(row[i]), u = to_float(row[(size_t)I + i]);
+    const float act = g / (1.f + expf(-g));
+    out[(size_t)n * I + i] = from_float<T>(act * u);
+}
+
+LLMP_API int llmp_swiglu(const void* gu, void* out, int dtype, int N, int I, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    LLMP_REQUIRE(I > 0, "swiglu: bad width %d", I);
+    LLMP_REQUIRE(N <= 65535 * 1024, "swiglu: too many rows %d", N);
+    // gridDim.y is limited to 65535: fold larger row counts into several launches.
+    const int max_rows = 65535;
+    for (int n0 = 0; n0 < N; n0 += max_rows) {
+        const int rows = N - n0 < max_rows ? N - n0 : max_rows;
+        dim3 grid((I + 255) / 256, rows);
+        if (dtype == LLMP_F32)
+            swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu + (size_t)n0 * 2 * I,
+                                                           (float*)out + (size_t)n0 * I, I);
+        else
+            swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu + (size_t)n0 * 2 * I,
+                                                          (bf16*)out + (size_t)n0 * I, I);
+    }
+    return llmp_check_launch("swiglu");
+}

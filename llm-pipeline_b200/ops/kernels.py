@@ -1,0 +1,249 @@
+"""Python bindings of the CUDA entry points (``csrc/*.cu``), one function per kernel.
+
+Arguments are CUDA tensors; the functions check types, contiguity and sizes, pass raw pointers
+and the current stream to the library, and raise ``KernelError`` with the library's message when
+an entry point refuses its arguments. There is no CPU implementation behind these functions: a
+tensor that is not on a CUDA device is an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import library
+
+F32, BF16 = 0, 1
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_long
+_F = ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {dtype}; the kernels take float32 and bfloat16")
+
+
+_SIGNATURES = {
+    "llmp_embedding": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "llmp_rope_tables": [_P, _P, _F, _P, _P, _I, _I, _P],
+    "llmp_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "llmp_qkv_post": [_P, _I, _P, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "llmp_swiglu": [_P, _P, _I, _I, _I, _P],
+    "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
+    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_argmax": [_P, _L, _I, _I, _P, _P],
+    "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
+}
+_bound = {}
+
+
+def _fn(name: str):
+    fn = _bound.get(name)
+    if fn is None:
+        lib = library()
+        fn = getattr(lib, name)
+        fn.argtypes = _SIGNATURES[name]
+        fn.restype = ctypes.c_int
+        _bound[name] = fn
+    return fn
+
+
+def _call(name: str, *args) -> None:
+    rc = _fn(name)(*args)
+    if rc != 0:
+        lib = library()
+        lib.llmp_last_error.restype = ctypes.c_char_p
+        raise KernelError(lib.llmp_last_error().decode(errors="replace"))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a kernel was given a tensor that is not on a CUDA device; this engine has no CPU path")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, message: str) -> None:
+    if not cond:
+        raise KernelError(message)
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+def tokens_per_attention_tile(num_heads: int, num_kv_heads: int) -> int:
+    fn = library().llmp_attention_tokens_per_tile
+    fn.argtypes = [_I, _I]
+    fn.restype = _I
+    n = fn(num_heads, num_kv_heads)
+    _need(n > 0, f"{num_heads} query heads cannot share {num_kv_heads} key/value heads")
+    return n
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, :] = float32(table[ids[n], :])"""
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous matrix")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (ids.numel(), table.shape[1]),
+          "embedding output must be float32 [tokens, hidden]")
+    _call("llmp_embedding", _ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), ids.numel(),
+          table.shape[1], table.shape[0], _stream())
+    return out
+
+
+def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, scaling: float, cos: torch.Tensor,
+                sin: torch.Tensor) -> None:
+    """cos/sin[n, j] = cos/sin(float(positions[n]) * inv_freq[j]) * scaling, all float32."""
+    _i32(positions, "positions")
+    half = inv_freq.numel()
+    _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous(), "inv_freq must be contiguous float32")
+    for t in (cos, sin):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (positions.numel(), half),
+              "rotary tables must be float32 [tokens, rotary_dim / 2]")
+    _call("llmp_rope_tables", _ptr(positions), _ptr(inv_freq), float(scaling), _ptr(cos), _ptr(sin),
+          positions.numel(), half, _stream())
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, delta_bias: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x = residual + delta (+ delta_bias); residual = x (unless ``rows`` selects rows);
+    out = weight * (x * rsqrt(mean(x^2) + eps)).  residual is float32, delta/out have the compute type."""
+    H = residual.shape[-1]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.dim() == 2,
+          "residual must be a contiguous float32 matrix")
+    M = rows.numel() if rows is not None else residual.shape[0]
+    _need(out.is_contiguous() and out.shape == (M, H), "norm output has the wrong shape")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape,
+              "delta must match the residual's shape and the output's type")
+    _need(weight.numel() == H and weight.is_contiguous(), "norm weight has the wrong size")
+    if delta_bias is not None:
+        _need(delta_bias.numel() == H and delta_bias.is_contiguous(), "delta bias has the wrong size")
+    if rows is not None:
+        _i32(rows, "rows")
+    _call("llmp_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(delta_bias),
+          dtype_code(delta_bias.dtype) if delta_bias is not None else F32, _ptr(weight), dtype_code(weight.dtype),
+          float(eps), _ptr(out), dtype_code(out.dtype), _ptr(rows), M, H, _stream())
+    return out
+
+
+def qkv_post(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, *,
+             bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+             eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+             slots: Optional[torch.Tensor], pages: Optional[torch.Tensor], page_size: int) -> None:
+    """In place on qkv [N, (nq + 2 nkv) d]: bias, per-head RMSNorm of q and k, rotary; k and v are
+    stored to their page slots (pages [P, 2, nkv, page_size, d])."""
+    N = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim,
+          "qkv must be contiguous [tokens, (heads + 2 kv heads) * head_dim]")
+    if pages is not None:
+        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and
+              tuple(pages.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "pages have the wrong layout")
+        _need(slots is not None, "a page write needs slots")
+    if slots is not None:
+        _i32(slots, "slots")
+        _need(slots.numel() == N, "one slot per token")
+    w_dtype = F32
+    if q_weight is not None:
+        _need(k_weight is not None and q_weight.dtype == k_weight.dtype and q_weight.numel() == head_dim and
+              k_weight.numel() == head_dim, "q/k norm weights must have head_dim entries of one type")
+        w_dtype = dtype_code(q_weight.dtype)
+    if rotary_dim:
+        _need(cos is not None and sin is not None and cos.shape == (N, rotary_dim // 2) and cos.dtype == torch.float32
+              and cos.is_contiguous() and sin.is_contiguous(), "rotary tables must be float32 [tokens, rotary_dim / 2]")
+    if bias is not None:
+        _need(bias.numel() == qkv.shape[1] and bias.is_contiguous(), "qkv bias has the wrong size")
+    _call("llmp_qkv_post", _ptr(qkv), dtype_code(qkv.dtype), _ptr(bias),
+          dtype_code(bias.dtype) if bias is not None else F32, _ptr(q_weight), _ptr(k_weight), w_dtype, float(eps),
+          _ptr(cos), _ptr(sin), int(rotary_dim), _ptr(slots), _ptr(pages), N, num_heads, num_kv_heads, head_dim,
+          int(page_size), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]"""
+    N, two_i = gate_up.shape
+    _need(gate_up.is_contiguous() and out.is_contiguous() and out.shape == (N, two_i // 2) and
+          out.dtype == gate_up.dtype and two_i % 2 == 0, "swiglu shapes do not match")
+    _call("llmp_swiglu", _ptr(gate_up), _ptr(out), dtype_code(out.dtype), N, two_i // 2, _stream())
+    return out
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias) on the CUDA cores with float32 accumulation."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm shapes do not match")
+    _need(a.dtype == w.dtype, "gemm operands must have one type")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
+    if bias is not None:
+        _need(bias.numel() == N and bias.is_contiguous(), "gemm bias has the wrong size")
+    _call("llmp_gemm_simt", _ptr(a), _ptr(w), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+          _ptr(out), dtype_code(a.dtype), dtype_code(out.dtype), M, N, K, a.stride(0), w.stride(0), out.stride(0),
+          _stream())
+    return out
+
+
+def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
+                    block_tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
+                    tile_req: torch.Tensor, tile_tok0: torch.Tensor, num_heads: int, num_kv_heads: int,
+                    head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+    """Causal attention of the step's query rows over the paged keys and values (general kernel)."""
+    for name, t in (("block_tables", block_tables), ("q_start", q_start), ("ctx_len", ctx_len),
+                    ("tile_req", tile_req), ("tile_tok0", tile_tok0)):
+        _i32(t, name)
+    _need(q.dtype == pages.dtype == out.dtype, "q, pages and out must have one type")
+    _need(out.is_contiguous() and out.shape[1] == num_heads * head_dim, "attention output must be [tokens, heads * head_dim]")
+    _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (2, num_kv_heads, page_size, head_dim),
+          "pages have the wrong layout")
+    _call("llmp_paged_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages),
+          dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(q_start), _ptr(ctx_len),
+          _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), num_heads, num_kv_heads, head_dim, page_size,
+          int(window), float(scale), _stream())
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
+    _i32(out, "out")
+    _call("llmp_argmax", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _stream())
+    return out
+
+
+def repetition_penalty(logits: torch.Tensor, tokens: torch.Tensor, offsets: torch.Tensor, penalty: torch.Tensor) -> None:
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
+    _i32(tokens, "tokens")
+    _i32(offsets, "offsets")
+    _need(penalty.dtype == torch.float32 and penalty.numel() == logits.shape[0], "one penalty per row")
+    _call("llmp_repetition_penalty", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(tokens),
+          _ptr(offsets), _ptr(penalty), _stream())
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, out_u: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """params: int32 [M, 8] rows {temperature, top_k, top_p, min_p, typical_p, seed low, seed high, step}
+    with the float fields stored by bit pattern."""
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
+    _need(params.dtype == torch.int32 and params.is_contiguous() and params.shape == (logits.shape[0], 8),
+          "sampling parameters must be int32 [rows, 8]")
+    _i32(out, "out")
+    _call("llmp_sample", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(params), _ptr(out),
+          _ptr(out_u), _stream())
+    return out

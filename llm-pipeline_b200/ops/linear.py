@@ -1,0 +1,49 @@
+"""y = x W^T (+ bias): which matrix product runs for which types and sizes.
+
+* float32 operands: always the CUDA-core kernel of ``csrc/gemm_simt.cu`` — a true 32-bit product
+  whose result for a row does not depend on the other rows.
+* bfloat16 operands: this package's tensor-core kernels where they cover the shape (registered in
+  ``_BF16_KERNELS`` by the modules that bind them), else the library product (cuBLAS through
+  ``torch``), which is what the reference's ``nn.Linear`` layers call
+  (src/llm_pipeline/models/qwen3/custom_builder.py:75-78,201-203,387).
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+
+from . import kernels
+
+# Each entry: fn(x, weight, out_dtype) -> tensor or None (None: "not my shape").
+_BF16_KERNELS: List[Callable] = []
+
+
+def register_bf16_kernel(fn: Callable) -> None:
+    _BF16_KERNELS.append(fn)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type)."""
+    if not x.is_cuda:
+        raise kernels.KernelError("linear() was given a CPU tensor; this engine has no CPU path")
+    out_dtype = out_dtype or x.dtype
+    M, N = x.shape[0], weight.shape[0]
+    if x.dtype == torch.float32:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        if M:
+            kernels.gemm_simt(x, weight, out, bias)
+        return out
+    for fn in _BF16_KERNELS:
+        out = fn(x, weight, out_dtype)
+        if out is not None:
+            return out if bias is None else out.add_(bias.to(out.dtype))
+    if M == 0:
+        return torch.empty((0, N), dtype=out_dtype, device=x.device)
+    if out_dtype == x.dtype:
+        out = torch.mm(x, weight.t())
+    else:
+        out = torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return out if bias is None else out.add_(bias.to(out.dtype))

@@ -1,0 +1,115 @@
+"""Interfaces of the parts a model is put together from.
+
+Every part takes its sizes and constants as constructor parameters, declares the tensors it
+expects (``param_specs``: full tensor name -> ``ParamSpec``), receives them through ``load`` and
+works on the tensors of one step. No part knows which model it is in.
+
+* ``Norm.add_norm(stream, rows=None)``: folds the stream's pending sum into the float32 residual
+  and returns the normalised rows in the compute type.
+* ``PositionEncoding.tables(ctx)``: per-step tensors derived from the token positions (for the
+  rotary kind: float32 cos/sin ``[tokens, rotary_dim / 2]``).
+* ``Mixer.forward(x, ctx, cache) -> (out, bias)``: mixes tokens of the same request; ``cache`` is
+  the ``LayerCache`` of this execution (pages and/or a state tensor). ``cache_spec()`` and
+  ``state_spec()`` tell the cache manager what it needs.
+* ``FeedForward.forward(x, ctx) -> (out, bias)``: works on each token alone.
+* ``Block.forward(stream, ctx, cache)``: the arrangement of the above around the residual stream.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+
+from ..cache.spec import KVPagesSpec, StateSpec
+from ..weights.source import ParamSpec
+
+TensorGetter = Callable[[str, str], torch.Tensor]   # (full tensor name, role) -> tensor on the device
+
+
+@dataclass
+class LayerCache:
+    """What one execution of a layer may touch: the pages of its cache id (``writes`` is False when
+    an earlier execution owns them), the index of their group (for block tables and slot
+    mappings in the step context), and the state tensor ``[slots, ...]`` of its cache id."""
+
+    pages: Optional[torch.Tensor] = None
+    group: Optional[int] = None
+    state: Optional[torch.Tensor] = None
+    writes: bool = True
+
+
+class ResidualStream:
+    """The hidden state between parts: a float32 residual ``[tokens, hidden]`` and a pending
+    addend in the compute type (with an optional bias vector) that the next norm folds in."""
+
+    def __init__(self, residual: torch.Tensor):
+        self.residual = residual
+        self.pending: Optional[torch.Tensor] = None
+        self.pending_bias: Optional[torch.Tensor] = None
+
+    def add(self, delta: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        if self.pending is not None:
+            raise RuntimeError("the residual stream already holds a pending addend")
+        self.pending, self.pending_bias = delta, bias
+
+
+class Part:
+    prefix: str = ""
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def load(self, get: TensorGetter) -> None:
+        pass
+
+
+class Norm(Part):
+    def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def tables(self, ctx):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[KVPagesSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx) -> torch.Tensor:
+        """float32 residual [tokens, hidden] of ctx.token_ids"""
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """float32 logits [rows, vocab]"""
+        raise NotImplementedError
+
+
+class Block:
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        raise NotImplementedError

@@ -1,0 +1,22 @@
+"""Arrangements of a mixer, a feed-forward and their norms around the residual stream.
+
+``pre_norm_residual`` is the decoder layer of
+src/llm_pipeline/models/qwen3/custom_builder.py:222-255: ``x += mixer(norm1(x))`` then
+``x += feed_forward(norm2(x))``. The sums are not taken here: each part's output is left pending
+on the stream and the next norm kernel adds it into the float32 residual."""
+
+from __future__ import annotations
+
+from .base import Block, LayerCache, ResidualStream
+from .registry import register_block
+
+
+@register_block("pre_norm_residual")
+class PreNormResidualBlock(Block):
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        h = self.mixer_norm.add_norm(stream, ctx)
+        out, bias = self.mixer.forward(h, ctx, cache)
+        stream.add(out, bias)
+        h = self.feed_forward_norm.add_norm(stream, ctx)
+        out, bias = self.feed_forward.forward(h, ctx)
+        stream.add(out, bias)

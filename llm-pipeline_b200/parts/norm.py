@@ -1,0 +1,39 @@
+"""RMSNorm fused with the residual add.
+
+Formula of src/llm_pipeline/models/qwen3/custom_builder.py:53-58: in float32,
+``weight * (x * rsqrt(mean(x^2) + eps))``, rounded once to the compute type. The residual adds of
+custom_builder.py:244,250 are folded in: the addend left by the previous part is summed into the
+float32 residual by the same kernel that normalises it."""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import kernels
+from ..weights.source import ParamSpec
+from .base import Norm, ResidualStream, TensorGetter
+from .registry import register_norm
+
+
+@register_norm("rms_norm")
+class RMSNorm(Norm):
+    def __init__(self, prefix: str, size: int, eps: float):
+        self.prefix, self.size, self.eps = prefix, int(size), float(eps)
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {f"{self.prefix}.weight": ParamSpec((self.size,), role="vector", init="norm")}
+
+    def load(self, get: TensorGetter) -> None:
+        self.weight = get(f"{self.prefix}.weight", "vector").contiguous()
+
+    def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        count = rows.numel() if rows is not None else stream.residual.shape[0]
+        out = torch.empty((count, self.size), dtype=ctx.dtype, device=stream.residual.device)
+        kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out,
+                            delta_bias=stream.pending_bias, rows=rows)
+        if rows is None:
+            stream.pending, stream.pending_bias = None, None
+        return out

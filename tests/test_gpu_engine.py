@@ -1,0 +1,53 @@
+"""The engine against the plain implementation under every way of cutting the work, in float32
+and in bfloat16, at tiny configurations that differ in every size and option."""
+
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    pytest.param(plain.TINY_A, 0, 16, (5, 17, 33), id="tiny_a"),
+    pytest.param(plain.TINY_B, 1, 8, (1, 9, 24, 40), id="tiny_b"),
+    pytest.param(plain.TINY_C, 2, 16, (3, 50, 21), id="tiny_c"),
+]
+DTYPES = [pytest.param(torch.float32, id="f32"), pytest.param(torch.bfloat16, id="bf16")]
+
+
+def _requests(config, lengths, extra=8):
+    return {f"r{i}": H.random_tokens(config["vocab_size"], n + extra, 1000 + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("config,seed,page,lengths", CASES)
+def test_cuts_match_plain(tmp_path, config, seed, page, lengths, dtype):
+    folder, weights = H.make_case(tmp_path, config, seed, dtype)
+    requests = _requests(config, lengths)
+    want = H.expected_logits(config, weights, requests)
+    tol = H.TOL[dtype]
+    runner = H.make_runner(folder, dtype, page_size=page, num_pages=64)
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, tol, "whole")
+    H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=32)), want, tol, "tail one by one")
+    H.assert_close(H.replay(runner, H.cut_portions(requests, (7, 2, 16, 3, 5))), want, tol, "portions")
+    H.assert_close(H.replay(runner, H.cut_portions(requests, (1,))), want, tol, "token by token")
+    assert runner.cache.num_live == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("config,seed,page,lengths", CASES)
+def test_mixed_batches_with_page_reuse(tmp_path, config, seed, page, lengths, dtype):
+    folder, weights = H.make_case(tmp_path, config, seed, dtype)
+    lengths = tuple(lengths) + (29, 12, 44, 7)
+    requests = _requests(config, lengths)
+    want = H.expected_logits(config, weights, requests)
+    # pages for four live requests of the longest length, and no more: later requests reuse pages
+    longest = max(len(t) for t in requests.values())
+    num_pages = 4 * (-(-longest // page))
+    runner = H.make_runner(folder, dtype, page_size=page, num_pages=num_pages)
+    got = H.replay(runner, H.cut_mixed(requests, (7, 2, 16, 3, 5), max_live=4))
+    H.assert_close(got, want, H.TOL[dtype], "mixed")
+    assert runner.cache.pages_reused > 0
+    assert runner.cache.num_live == 0
