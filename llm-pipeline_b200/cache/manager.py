@@ -186,7 +186,7 @@ class CacheManager:
         """Per group, how many pages ``reserve(req_id, new_length)`` would have to take."""
         out = []
         for group in self.groups:
-            table = group.tables[req_id]
+            table = group.tables.get(req_id, ())   # a request that is not admitted yet holds nothing
             want = -(-new_length // self.page_size)
             out.append(max(0, want - len(table)))
         return out

@@ -1,0 +1,148 @@
+"""Generation: requests in, token ids out, through the scheduler, the step function and the sampler.
+
+``GenerationEngine`` is the architecture-neutral engine; ``llm_pipeline_b200.inference`` wraps it
+under the reference's names (``Qwen3InferenceEngine``, ``Qwen3InferenceConfig``). One ``step()``
+plans a batch (``Scheduler.schedule``), runs it (``ModelRunner.step``) asking for logits only at
+the last token of the requests that are due a new token, samples, and records the result. The
+reference's loop for one prompt is src/llm_pipeline/inference/qwen3_engine.py:472-550: prefill,
+then one token per model call, stopping at EOS or ``max_tokens``.
+"""
+
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field, replace
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import CacheManager
+from ..config import ModelConfig, load_config
+from ..models import Model, build_model, load_model
+from ..sampling import Sampler, SamplingConfig
+from .runner import ModelRunner, StepEntry
+from .scheduler import Request, Scheduler, StepPlan
+
+
+@dataclass
+class GenerationResult:
+    req_id: Hashable
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finish_reason: Optional[str]
+    preemptions: int = 0
+    text: Optional[str] = None
+
+
+class GenerationEngine:
+    def __init__(self, model: Model, config: Optional[ModelConfig] = None, *, page_size: int = 16,
+                 num_pages: Optional[int] = None, memory_fraction: float = 0.8, max_num_seqs: int = 64,
+                 max_num_batched_tokens: int = 2048, max_model_len: Optional[int] = None,
+                 max_prefill_chunk: Optional[int] = None, sampling: Optional[SamplingConfig] = None):
+        self.model, self.config = model, config
+        self.device, self.dtype = model.device, model.dtype
+        max_model_len = int(max_model_len or model.spec.max_position)
+        specs = model.cache_specs()
+        if num_pages is None:
+            num_pages = self._pages_that_fit(specs, page_size, memory_fraction, max_num_seqs, max_model_len)
+        self.cache = CacheManager(specs, page_size=page_size, num_pages=num_pages, max_requests=max_num_seqs,
+                                  max_request_tokens=max_model_len, device=self.device, dtype=self.dtype)
+        self.runner = ModelRunner(model, self.cache)
+        self.scheduler = Scheduler(self.cache, max_num_seqs, max_num_batched_tokens, max_model_len, max_prefill_chunk)
+        self.sampler = Sampler(sampling)
+        self._ids = itertools.count()
+        self._requests: Dict[Hashable, Request] = {}
+        self.steps = 0
+        self.tokens_prefilled = 0
+        self.tokens_decoded = 0
+
+    @classmethod
+    def from_folder(cls, model_dir: str, device: str = "cuda:0", dtype: torch.dtype = torch.bfloat16, **kwargs):
+        config, model = load_model(model_dir, device, dtype)
+        return cls(model, config, **kwargs)
+
+    def _pages_that_fit(self, specs, page_size: int, fraction: float, max_num_seqs: int, max_model_len: int) -> int:
+        """Pages per group from the device memory that is free after the weights: ``fraction`` of it,
+        capped at what ``max_num_seqs`` requests of ``max_model_len`` tokens can use."""
+        element = 4 if self.dtype == torch.float32 else 2
+        per_page = sum(2 * kv.num_kv_heads * kv.head_dim * page_size * element for kv, _ in specs if kv is not None)
+        if per_page == 0:
+            return 1
+        free, _total = torch.cuda.mem_get_info(self.device)
+        cap = max_num_seqs * -(-max_model_len // page_size)
+        return max(1, min(cap, int(free * fraction) // per_page))
+
+    # -- requests --------------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], max_tokens: int = 16,
+                    sampling: Optional[SamplingConfig] = None, eos_token_ids: Optional[Sequence[int]] = None,
+                    ignore_eos: bool = False, req_id: Optional[Hashable] = None) -> Hashable:
+        req_id = next(self._ids) if req_id is None else req_id
+        if req_id in self._requests and self._requests[req_id].status != "finished":
+            raise ValueError(f"request id {req_id!r} is in use")
+        for t in prompt_token_ids:
+            if not 0 <= int(t) < self.model.spec.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.model.spec.vocab_size}")
+        if eos_token_ids is None:
+            eos_token_ids = self.config.eos_token_ids() if self.config is not None else []
+        request = Request(req_id, [int(t) for t in prompt_token_ids], sampling or self.sampler.config,
+                          int(max_tokens), set(int(t) for t in eos_token_ids), ignore_eos)
+        self.scheduler.add(request)
+        self._requests[req_id] = request
+        return req_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # -- one step --------------------------------------------------------------------------
+    def step(self) -> List[Request]:
+        """Plan, run and record one batch; returns the requests that finished in it."""
+        plan: StepPlan = self.scheduler.schedule()
+        finished = list(plan.aborted)
+        if not plan.entries:
+            if not finished and self.scheduler.has_unfinished():
+                raise RuntimeError("the scheduler could not plan a step although requests are unfinished")
+            return finished
+        entries = [StepEntry(e.request.req_id, e.token_ids, [e.count - 1] if e.samples else []) for e in plan.entries]
+        logits = self.runner.step(entries)
+        sampled: Dict[Hashable, int] = {}
+        due = [e for e in plan.entries if e.samples]
+        if due:
+            tokens = self.sampler.sample_rows(
+                logits, [e.request.sampling for e in due], [len(e.request.output) for e in due],
+                [e.request.output if e.request.sampling.repetition_penalty != 1.0 else None for e in due])
+            for e, token in zip(due, tokens.tolist()):
+                sampled[e.request.req_id] = token
+        self.steps += 1
+        for e in plan.entries:
+            if e.count == 1 and e.request.output:
+                self.tokens_decoded += 1
+            else:
+                self.tokens_prefilled += e.count
+        finished += self.scheduler.finish_step(plan, sampled)
+        return finished
+
+    # -- whole generations -------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 16, temperature: Optional[float] = None,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, seed: Optional[int] = None,
+                 ignore_eos: bool = False, **sampling_overrides) -> List[GenerationResult]:
+        """Generate for every prompt (lists of token ids); results in the order of the prompts.
+        Prompt i samples with seed ``seed + i``."""
+        base = self.sampler.config.merged({"temperature": temperature, "top_k": top_k, "top_p": top_p,
+                                           **sampling_overrides})
+        first_seed = base.seed if seed is None else int(seed)
+        ids = [self.add_request(p, max_tokens, replace(base, seed=first_seed + i), ignore_eos=ignore_eos)
+               for i, p in enumerate(prompts)]
+        while any(self._requests[i].status != "finished" for i in ids):
+            self.step()
+        results = []
+        for i in ids:
+            r = self._requests.pop(i)
+            results.append(GenerationResult(i, r.prompt, r.output, r.finish_reason, r.preemptions))
+        return results
+
+    def stats(self) -> Dict[str, object]:
+        out = {"steps": self.steps, "tokens_prefilled": self.tokens_prefilled, "tokens_decoded": self.tokens_decoded}
+        out.update(self.scheduler.stats())
+        out.update(self.cache.stats())
+        return out

@@ -1,0 +1,154 @@
+"""The Python entry point under the reference's names.
+
+``Qwen3InferenceConfig`` keeps the field names and meanings of
+src/llm_pipeline/inference/qwen3_engine.py:21-83 where this engine has the thing they configure
+(model path, device, dtype, generation and sampling defaults, ``max_batch_size``,
+``block_size`` / ``num_blocks`` / ``max_sequence_length`` / ``memory_fraction`` of the paged
+cache) and adds the token budget of the scheduler. Fields of the reference that switch between
+its alternative code paths (``use_paged_attention``, ``enable_continuous_batching``,
+``use_cuda_graphs``, ``use_torch_compile``, ``use_flash_attention``, tensor parallelism, prefix
+and LRU caches) have no counterpart: there is one path, paged and continuously batched.
+
+``Qwen3InferenceEngine.generate(prompt, max_tokens, temperature, top_k, top_p)`` follows
+:311-350: a string gives a string, a list of strings gives a list. Prompts may also be lists of
+token ids (a model folder with random weights has no tokenizer); the result is then a list of
+token ids per prompt.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .engine.generate import GenerationEngine, GenerationResult
+from .sampling import SamplingConfig
+
+_DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp32": torch.float32, "float32": torch.float32}
+
+
+@dataclass
+class Qwen3InferenceConfig:
+    model_path: str
+    device: str = "cuda:0"
+    dtype: Union[torch.dtype, str] = torch.bfloat16
+    # generation (reference :36-49)
+    max_length: int = 2048
+    max_new_tokens: int = 512
+    temperature: float = 1.0
+    top_p: float = 0.9
+    top_k: int = 50
+    repetition_penalty: float = 1.0
+    typical_p: float = 1.0
+    min_p: float = 0.0
+    do_sample: bool = True
+    pad_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None
+    seed: int = 0
+    # batching and cache (reference :52-71)
+    max_batch_size: int = 8
+    block_size: int = 16
+    num_blocks: Optional[int] = None
+    max_sequence_length: int = 2048
+    memory_fraction: float = 0.8
+    # scheduler
+    max_num_batched_tokens: int = 2048
+    max_prefill_chunk: Optional[int] = None
+
+
+def resolve_dtype(dtype: Union[torch.dtype, str]) -> torch.dtype:
+    if isinstance(dtype, str):
+        if dtype not in _DTYPES:
+            raise ValueError(f"dtype {dtype!r} is not supported; this engine computes in bf16 or fp32")
+        return _DTYPES[dtype]
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"dtype {dtype} is not supported; this engine computes in bfloat16 or float32")
+    return dtype
+
+
+class Qwen3InferenceEngine:
+    def __init__(self, config: Qwen3InferenceConfig):
+        self.config = config
+        self.device = torch.device(config.device)
+        dtype = resolve_dtype(config.dtype)
+        sampling = SamplingConfig(temperature=config.temperature, top_k=config.top_k, top_p=config.top_p,
+                                  repetition_penalty=config.repetition_penalty, typical_p=config.typical_p,
+                                  min_p=config.min_p, do_sample=config.do_sample, pad_token_id=config.pad_token_id,
+                                  eos_token_id=config.eos_token_id, seed=config.seed)
+        self.engine = GenerationEngine.from_folder(
+            config.model_path, device=config.device, dtype=dtype, page_size=config.block_size,
+            num_pages=config.num_blocks, memory_fraction=config.memory_fraction, max_num_seqs=config.max_batch_size,
+            max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=config.max_sequence_length,
+            max_prefill_chunk=config.max_prefill_chunk, sampling=sampling)
+        self.model_config = self.engine.config
+        self.tokenizer = self._load_tokenizer(config.model_path)
+        if self.tokenizer is not None:
+            if config.pad_token_id is None:
+                config.pad_token_id = getattr(self.tokenizer, "pad_token_id", None)
+            if config.eos_token_id is None:
+                config.eos_token_id = getattr(self.tokenizer, "eos_token_id", None)
+
+    @staticmethod
+    def _load_tokenizer(path: str):
+        """The tokenizer of the model folder, if it has one (the reference loads it with
+        ``AutoTokenizer``, src/llm_pipeline/models/qwen3/factory.py:97)."""
+        if not any(os.path.isfile(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json", "vocab.json")):
+            return None
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(path, local_files_only=True)
+
+    def _eos_ids(self) -> List[int]:
+        ids = set(self.model_config.eos_token_ids())
+        if self.config.eos_token_id is not None:
+            ids.add(int(self.config.eos_token_id))
+        return sorted(ids)
+
+    def generate(self, prompt, max_tokens: Optional[int] = None, temperature: Optional[float] = None,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, **kwargs):
+        single = isinstance(prompt, str) or (isinstance(prompt, Sequence) and len(prompt) > 0
+                                             and isinstance(prompt[0], int))
+        prompts = [prompt] if single else list(prompt)
+        as_text = all(isinstance(p, str) for p in prompts)
+        if as_text:
+            if self.tokenizer is None:
+                raise ValueError("the model folder has no tokenizer; pass prompts as lists of token ids")
+            token_prompts = [self.tokenizer(p)["input_ids"] for p in prompts]
+        else:
+            token_prompts = [list(p) for p in prompts]
+        results = self.generate_ids(token_prompts, max_tokens, temperature, top_k, top_p, **kwargs)
+        if as_text:
+            outs = [self.tokenizer.decode(r.token_ids, skip_special_tokens=True) for r in results]
+        else:
+            outs = [r.token_ids for r in results]
+        return outs[0] if single else outs
+
+    def generate_ids(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None,
+                     temperature: Optional[float] = None, top_k: Optional[int] = None, top_p: Optional[float] = None,
+                     **kwargs) -> List[GenerationResult]:
+        max_tokens = max_tokens or self.config.max_new_tokens
+        results: List[GenerationResult] = []
+        prompts = list(prompts)
+        eos = self._eos_ids()
+        base = self.engine.sampler.config.merged({"temperature": temperature, "top_k": top_k, "top_p": top_p, **kwargs})
+        from dataclasses import replace
+        ids = [self.engine.add_request(p, max_tokens, replace(base, seed=base.seed + i), eos_token_ids=eos,
+                                       ignore_eos=bool(kwargs.get("ignore_eos", False)))
+               for i, p in enumerate(prompts)]
+        done = {}
+        while len(done) < len(ids):
+            for request in self.engine.step():
+                done[request.req_id] = request
+        for i in ids:
+            r = done[i]
+            self.engine._requests.pop(i, None)
+            results.append(GenerationResult(i, r.prompt, r.output, r.finish_reason, r.preemptions))
+        return results
+
+    def batch_generate(self, prompts, **kwargs):
+        return self.generate(list(prompts), **kwargs)
+
+    def get_stats(self):
+        return self.engine.stats()

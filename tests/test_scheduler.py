@@ -1,0 +1,163 @@
+"""The scheduler's decisions, with the cache manager keeping books only and a stand-in for the
+step function that reserves, commits and hands back scripted tokens."""
+
+import pytest
+
+from llm_pipeline_b200.cache import CacheManager, KVPagesSpec
+from llm_pipeline_b200.engine.scheduler import Request, Scheduler
+from llm_pipeline_b200.sampling import SamplingConfig
+
+
+def make(num_pages=64, page_size=4, max_seqs=4, budget=16, chunk=None, max_len=256):
+    cache = CacheManager([(KVPagesSpec(1, 16), None)], page_size=page_size, num_pages=num_pages, max_requests=8,
+                         max_request_tokens=max_len, device=None)
+    return cache, Scheduler(cache, max_seqs, budget, max_len, chunk)
+
+
+def request(rid, prompt_len, max_tokens=4, eos=()):
+    return Request(rid, list(range(1, prompt_len + 1)), SamplingConfig(), max_tokens, set(eos))
+
+
+def run_step(cache, sched, token=lambda req: 100 + len(req.output)):
+    """What the engine does around a plan: admit, reserve, commit, sample."""
+    plan = sched.schedule()
+    for e in plan.entries:
+        if e.request.req_id not in cache:
+            cache.admit(e.request.req_id)
+        assert e.start == cache.length(e.request.req_id)
+        assert cache.reserve(e.request.req_id, e.start + e.count), "the plan must fit the pages"
+        cache.commit(e.request.req_id, e.start + e.count)
+    sampled = {e.request.req_id: token(e.request) for e in plan.entries if e.samples}
+    finished = sched.finish_step(plan, sampled)
+    cache.check()
+    return plan, finished
+
+
+def test_prompt_is_cut_under_the_token_budget_and_then_decodes():
+    cache, sched = make(budget=16)
+    sched.add(request("a", 40, max_tokens=3))
+    sizes, samples = [], []
+    while sched.has_unfinished():
+        plan, _ = run_step(cache, sched)
+        sizes.append([e.count for e in plan.entries])
+        samples.append([e.samples for e in plan.entries])
+    assert sizes == [[16], [16], [8], [1], [1]]
+    assert samples == [[False], [False], [True], [True], [True]]
+    assert cache.num_live == 0 and cache.groups[0].pool.num_free == 64
+
+
+def test_decodes_go_first_and_prompts_fill_the_rest():
+    cache, sched = make(budget=12, chunk=8)
+    sched.add(request("a", 5, max_tokens=8))
+    run_step(cache, sched)                      # a: whole prompt, first token
+    sched.add(request("b", 30, max_tokens=2))
+    sched.add(request("c", 6, max_tokens=2))
+    plan, _ = run_step(cache, sched)
+    assert [(e.request.req_id, e.count, e.samples) for e in plan.entries] == [("a", 1, True), ("b", 8, False), ("c", 3, False)]
+    plan, _ = run_step(cache, sched)            # a decodes; b (admitted first) continues; c gets what is left
+    assert [(e.request.req_id, e.count) for e in plan.entries] == [("a", 1), ("b", 8), ("c", 3)]
+    assert plan.num_tokens <= 12
+
+
+def test_admission_is_limited_by_sequences_and_keeps_arrival_order():
+    cache, sched = make(max_seqs=2, budget=64)
+    for rid, n in (("a", 4), ("b", 4), ("c", 4)):
+        sched.add(request(rid, n, max_tokens=2))
+    plan, _ = run_step(cache, sched)
+    assert [e.request.req_id for e in plan.entries] == ["a", "b"] and [r.req_id for r in sched.waiting] == ["c"]
+    plan, finished = run_step(cache, sched)     # a and b finish (2 tokens), c still waits in this step
+    assert sorted(r.req_id for r in finished) == ["a", "b"]
+    plan, _ = run_step(cache, sched)
+    assert [e.request.req_id for e in plan.entries] == ["c"]
+
+
+def test_finish_on_eos_length_and_model_len():
+    cache, sched = make(max_len=12)
+    sched.add(request("eos", 3, max_tokens=10, eos={101}))
+    sched.add(request("len", 3, max_tokens=2))
+    sched.add(request("ctx", 9, max_tokens=50))
+    reasons = {}
+    while sched.has_unfinished():
+        _, finished = run_step(cache, sched)
+        reasons.update({r.req_id: (r.finish_reason, len(r.output)) for r in finished})
+    assert reasons == {"eos": ("stop", 2), "len": ("length", 2), "ctx": ("length", 3)}
+    with pytest.raises(ValueError, match="no room"):
+        sched.add(request("big", 12))
+    with pytest.raises(ValueError, match="empty"):
+        sched.add(request("none", 0))
+
+
+def test_waiting_request_is_not_admitted_without_pages_and_nobody_overtakes():
+    cache, sched = make(num_pages=6, page_size=4, budget=64)       # 24 tokens in all
+    sched.add(request("a", 14, max_tokens=6))
+    sched.add(request("b", 12, max_tokens=2))
+    sched.add(request("c", 2, max_tokens=2))
+    plan, _ = run_step(cache, sched)
+    assert [e.request.req_id for e in plan.entries] == ["a"]       # b needs 3 pages, 2 are free; c stays behind b
+    assert [r.req_id for r in sched.waiting] == ["b", "c"] and not plan.preempted
+
+
+def test_running_out_of_pages_preempts_the_newest_and_recomputes_it():
+    cache, sched = make(num_pages=6, page_size=4, budget=64)
+    sched.add(request("a", 11, max_tokens=12))
+    sched.add(request("b", 9, max_tokens=12))
+    run_step(cache, sched)                                          # a: 3 pages, b: 3 pages -> pool is full
+    outputs_before = None
+    preempted_at = None
+    for step in range(40):
+        plan, _ = run_step(cache, sched)
+        if plan.preempted and preempted_at is None:
+            preempted_at = step
+            assert [r.req_id for r in plan.preempted] == ["b"]      # the request admitted last
+            assert sched.waiting[0].req_id == "b" and sched.waiting[0].computed == 0
+            assert "b" not in cache
+            assert [e.request.req_id for e in plan.entries] == ["a"]
+            outputs_before = list(sched.waiting[0].output)
+        if not sched.has_unfinished():
+            break
+    assert preempted_at is not None and sched.num_preemptions >= 1
+    assert not sched.has_unfinished() and cache.num_live == 0
+    assert cache.groups[0].pool.num_free == 6
+    assert outputs_before is not None
+
+
+def test_preempted_request_is_recomputed_from_prompt_plus_output():
+    cache, sched = make(num_pages=5, page_size=4, budget=64)
+    a, b = request("a", 8, max_tokens=9), request("b", 7, max_tokens=9)
+    sched.add(a)
+    sched.add(b)
+    done = {}
+    portions = []
+    for _ in range(60):
+        plan, finished = run_step(cache, sched)
+        portions += [(e.request.req_id, e.start, e.count) for e in plan.entries if e.request is b]
+        done.update({r.req_id: r for r in finished})
+        if not sched.has_unfinished():
+            break
+    assert set(done) == {"a", "b"} and b.preemptions >= 1
+    restarts = [p for p in portions if p[1] == 0]
+    assert len(restarts) == 1 + b.preemptions
+    assert restarts[1][2] > 7                    # the recomputation covers the prompt and the generated tokens
+    assert done["b"].output == [100 + i for i in range(9)]       # every token sampled once, in order
+
+
+def test_a_single_request_that_cannot_fit_is_finished_not_looped():
+    cache, sched = make(num_pages=2, page_size=4, budget=64)
+    sched.add(request("a", 6, max_tokens=50))
+    reasons = []
+    for _ in range(10):
+        plan, finished = run_step(cache, sched)
+        reasons += [r.finish_reason for r in finished] + [r.finish_reason for r in plan.aborted]
+        if not sched.has_unfinished():
+            break
+    assert reasons == ["out_of_pages"] and cache.num_live == 0
+    sched.add(request("b", 20, max_tokens=2))                     # cannot even start
+    plan, _ = run_step(cache, sched)
+    assert [r.finish_reason for r in plan.aborted] == ["out_of_pages"] and not sched.has_unfinished()
+
+
+def test_abort_frees_pages():
+    cache, sched = make()
+    sched.add(request("a", 9))
+    run_step(cache, sched)
+    assert sched.abort("a").finish_reason == "abort" and cache.num_live == 0 and not sched.has_unfinished()
