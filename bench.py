@@ -1,0 +1,372 @@
+"""Serving benchmark on one B200: decode tokens per second of a Qwen3-8B-shaped model.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+The default run has the layer sizes of the Qwen3-8B configuration (36 layers, hidden 4096, 32 query
+and 8 key/value heads of 128, intermediate 12288, vocabulary 151936) with random bfloat16 weights,
+a batch of 8 requests and 2,048 tokens of context each. A "step" is one decode step: one new token
+for every request of the batch, from the embedding to the sampled token id. It prints one JSON line:
+``value`` is decoded tokens per second timed on the device with CUDA events; ``e2e`` is the same
+through the Python entry point (``GenerationEngine.step``: host token lists in, host token ids out,
+the index arrays copied from pinned memory every step); ``prefill`` is one 2,048-token prompt in one
+step; ``roofline`` is the decode step against the bytes it must read; ``points`` are decode at batch
+1 and 64. All weights and token ids are synthetic (seeded); the inputs are far larger than L2, so
+no flush is needed between iterations.
+
+``--impl reference`` runs DavidAkinpelu/llm-pipeline's own ``Qwen3ForCausalLM`` from
+``baseline/_ref`` (installed offline with pip --no-deps --target) with its ``past_key_values``
+loop at the same sizes and prints the same line with ``"impl": "reference"``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "attention_bias": False,
+    "max_position_embeddings": 4096, "hidden_act": "silu",
+}
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            return {"hbm_gbs": float(data["hbm_gbs"]),
+                    "bf16_tflops": float(data.get("bf16_tflops_sustained") or data["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, max_clock = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.samples:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(int(float(parts[0])))
+                max_clock = int(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def weight_bytes(cfg, layers, element=2):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d, nq, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    per_layer = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I + 2 * H + 2 * d
+    return (layers * per_layer + V * H + H) * element          # the layers, the output head and the final norm
+
+
+def kv_bytes_per_token(cfg, layers, element=2):
+    return 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * layers * element
+
+
+def prefill_flops(cfg, layers, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d, nq, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    per_token = 2 * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I)
+    attention = 4 * nq * d * T * (T + 1) / 2           # causal QK^T and PV
+    return layers * (per_token * T + attention) + 2 * V * H
+
+
+def build_ours(cfg, layers, batch_cap, dtype):
+    import torch
+
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.engine.generate import GenerationEngine
+    from llm_pipeline_b200.models import build_model
+    from llm_pipeline_b200.ops import build_library
+    from llm_pipeline_b200.weights import random_tensors
+
+    build_library()
+    config = resolve_config({**cfg, "num_hidden_layers": layers})
+    model = build_model(config)
+    model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
+    tokens_per_request = CONTEXT + 128
+    pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
+    engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=pages, max_num_seqs=batch_cap,
+                              max_num_batched_tokens=PREFILL_TOKENS, max_model_len=tokens_per_request)
+    return engine
+
+
+def random_prompts(vocab, count, length, seed):
+    import torch
+
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (count, length), generator=gen).tolist()
+
+
+def time_decode(engine, batch, steps, warmup, seed, e2e=True):
+    """Device-timed decode steps through the step function, and wall-clock steps through
+    ``GenerationEngine.step`` (host lists in and out). Returns a dict of figures."""
+    import torch
+
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.ops import kernels
+    from llm_pipeline_b200.sampling import SamplingConfig
+
+    vocab = engine.model.spec.vocab_size
+    prompts = random_prompts(vocab, batch, CONTEXT - 1, seed)
+    runner = engine.runner
+    ids = [f"bench{seed}_{i}" for i in range(batch)]
+    # fill the cache: every request gets CONTEXT - 1 tokens, in portions of up to 2,048 tokens
+    for rid, prompt in zip(ids, prompts):
+        runner.step([StepEntry(rid, prompt, [])])
+    last = [p[-1] for p in prompts]
+    out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+    def one_step(tokens):
+        logits = runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)])
+        return kernels.argmax(logits, out)
+
+    tokens = last
+    for _ in range(warmup):
+        tokens = one_step(tokens).tolist()
+    torch.cuda.synchronize()
+    launches_before = kernels.launch_count
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        tokens = one_step(tokens).tolist()       # the sampled ids go to the host and come back as the next input
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    launches = kernels.launch_count - launches_before
+    h2d = runner.last_h2d_bytes
+    for rid in ids:
+        runner.release(rid)
+    if not e2e:
+        return {"ms": ms, "tok_s": batch * 1e3 / ms, "launches": launches, "h2d": h2d}
+
+    # end to end: the public entry point, requests in as host token lists, tokens out as host ints
+    greedy = SamplingConfig(temperature=0.0)
+    e2e_prompts = random_prompts(vocab, batch, CONTEXT - 1 - warmup, seed + 1)
+    for p in e2e_prompts:
+        engine.add_request(p, max_tokens=warmup + steps + 1, sampling=greedy, ignore_eos=True)
+    while any(r.num_pending > 1 or not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
+        engine.step()                            # prompts, portion by portion
+    for _ in range(warmup - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    e2e_h2d = runner.last_h2d_bytes
+    while engine.has_unfinished():
+        engine.step()
+    return {"ms": ms, "tok_s": batch * 1e3 / ms, "launches": launches, "h2d": h2d,
+            "e2e_ms": e2e_ms, "e2e_tok_s": batch * 1e3 / e2e_ms, "e2e_h2d": e2e_h2d, "e2e_d2h": batch * 4}
+
+
+def time_prefill(engine, tokens, repeats, warmup):
+    import torch
+
+    from llm_pipeline_b200.engine import StepEntry
+
+    vocab = engine.model.spec.vocab_size
+    runner = engine.runner
+    times = []
+    for i in range(warmup + repeats):
+        prompt = random_prompts(vocab, 1, tokens, 500 + i)[0]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry("prefill", prompt, [tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.release("prefill")
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run_ours(args):
+    import torch
+
+    cfg = QWEN3_8B
+    layers = args.layers or cfg["num_hidden_layers"]
+    peak = peaks()
+    dtype = torch.bfloat16
+    engine = build_ours(cfg, layers, max(64, args.batch), dtype)
+    clocks = ClockSampler()
+    clocks.start()
+    main = time_decode(engine, args.batch, args.steps, args.warmup, seed=1)
+    clock_info = clocks.stop()
+    points = {}
+    for b in (1, 64):
+        r = time_decode(engine, b, max(5, args.steps // 2), args.warmup, seed=10 + b, e2e=False)
+        points[f"decode_b{b}"] = round(r["tok_s"], 1)
+    prefill_ms = time_prefill(engine, PREFILL_TOKENS, repeats=5, warmup=3)
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    step_bytes = weight_bytes(cfg, layers) + args.batch * (CONTEXT + args.warmup + args.steps // 2) * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (main["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, 2,048-token context (Qwen3-8B bf16)",
+        "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_model": cfg["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+                   "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2, no flush", "peaks": peak["source"]},
+        "e2e": {"value": round(main["e2e_tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(main["e2e_ms"], 4),
+                "h2d_bytes_per_step": main["e2e_h2d"], "d2h_bytes_per_step": main["e2e_d2h"]},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_info,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    """The reference's own model class and cache loop, unmodified, from baseline/_ref."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "llm_pipeline")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --no-deps --target)"}))
+        return 0
+    sys.path.insert(0, ref_root)
+    try:
+        import torch
+        from llm_pipeline.models.qwen3.custom_builder import Qwen3Config as RefConfig, Qwen3ForCausalLM
+    except Exception as e:      # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:200]}))
+        return 0
+    cfg = dict(QWEN3_8B)
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    torch.manual_seed(0)
+    with torch.device("cuda:0"):
+        torch.set_default_dtype(torch.bfloat16)
+        model = Qwen3ForCausalLM(RefConfig(**cfg)).eval()
+        torch.set_default_dtype(torch.float32)
+    for p in model.parameters():
+        p.data.normal_(0, 0.02)
+    batch = args.batch
+    ids = torch.tensor(random_prompts(cfg["vocab_size"], batch, CONTEXT - 1, 1), device="cuda:0")
+    clocks = ClockSampler()
+    with torch.no_grad():
+        out = model(input_ids=ids, use_cache=True)
+        past = out.past_key_values
+        token = out.logits[:, -1, :].argmax(-1, keepdim=True)
+
+        def one_step(token, past):
+            out = model(input_ids=token, past_key_values=past, use_cache=True)
+            nxt = out.logits[:, -1, :].argmax(-1, keepdim=True)
+            return torch.tensor(nxt.tolist(), device="cuda:0"), out.past_key_values
+
+        for _ in range(args.warmup):
+            token, past = one_step(token, past)
+        torch.cuda.synchronize()
+        clocks.start()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(args.steps):
+            token, past = one_step(token, past)
+        stop.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    ms = start.elapsed_time(stop) / args.steps
+    line = {
+        "metric": "decode tok/s at batch 8, 2,048-token context (Qwen3-8B bf16)", "impl": "reference",
+        "value": round(batch * 1e3 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_model": QWEN3_8B["num_hidden_layers"],
+                   "global_batch": batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+                   "path": "Qwen3ForCausalLM.forward with past_key_values"},
+        "e2e": {"value": round(batch * 1e3 / wall_ms, 1), "unit": "tokens/s", "h2d_bytes_per_step": batch * 8,
+                "d2h_bytes_per_step": batch * 8},
+        "gpu_launches": 0, "clocks": clocks.stop(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    parser.add_argument("--batch", type=int, default=8)
+    args = parser.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print("bench.py measures a single-GPU engine: run it with --gpus 1 (no multi-GPU path is built)")
+        return 2
+    args.warmup = max(3, args.warmup)
+    return run_reference(args) if args.impl == "reference" else run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

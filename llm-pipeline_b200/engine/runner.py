@@ -58,6 +58,7 @@ class ModelRunner:
         self._views = _CacheViews(cache)
         self.steps = 0
         self.tokens_run = 0
+        self.last_h2d_bytes = 0
 
     # -- building the step's index arrays ------------------------------------------------------
     def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
@@ -139,6 +140,7 @@ class ModelRunner:
             flat += mapping + tables
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
         cursor = 0
 
         def take(count: int) -> torch.Tensor:

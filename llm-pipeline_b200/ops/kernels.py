@@ -47,6 +47,7 @@ _SIGNATURES = {
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
 }
 _bound = {}
+launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
 
 
 def _fn(name: str):
@@ -61,6 +62,8 @@ def _fn(name: str):
 
 
 def _call(name: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     rc = _fn(name)(*args)
     if rc != 0:
         lib = library()

@@ -1,0 +1,175 @@
+"""Generation through the entry points, and trace replay as a program."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = [pytest.param(torch.float32, id="f32"), pytest.param(torch.bfloat16, id="bf16")]
+
+
+def engine_for(folder, dtype, **kw):
+    from llm_pipeline_b200.inference import Qwen3InferenceConfig, Qwen3InferenceEngine
+    defaults = dict(model_path=folder, dtype=dtype, block_size=8, num_blocks=128, max_sequence_length=512,
+                    max_batch_size=8, max_num_batched_tokens=64)
+    defaults.update(kw)
+    return Qwen3InferenceEngine(Qwen3InferenceConfig(**defaults))
+
+
+def margins_ok(config, weights, prompt, generated, margin):
+    """True when every greedy choice of the plain implementation wins by more than ``margin``."""
+    ids = list(prompt)
+    for token in generated:
+        logits = plain.forward_logits(config, weights, ids)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) <= margin:
+            return False
+        ids.append(token)
+    return True
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tiny,seed", [(plain.TINY_A, 0), (plain.TINY_B, 1)], ids=["a", "b"])
+def test_greedy_generation_matches_plain(tmp_path, tiny, seed, dtype):
+    folder, weights = H.make_case(tmp_path, tiny, seed, dtype, std=0.08)
+    engine = engine_for(folder, dtype)
+    prompts = [H.random_tokens(tiny["vocab_size"], n, 300 + n) for n in (1, 9, 24, 40)]   # 1: the first token of a sequence
+    got = engine.generate(prompts, max_tokens=8, temperature=0.0)
+    checked = 0
+    for prompt, tokens in zip(prompts, got):
+        want = plain.greedy_generate(tiny, weights, prompt, 8)
+        if dtype == torch.float32 or margins_ok(tiny, weights, prompt, want, 0.05):
+            assert tokens == want
+            checked += 1
+    assert checked >= (4 if dtype == torch.float32 else 2)
+    single = engine.generate(prompts[2], max_tokens=8, temperature=0.0)
+    assert single == got[2]
+    assert engine.engine.cache.num_live == 0
+
+
+def test_long_decoding_stays_exact(tmp_path):
+    folder, weights = H.make_case(tmp_path, plain.TINY_A, 0, torch.float32, std=0.08)
+    engine = engine_for(folder, torch.float32, block_size=16)
+    prompt = H.random_tokens(256, 5, 42)
+    tokens = engine.generate(prompt, max_tokens=150, temperature=0.0)
+    assert len(tokens) == 150
+    logits = plain.forward_logits(plain.TINY_A, weights, prompt + tokens[:-1])
+    assert logits[4:].argmax(dim=-1).tolist() == tokens      # every decoded token is the plain argmax at its place
+
+
+def test_sampling_is_seeded_and_independent_of_the_batch(tmp_path):
+    from llm_pipeline_b200.sampling import uniform_of
+    tiny = plain.TINY_B
+    folder, weights = H.make_case(tmp_path, tiny, 1, torch.float32, std=0.08)
+    engine = engine_for(folder, torch.float32)
+    prompts = [H.random_tokens(tiny["vocab_size"], n, 500 + n) for n in (1, 9, 24, 40)]
+    a = engine.generate(prompts, max_tokens=6, temperature=0.7, top_k=0, top_p=1.0, seed=123)
+    b = engine.generate(prompts, max_tokens=6, temperature=0.7, top_k=0, top_p=1.0, seed=123)
+    assert a == b
+    alone = engine.generate([prompts[2]], max_tokens=6, temperature=0.7, top_k=0, top_p=1.0, seed=125)
+    assert alone[0] == a[2]                                  # prompt i draws with seed + i, whoever else is in the batch
+    other = engine.generate(prompts, max_tokens=6, temperature=0.7, top_k=0, top_p=1.0, seed=7)
+    assert other != a
+    # every draw is the inverse-CDF pick of the plain sampler for the same uniform number
+    for i, (prompt, tokens) in enumerate(zip(prompts, a)):
+        ids = list(prompt)
+        for step, token in enumerate(tokens):
+            probs = plain.filtered_probs(plain.forward_logits(tiny, weights, ids)[-1], 0.7)
+            cdf = torch.cumsum(probs.double(), 0)
+            u = uniform_of(123 + i, step)
+            assert float(cdf[token] - probs[token].double()) - 1e-4 <= u <= float(cdf[token]) + 1e-4
+            ids.append(token)
+    filtered = engine.generate(prompts, max_tokens=6, temperature=0.7, top_k=5, top_p=0.9, seed=3)
+    for prompt, tokens in zip(prompts, filtered):
+        ids = list(prompt)
+        for token in tokens:
+            probs = plain.filtered_probs(plain.forward_logits(tiny, weights, ids)[-1], 0.7, top_k=5, top_p=0.9)
+            assert probs[token] > 0
+            ids.append(token)
+
+
+def test_preemption_recomputes_to_the_same_tokens(tmp_path):
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    prompts = [H.random_tokens(tiny["vocab_size"], n, 700 + n) for n in (20, 18, 22)]
+    roomy = engine_for(folder, torch.float32, block_size=4, num_blocks=256)
+    want = roomy.generate(prompts, max_tokens=24, temperature=0.0)
+    tight = engine_for(folder, torch.float32, block_size=4, num_blocks=26)    # 104 token slots for 3 x (up to 46)
+    results = tight.generate_ids(prompts, max_tokens=24, temperature=0.0)
+    assert [r.token_ids for r in results] == want
+    assert sum(r.preemptions for r in results) >= 1 and tight.engine.scheduler.num_preemptions >= 1
+    assert tight.engine.cache.num_live == 0 and tight.engine.cache.groups[0].pool.num_free == 26
+    assert tight.engine.cache.pages_reused > 0
+
+
+def test_eos_and_stats(tmp_path):
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    prompt = H.random_tokens(256, 7, 9)
+    free_run = plain.greedy_generate(tiny, weights, prompt, 12)
+    engine = engine_for(folder, torch.float32, eos_token_id=free_run[4])
+    out = engine.generate_ids([prompt], max_tokens=12, temperature=0.0)[0]
+    stop_at = free_run.index(free_run[4])
+    assert out.token_ids == free_run[:stop_at + 1] and out.finish_reason == "stop"
+    stats = engine.get_stats()
+    assert stats["finished"] == 1 and stats["tokens_prefilled"] == 7 and stats["live_requests"] == 0
+
+
+def write_trace(path, steps):
+    with open(path, "w") as f:
+        for i, (entries, end) in enumerate(steps):
+            f.write(json.dumps({"step": i, "entries": [{"id": rid, "tokens": toks, "want": want} for rid, toks, want in entries],
+                                "end": end}) + "\n")
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype_name):
+    dtype = torch.float32 if dtype_name == "float32" else torch.bfloat16
+    tiny = plain.TINY_B
+    folder, weights = H.make_case(tmp_path / "model", tiny, 1, dtype)
+    requests = {f"q{i}": H.random_tokens(tiny["vocab_size"], n, 900 + i) for i, n in enumerate((33, 70, 12, 57, 41, 25))}
+    steps = H.cut_mixed(requests, (7, 2, 16, 3, 5), max_live=4)
+    steps.insert(3, ([], []))                                         # a step that brings nothing
+    write_trace(tmp_path / "trace.jsonl", steps)
+    out_dir = tmp_path / "out"
+    with open(tmp_path / "trace.jsonl") as stdin:
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype_name,
+                               "--out", str(out_dir), "--max-tokens", str(4 * 128)], stdin=stdin, capture_output=True,
+                              text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:len(steps)] == [f"done {i}" for i in range(len(steps))]
+    want = H.expected_logits(tiny, weights, requests)
+    cursor = {rid: 0 for rid in requests}
+    V = tiny["vocab_size"]
+    for i, (entries, _end) in enumerate(steps):
+        wanted = sum(len(w) for _, _, w in entries)
+        path = out_dir / f"{i}.f32"
+        if wanted == 0:
+            assert not path.exists()
+            continue
+        data = torch.frombuffer(bytearray(path.read_bytes()), dtype=torch.float32).view(wanted, V)
+        row = 0
+        for rid, toks, w in entries:
+            ref = want[rid][cursor[rid]:cursor[rid] + len(toks)][w]
+            assert float((data[row:row + len(w)] - ref).abs().max()) <= H.TOL[dtype], (i, rid)
+            row += len(w)
+            cursor[rid] += len(toks)
+
+
+def test_cli_infer_with_token_ids(tmp_path):
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    prompt = [5, 17, 3, 200, 9]
+    proc = subprocess.run([sys.executable, "-m", "llm_pipeline_b200.cli", "infer", "--model", folder, "--prompt-ids",
+                           " ".join(map(str, prompt)), "--dtype", "fp32", "--max-new-tokens", "6", "--temperature", "0"],
+                          capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.split()] == plain.greedy_generate(tiny, weights, prompt, 6)

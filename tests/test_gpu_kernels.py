@@ -1,0 +1,286 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same operation, at sizes
+other than the engine's tiny models: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head counts."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [pytest.param(torch.float32, id="f32"), pytest.param(torch.bfloat16, id="bf16")]
+
+
+def K():
+    from llm_pipeline_b200.ops import kernels
+    return kernels
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    table = rnd(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 200, dtype=torch.float32, device=DEV)
+    K().embedding(ids, table, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+def test_rope_tables_match_the_reference_formula():
+    positions = torch.tensor([0, 1, 17, 4095, 100000], dtype=torch.int32, device=DEV)
+    for head_dim, theta in ((48, 10000.0), (128, 1000000.0)):
+        exponent = torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim
+        inv_freq = (1.0 / (theta ** exponent)).to(DEV)
+        cos = torch.empty(5, head_dim // 2, device=DEV)
+        sin = torch.empty_like(cos)
+        K().rope_tables(positions, inv_freq, 1.0, cos, sin)
+        want_cos, want_sin = plain.rope_cos_sin(positions.cpu(), head_dim, theta)
+        assert torch.allclose(cos.cpu(), want_cos[:, :head_dim // 2], atol=2e-6)
+        assert torch.allclose(sin.cpu(), want_sin[:, :head_dim // 2], atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [1000, 4096 + 16])
+def test_add_rmsnorm(dtype, H):
+    residual = rnd(7, H, seed=1)
+    delta = rnd(7, H, dtype=dtype, seed=2)
+    bias = rnd(H, seed=3, scale=0.1)
+    weight = (1 + 0.1 * rnd(H, seed=4)).to(dtype)
+    x = residual + delta.float() + bias
+    want = plain.rms_norm(x, weight.float(), 1e-5)
+    res = residual.clone()
+    out = torch.empty(7, H, dtype=dtype, device=DEV)
+    K().add_rmsnorm(res, delta, weight, 1e-5, out, delta_bias=bias)
+    assert torch.allclose(res, x, atol=1e-6)
+    assert torch.allclose(out.float(), want, atol=tol(dtype, 2e-5, 4e-2), rtol=tol(dtype, 1e-5, 1e-2))
+    # selected rows: the residual is left alone
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    res2 = residual.clone()
+    out2 = torch.empty(3, H, dtype=dtype, device=DEV)
+    K().add_rmsnorm(res2, delta, weight, 1e-5, out2, delta_bias=bias, rows=rows)
+    assert torch.equal(res2, residual)
+    assert torch.equal(out2, out[rows.long()])
+    # no addend: plain norm of the residual
+    out3 = torch.empty(7, H, dtype=dtype, device=DEV)
+    K().add_rmsnorm(res2, None, weight, 1e-5, out3)
+    assert torch.allclose(out3.float(), plain.rms_norm(residual, weight.float(), 1e-5), atol=tol(dtype, 2e-5, 4e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot", [(5, 5, 48, 48), (8, 2, 128, 128), (3, 1, 80, 32)])
+def test_qkv_post_norm_rotary_and_page_write(dtype, nq, nkv, d, rot):
+    N, page_size, pages_n = 11, 4, 9
+    qkv = rnd(N, (nq + 2 * nkv) * d, dtype=dtype, seed=5)
+    bias = rnd((nq + 2 * nkv) * d, seed=6, scale=0.1)
+    qw, kw = (1 + 0.1 * rnd(d, seed=7)), (1 + 0.1 * rnd(d, seed=8))
+    positions = torch.tensor([3, 4, 5, 6, 7, 8, 0, 1, 2, 90, 91], dtype=torch.int32, device=DEV)
+    exponent = torch.arange(0, rot, 2, dtype=torch.int64).float() / rot
+    inv_freq = (1.0 / (10000.0 ** exponent)).to(DEV)
+    cos = torch.empty(N, rot // 2, device=DEV)
+    sin = torch.empty_like(cos)
+    K().rope_tables(positions, inv_freq, 1.0, cos, sin)
+    slots = torch.tensor([20, 21, 22, 23, 4, 5, 35, 34, 33, -1, 0], dtype=torch.int32, device=DEV)
+    pages = torch.zeros(pages_n, 2, nkv, page_size, d, dtype=dtype, device=DEV)
+    work = qkv.clone()
+    K().qkv_post(work, nq, nkv, d, bias=bias, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin, rotary_dim=rot,
+                 slots=slots, pages=pages, page_size=page_size)
+    x = qkv.float() + bias
+    q, k, v = x[:, :nq * d].view(N, nq, d), x[:, nq * d:(nq + nkv) * d].view(N, nkv, d), x[:, (nq + nkv) * d:].view(N, nkv, d)
+    q, k = plain.rms_norm(q, qw, 1e-6), plain.rms_norm(k, kw, 1e-6)
+
+    def rotate(t):
+        c = torch.cat((cos, cos), -1)[:, None, :]
+        s = torch.cat((sin, sin), -1)[:, None, :]
+        head = t[..., :rot]
+        return torch.cat((head * c + plain.rotate_half(head) * s, t[..., rot:]), dim=-1)
+
+    q, k = rotate(q), rotate(k)
+    t = tol(dtype, 1e-5, 5e-2)
+    assert torch.allclose(work[:, :nq * d].float().view(N, nq, d), q, atol=t)
+    for n in range(N):
+        s = int(slots[n])
+        if s < 0:
+            continue
+        assert torch.allclose(pages[s // page_size, 0, :, s % page_size].float(), k[n], atol=t)
+        assert torch.allclose(pages[s // page_size, 1, :, s % page_size].float(), v[n], atol=t)
+    untouched = torch.ones(pages_n * page_size, dtype=torch.bool)
+    untouched[[int(s) for s in slots if s >= 0]] = False
+    flat = pages.float().permute(0, 3, 1, 2, 4).reshape(pages_n * page_size, -1)
+    assert float(flat[untouched].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    gu = rnd(9, 2 * 300, dtype=dtype, seed=9, scale=2.0)
+    out = torch.empty(9, 300, dtype=dtype, device=DEV)
+    K().swiglu(gu, out)
+    g, u = gu.float()[:, :300], gu.float()[:, 300:]
+    assert torch.allclose(out.float(), torch.nn.functional.silu(g) * u, atol=tol(dtype, 1e-6, 3e-2), rtol=tol(dtype, 1e-6, 1e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 77), (70, 130, 77), (64, 64, 16), (3, 1000, 515)])
+def test_gemm_simt(dtype, M, N, Kd):
+    a, w = rnd(M, Kd, dtype=dtype, seed=10), rnd(N, Kd, dtype=dtype, seed=11)
+    bias = rnd(N, seed=12)
+    want = a.double() @ w.double().t() + bias.double()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV) if dtype == torch.bfloat16 else torch.empty(M, N, device=DEV)
+    K().gemm_simt(a, w, out, bias)
+    assert torch.allclose(out.double(), want, atol=2e-4, rtol=1e-5)
+    # a row's result does not depend on the other rows
+    single = torch.empty(1, N, dtype=out.dtype, device=DEV)
+    K().gemm_simt(a[M - 1:M], w, single, bias)
+    assert torch.equal(single[0], out[M - 1])
+
+
+def attention_reference(q, k, v, window, scale):
+    """q [T, nq, d] at positions P..P+T-1 over keys k, v [S, nkv, d]; S = P + T."""
+    T, nq, d = q.shape
+    S, nkv, _ = k.shape
+    G = nq // nkv
+    kk, vv = k.repeat_interleave(G, dim=1), v.repeat_interleave(G, dim=1)
+    scores = torch.einsum("tnd,snd->nts", q.double(), kk.double()) * scale
+    qpos = torch.arange(S - T, S)[:, None]
+    kpos = torch.arange(S)[None, :]
+    mask = kpos > qpos
+    if window:
+        mask = mask | (kpos < qpos - window + 1)
+    scores = scores.masked_fill(mask[None].to(scores.device), float("-inf"))
+    return torch.einsum("nts,snd->tnd", torch.softmax(scores, dim=-1), vv.double()).float()
+
+
+def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None):
+    """requests: list of (context_before, new_tokens). Pages are handed out in a scrambled order."""
+    k_ = K()
+    gen = torch.Generator().manual_seed(seed)
+    R = len(requests)
+    total_pages = sum(-(-(p + t) // page_size) for p, t in requests) + 3
+    order = torch.randperm(total_pages, generator=gen).tolist()
+    pages = rnd(total_pages, 2, nkv, page_size, d, dtype=dtype, seed=seed + 1)      # stale data everywhere
+    width = max(-(-(p + t) // page_size) for p, t in requests)
+    tables = torch.full((R, width), -1, dtype=torch.int32)
+    N = sum(t for _, t in requests)
+    q = rnd(N, nq * d, dtype=dtype, seed=seed + 2)
+    ks, vs, q_start, ctx = [], [], [0], []
+    for r, (P, T) in enumerate(requests):
+        S = P + T
+        k, v = rnd(S, nkv, d, dtype=dtype, seed=seed + 10 + r), rnd(S, nkv, d, dtype=dtype, seed=seed + 50 + r)
+        if boost is not None and r == boost[0]:
+            # make one far key decisive for the last query of this request
+            _, key_pos, head = boost
+            kvh = head // (nq // nkv)
+            qrow = q_start[-1] + T - 1
+            direction = torch.nn.functional.normalize(rnd(d, seed=99), dim=0)
+            q[qrow, head * d:(head + 1) * d] = (direction * 6 * math.sqrt(d) ** 0.5).to(dtype)
+            k[key_pos, kvh] = (direction * 6 * math.sqrt(d) ** 0.5).to(dtype)
+        for i in range(-(-S // page_size)):
+            page = order.pop()
+            tables[r, i] = page
+            n = min(page_size, S - i * page_size)
+            pages[page, 0, :, :n] = k[i * page_size:i * page_size + n].transpose(0, 1)
+            pages[page, 1, :, :n] = v[i * page_size:i * page_size + n].transpose(0, 1)
+        ks.append(k)
+        vs.append(v)
+        q_start.append(q_start[-1] + T)
+        ctx.append(S)
+    tpt = k_.tokens_per_attention_tile(nq, nkv)
+    tile_req, tile_tok0 = [], []
+    for r, (_, T) in enumerate(requests):
+        for t0 in range(0, T, tpt):
+            tile_req.append(r)
+            tile_tok0.append(t0)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)   # noqa: E731
+    out = torch.zeros(N, nq * d, dtype=dtype, device=DEV)
+    scale = d ** -0.5
+    k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
+                       dev(tile_tok0), nq, nkv, d, page_size, window, scale)
+    want = torch.cat([attention_reference(q[q_start[r]:q_start[r + 1]].float().view(-1, nq, d).cpu(), ks[r].float().cpu(),
+                                          vs[r].float().cpu(), window, scale) for r in range(R)])
+    return out.float().cpu().view(N, nq, d), want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (9, 3, 48, 4), (32, 8, 128, 16), (5, 5, 80, 16),
+                                           (40, 2, 64, 32)])
+def test_paged_attention_mixed_batch(dtype, nq, nkv, d, page):
+    got, want = run_paged(dtype, nq, nkv, d, page, [(0, 37), (130, 1), (63, 2), (64, 33), (5, 1), (0, 1)], seed=3)
+    assert torch.allclose(got, want, atol=tol(dtype, 2e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_one_far_key_among_hundreds(dtype):
+    # decode over 700 keys: key 3 (first page) decides head 5; then key 511 (a page's last slot)
+    for key_pos in (3, 511, 512, 699):
+        got, want = run_paged(dtype, 8, 2, 64, 16, [(699, 1), (40, 8)], seed=4, boost=(0, key_pos, 5))
+        assert torch.allclose(got, want, atol=tol(dtype, 3e-5, 3e-2)), key_pos
+        assert float(want[0, 5].abs().max()) > 0.5      # the boosted key dominates: its value shows in the output
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
+def test_paged_attention_window_edge(dtype, window):
+    # the key just inside and just outside the window of the last query are the decisive ones
+    for offset in (0, 1):
+        P, T = 150, 3
+        key_pos = P + T - 1 - window + 1 - offset       # offset 0: the oldest key inside; 1: the first outside
+        if key_pos < 0:
+            continue
+        got, want = run_paged(dtype, 4, 2, 32, 8, [(P, T), (20, 5)], window=window, seed=5, boost=(0, key_pos, 1))
+        assert torch.allclose(got, want, atol=tol(dtype, 3e-5, 3e-2)), (window, offset)
+
+
+def test_argmax_and_sampling_rows():
+    k_ = K()
+    from llm_pipeline_b200.sampling import Sampler, SamplingConfig, uniform_of
+    V = 1531
+    logits = rnd(6, V, seed=20, scale=3.0)
+    logits[2, 77] = logits[2].max() + 1
+    logits[2, 900] = logits[2, 77]                   # a tie: the lower index wins
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    k_.argmax(logits, out)
+    assert out.tolist() == logits.cpu().argmax(dim=-1).tolist() and out[2] == 77
+    sampler = Sampler()
+    configs = [SamplingConfig(temperature=0.0), SamplingConfig(temperature=0.7, top_k=0, top_p=1.0, seed=1),
+               SamplingConfig(temperature=1.3, top_k=40, top_p=1.0, seed=2),
+               SamplingConfig(temperature=0.9, top_k=50, top_p=0.9, seed=3),
+               SamplingConfig(temperature=1.0, top_k=0, top_p=0.5, min_p=0.05, seed=4),
+               SamplingConfig(temperature=0.8, top_k=200, top_p=0.95, typical_p=0.9, seed=5)]
+    for step in range(12):
+        got = sampler.sample_rows(logits, configs, [step] * 6).tolist()
+        assert got[0] == int(logits[0].argmax())
+        for r in range(1, 6):
+            c = configs[r]
+            probs = plain.filtered_probs(logits[r].cpu(), c.temperature, c.top_k, c.top_p, c.min_p, c.typical_p)
+            u = uniform_of(c.seed, step)
+            assert probs[got[r]] > 0, (r, step)
+            cdf = torch.cumsum(probs.double(), 0)
+            lo = float(cdf[got[r]] - probs[got[r]].double())
+            assert lo - 1e-4 <= u <= float(cdf[got[r]]) + 1e-4, (r, step, u, lo, float(cdf[got[r]]))
+    # a row's draw does not depend on the rows around it
+    alone = sampler.sample_rows(logits[3:4], [configs[3]], [5]).tolist()[0]
+    assert alone == sampler.sample_rows(logits, configs, [5] * 6).tolist()[3]
+    # repetition penalty moves mass away from listed tokens
+    cfg = SamplingConfig(temperature=0.0, repetition_penalty=50.0)
+    top = int(logits[1].argmax())
+    assert sampler.sample_rows(logits[1:2], [cfg], [0], [[top]]).tolist()[0] != top
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    k_ = K()
+    with pytest.raises(k_.KernelError, match="CUDA"):
+        k_.embedding(torch.zeros(1, dtype=torch.int32), torch.zeros(2, 2), torch.zeros(1, 2))
+    with pytest.raises(k_.KernelError, match="multiple of 16"):
+        run_paged(torch.float32, 2, 1, 24, 8, [(0, 2)])
+    with pytest.raises(k_.KernelError, match="float32 and bfloat16"):
+        k_.swiglu(torch.zeros(2, 4, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV))

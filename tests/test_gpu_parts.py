@@ -1,0 +1,304 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with state
+of its own that is registered, built and stepped from this file without touching the framework."""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [pytest.param(torch.float32, id="f32"), pytest.param(torch.bfloat16, id="bf16")]
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 3e-2
+
+
+def getter(weights, dtype):
+    from llm_pipeline_b200.weights import stored_dtype_policy
+
+    def get(name, role):
+        t = weights[name]
+        return t.to(device=DEV, dtype=stored_dtype_policy(role, t.dtype, dtype))
+    return get
+
+
+def context_for(dtype, cache_specs, chunks, page_size=8, num_pages=32, vocab=1000):
+    """A runner over a model stand-in, so that parts can be stepped with real step contexts."""
+    from llm_pipeline_b200.cache import CacheManager
+    from llm_pipeline_b200.engine import ModelRunner
+
+    cache = CacheManager(cache_specs, page_size=page_size, num_pages=num_pages, max_requests=4,
+                         max_request_tokens=512, device=DEV, dtype=dtype)
+    model = SimpleNamespace(device=DEV, dtype=dtype, spec=SimpleNamespace(vocab_size=vocab))
+    return ModelRunner(model, cache), cache
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rms_norm_part(dtype):
+    from llm_pipeline_b200.parts import ResidualStream, lookup
+    w = {"n.weight": 1 + 0.1 * torch.randn(200)}
+    norm = lookup("norm", "rms_norm")("n", size=200, eps=1e-5)
+    assert set(norm.param_specs()) == {"n.weight"}
+    norm.load(getter(w, dtype))
+    x = torch.randn(5, 200, device=DEV)
+    delta = torch.randn(5, 200, device=DEV).to(dtype)
+    stream = ResidualStream(x.clone())
+    stream.add(delta)
+    out = norm.add_norm(stream, SimpleNamespace(dtype=dtype))
+    want = plain.rms_norm(x + delta.float(), w["n.weight"].to(DEV).to(dtype).float(), 1e-5)
+    assert stream.pending is None and torch.allclose(stream.residual, x + delta.float(), atol=1e-6)
+    assert torch.allclose(out.float(), want, atol=tol(dtype), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+def test_rotary_part_tables():
+    from llm_pipeline_b200.parts import lookup
+    rope = lookup("position", "rotary")("", rotary_dim=48, theta=50000.0)
+    ctx = SimpleNamespace(device=DEV, num_tokens=4, positions=torch.tensor([0, 5, 6, 2000], dtype=torch.int32, device=DEV))
+    cos, sin = rope.tables(ctx)
+    want_cos, want_sin = plain.rope_cos_sin(ctx.positions.cpu(), 48, 50000.0)
+    assert torch.allclose(cos.cpu(), want_cos[:, :24], atol=2e-6) and torch.allclose(sin.cpu(), want_sin[:, :24], atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_part(dtype):
+    from llm_pipeline_b200.parts import lookup
+    cfg = plain.TINY_C
+    w = {k.replace("model.layers.0.mlp", "ff"): v for k, v in plain.random_weights(cfg, 3, std=0.1).items() if ".layers.0.mlp." in k}
+    if dtype == torch.bfloat16:
+        w = {k: v.to(dtype).float() for k, v in w.items()}
+    ff = lookup("feed_forward", "swiglu")("ff", hidden_size=cfg["hidden_size"], intermediate_size=cfg["intermediate_size"])
+    ff.load(getter(w, dtype))
+    x = torch.randn(6, cfg["hidden_size"], device=DEV).to(dtype)
+    out, bias = ff.forward(x, SimpleNamespace(dtype=dtype))
+    want = plain.mlp(x.float().cpu(), w, "ff")
+    assert bias is None and torch.allclose(out.float().cpu(), want, atol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    from llm_pipeline_b200.parts import lookup
+    w = {"e.weight": torch.randn(300, 40).to(dtype).float(), "h.weight": torch.randn(300, 40).to(dtype).float()}
+    emb = lookup("embedding", "token_embedding")("e", vocab_size=300, hidden_size=40)
+    emb.load(getter(w, dtype))
+    ids = torch.tensor([1, 299, 17], dtype=torch.int32, device=DEV)
+    out = emb.forward(SimpleNamespace(device=DEV, num_tokens=3, token_ids=ids))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), w["e.weight"][ids.cpu().long()])
+    for tied, name in ((None, "h.weight"), ("e", "e.weight")):
+        head = lookup("head", "linear_head")("h", vocab_size=300, hidden_size=40, tied_to=tied)
+        head.load(getter(w, dtype))
+        x = torch.randn(3, 40, device=DEV).to(dtype)
+        logits = head.forward(x, None)
+        assert logits.dtype == torch.float32
+        assert torch.allclose(logits.cpu(), x.float().cpu() @ w[name].t(), atol=1e-4 if dtype == torch.float32 else 5e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tiny", [plain.TINY_B, plain.TINY_C], ids=["b", "c"])
+def test_attention_part_alone_in_two_portions(dtype, tiny):
+    """The mixer on a sequence cut in two steps equals the plain attention on the whole sequence."""
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.parts import LayerCache, lookup
+    cfg = resolve_config(tiny)
+    spec = cfg.model_spec()
+    part = spec.layers[1].mixer
+    weights = {k: v for k, v in plain.random_weights(tiny, 4, std=0.08).items()}
+    if dtype == torch.bfloat16:
+        weights = {k: v.to(dtype).float() for k, v in weights.items()}
+    mixer = lookup("mixer", part.kind)(part.prefix, **part.args)
+    mixer.load(getter(weights, dtype))
+    rope = lookup("position", "rotary")("", **spec.positions["rope"].args)
+    runner, cache = context_for(dtype, [(mixer.cache_spec(), None)], None)
+    T, cutat = 29, 18
+    x = torch.randn(T, tiny["hidden_size"])
+    if dtype == torch.bfloat16:
+        x = x.to(dtype).float()
+    cos, sin = plain.rope_cos_sin(torch.arange(T), tiny["head_dim"], tiny["rope_theta"])
+    want = plain.attention(x, weights, part.prefix, tiny, cos, sin)
+    got = []
+    for lo, hi in ((0, cutat), (cutat, T)):
+        ctx = runner._prepare([StepEntry("r", [1] * (hi - lo), [])])
+        ctx.position_tables = {"rope": rope.tables(ctx)}
+        out, bias = mixer.forward(x[lo:hi].to(DEV).to(dtype), ctx, LayerCache(cache.pages_tensor(0), 0, None, True))
+        out = out.float() + (bias.float() if bias is not None else 0)
+        got.append(out.cpu())
+        cache.commit("r", hi)
+    assert torch.allclose(torch.cat(got), want, atol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(dtype):
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.parts import LayerCache, ResidualStream, lookup
+    tiny = plain.TINY_A
+    spec = resolve_config(tiny).model_spec()
+    layer = spec.layers[1]
+    weights = plain.random_weights(tiny, 5, std=0.08)
+    if dtype == torch.bfloat16:
+        weights = {k: v.to(dtype).float() for k, v in weights.items()}
+    make = lambda family, p: lookup(family, p.kind)(p.prefix, **p.args)   # noqa: E731
+    block = lookup("block", layer.block)(make("mixer", layer.mixer), make("feed_forward", layer.feed_forward),
+                                         make("norm", layer.mixer_norm), make("norm", layer.feed_forward_norm))
+    for part in block.parts():
+        part.load(getter(weights, dtype))
+    rope = make("position", spec.positions["rope"])
+    runner, cache = context_for(dtype, [(block.mixer.cache_spec(), None)], None)
+    T = 21
+    x = torch.randn(T, tiny["hidden_size"])
+    cos, sin = plain.rope_cos_sin(torch.arange(T), tiny["head_dim"], tiny["rope_theta"])
+    want = plain.decoder_layer(x, weights, 1, tiny, cos, sin)
+    ctx = runner._prepare([StepEntry("r", [1] * T, [])])
+    ctx.position_tables = {"rope": rope.tables(ctx)}
+    stream = ResidualStream(x.to(DEV))
+    block.forward(stream, ctx, LayerCache(cache.pages_tensor(0), 0, None, True))
+    got = stream.residual + stream.pending.float()
+    assert torch.allclose(got.cpu(), want, atol=tol(dtype))
+
+
+# ------------------------------------------------------------------------------------------
+# A toy mixer with state of its own: a decayed running sum of its inputs per request.
+#   s_t = decay * s_{t-1} + x_t ;  out_t = s_t * gain
+# The state is one vector per request, kept in the request's slot between steps.
+# ------------------------------------------------------------------------------------------
+
+def _register_toy():
+    from llm_pipeline_b200.cache import StateSpec
+    from llm_pipeline_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
+                                          register_architecture)
+    from llm_pipeline_b200.parts import Mixer, register_mixer
+    from llm_pipeline_b200.weights import ParamSpec
+
+    @register_mixer("toy_decayed_sum")
+    class DecayedSum(Mixer):
+        def __init__(self, prefix, hidden_size, decay):
+            self.prefix, self.hidden_size, self.decay = prefix, hidden_size, decay
+            self.gain = None
+
+        def state_spec(self):
+            return StateSpec((self.hidden_size,), torch.float32)
+
+        def param_specs(self):
+            return {f"{self.prefix}.gain": ParamSpec((self.hidden_size,), role="vector", init="norm")}
+
+        def load(self, get):
+            self.gain = get(f"{self.prefix}.gain", "vector").float()
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            row = 0
+            for r, n in enumerate(ctx.q_lens):
+                slot = int(ctx.slots[r])
+                s = cache.state[slot]
+                for i in range(n):
+                    s = self.decay * s + x[row + i].float()
+                    out[row + i] = (s * self.gain).to(x.dtype)
+                cache.state[slot] = s
+                row += n
+            return out, None
+
+    class ToyConfig(ModelConfig):
+        architecture = "ToyHybridForCausalLM"
+
+        def __init__(self, data):
+            self.data = data
+
+        @classmethod
+        def from_json(cls, data):
+            return cls(dict(data))
+
+        def to_json(self):
+            return dict(self.data)
+
+        def model_spec(self):
+            d = self.data
+            H, V = d["hidden_size"], d["vocab_size"]
+            norm = {"size": H, "eps": d["eps"]}
+            ff = lambda i: PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["intermediate_size"]}, f"layers.{i}.ff")  # noqa: E731
+            attn = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"],
+                                          "head_dim": d["head_dim"], "scale": d["head_dim"] ** -0.5, "qk_norm": False,
+                                          "window": d["window"], "position": "rope"}, "layers.1.attn")
+            layers = (
+                LayerSpec("pre_norm_residual", PartSpec("toy_decayed_sum", {"hidden_size": H, "decay": d["decay"]}, "layers.0.mix"),
+                          ff(0), PartSpec("rms_norm", norm, "layers.0.n1"), PartSpec("rms_norm", norm, "layers.0.n2")),
+                LayerSpec("pre_norm_residual", attn, ff(1), PartSpec("rms_norm", norm, "layers.1.n1"),
+                          PartSpec("rms_norm", norm, "layers.1.n2")),
+            )
+            # layer 0 runs twice (two caches, so two states), the windowed attention layer once
+            return ModelSpec("ToyHybridForCausalLM", V, H, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "embed"),
+                             {"rope": PartSpec("rotary", {"rotary_dim": d["head_dim"], "theta": 10000.0})}, layers,
+                             (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2)),
+                             PartSpec("rms_norm", norm, "final"), PartSpec("linear_head", {"vocab_size": V, "hidden_size": H,
+                                                                                           "tied_to": "embed"}, "head"), 512)
+
+    register_architecture("ToyHybridForCausalLM", ToyConfig)
+
+
+TOY = {"architectures": ["ToyHybridForCausalLM"], "hidden_size": 48, "vocab_size": 97, "intermediate_size": 80, "heads": 3,
+       "kv_heads": 3, "head_dim": 16, "eps": 1e-5, "decay": 0.9, "window": 11}
+
+
+def toy_reference(weights, ids):
+    """The toy model on one whole sequence in plain PyTorch."""
+    d = TOY
+    H, T = d["hidden_size"], len(ids)
+    x = weights["embed.weight"][torch.tensor(ids)]
+
+    def ff(h, i):
+        g, u = h @ weights[f"layers.{i}.ff.gate_proj.weight"].t(), h @ weights[f"layers.{i}.ff.up_proj.weight"].t()
+        return (torch.nn.functional.silu(g) * u) @ weights[f"layers.{i}.ff.down_proj.weight"].t()
+
+    def toy_layer(x):
+        h = plain.rms_norm(x, weights["layers.0.n1.weight"], d["eps"])
+        s, outs = torch.zeros(H), []
+        for t in range(T):
+            s = d["decay"] * s + h[t]
+            outs.append(s * weights["layers.0.mix.gain"])
+        x = x + torch.stack(outs)
+        return x + ff(plain.rms_norm(x, weights["layers.0.n2.weight"], d["eps"]), 0)
+
+    def attn_layer(x):
+        h = plain.rms_norm(x, weights["layers.1.n1.weight"], d["eps"])
+        nh, hd = d["heads"], d["head_dim"]
+        cos, sin = plain.rope_cos_sin(torch.arange(T), hd, 10000.0)
+        q = (h @ weights["layers.1.attn.q_proj.weight"].t()).view(T, nh, hd).transpose(0, 1)
+        k = (h @ weights["layers.1.attn.k_proj.weight"].t()).view(T, nh, hd).transpose(0, 1)
+        v = (h @ weights["layers.1.attn.v_proj.weight"].t()).view(T, nh, hd).transpose(0, 1)
+        q, k = plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin)
+        scores = (q @ k.transpose(1, 2)) * hd ** -0.5
+        pos = torch.arange(T)
+        masked = (pos[None, :] > pos[:, None]) | (pos[None, :] < pos[:, None] - d["window"] + 1)
+        probs = torch.softmax(scores.masked_fill(masked[None], float("-inf")), dim=-1)
+        a = (probs @ v).transpose(0, 1).reshape(T, nh * hd) @ weights["layers.1.attn.o_proj.weight"].t()
+        x = x + a
+        return x + ff(plain.rms_norm(x, weights["layers.1.n2.weight"], d["eps"]), 1)
+
+    x = toy_layer(attn_layer(toy_layer(x)))
+    return plain.rms_norm(x, weights["final.weight"], d["eps"]) @ weights["embed.weight"].t()
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """Different mixers in different layers, a layer named twice in the schedule, a windowed
+    attention group that gives pages back, and per-request state carried across steps."""
+    _register_toy()
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    folder = write_random_model(TOY, seed=11, out_dir=str(tmp_path), dtype=torch.float32, std=0.15)
+    weights = load_file(f"{folder}/model.safetensors")
+    assert "layers.0.mix.gain" in weights and "layers.1.attn.q_norm.weight" not in weights
+    runner = H.make_runner(folder, torch.float32, page_size=4, num_pages=32, max_request_tokens=256)
+    assert [kv is not None for kv, _ in runner.model.cache_specs()] == [False, True, False]
+    assert [st is not None for _, st in runner.model.cache_specs()] == [True, False, True]
+    requests = {f"t{i}": H.random_tokens(TOY["vocab_size"], n, 70 + i) for i, n in enumerate((40, 9, 23, 31, 17))}
+    want = {rid: toy_reference(weights, ids) for rid, ids in requests.items()}
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, 1e-4, "toy whole")
+    H.assert_close(H.replay(runner, H.cut_portions(requests, (5, 2, 9, 1))), want, 1e-4, "toy portions")
+    H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 1e-4, "toy mixed")
+    # the windowed group never held more pages per request than the window needs
+    assert runner.cache.groups[0].pool.high_water < 32 and runner.cache.pages_reused > 0
