@@ -24,6 +24,7 @@ class StepContext:
         self.q_lens: List[int] = []          # new tokens in this step, per request
         self.max_q_len = 0
         self.max_ctx_len = 0
+        self.decode_ctx_bound = 0            # when set: the context length the decode kernels size their grid for
         # device side (int32)
         self.token_ids: torch.Tensor = None  # [N]
         self.positions: torch.Tensor = None  # [N]
@@ -57,6 +58,12 @@ class StepContext:
         """Causal attention of the step's query rows (the first ``num_heads * head_dim`` columns of
         ``qkv``) over the pages of ``cache``."""
         page_size = cache.pages.shape[3]
+        if self.max_q_len == 1:
+            # every request brings one token: row r is request r
+            kernels.decode_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group],
+                                     self.ctx_len, self.decode_ctx_bound or self.max_ctx_len, mixer.num_heads,
+                                     mixer.num_kv_heads, mixer.head_dim, page_size, mixer.window or 0, mixer.scale)
+            return
         tile_req, tile_tok0 = self.attention_tiles(mixer.tokens_per_tile)
         kernels.paged_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group], self.q_start,
                                 self.ctx_len, tile_req, tile_tok0, mixer.num_heads, mixer.num_kv_heads,

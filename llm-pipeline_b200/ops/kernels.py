@@ -42,6 +42,7 @@ _SIGNATURES = {
     "llmp_swiglu": [_P, _P, _I, _I, _I, _P],
     "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -221,6 +222,38 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: to
           dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(q_start), _ptr(ctx_len),
           _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), num_heads, num_kv_heads, head_dim, page_size,
           int(window), float(scale), _stream())
+    return out
+
+
+def decode_scratch_floats(rows: int, num_heads: int, head_dim: int, max_ctx: int) -> int:
+    fn = library().llmp_decode_scratch_floats
+    fn.argtypes = [_I, _I, _I, _I]
+    fn.restype = _L
+    return int(fn(rows, num_heads, head_dim, max_ctx))
+
+
+def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
+                     block_tables: torch.Tensor, ctx_len: torch.Tensor, max_ctx: int, num_heads: int,
+                     num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one query row per request (row r belongs to request r, at position ctx_len[r] - 1)
+    over the request's pages; keys are split into fixed ranges whose partial results go through
+    ``scratch`` (float32, at least ``decode_scratch_floats(...)`` entries; allocated when None)."""
+    _i32(block_tables, "block_tables")
+    _i32(ctx_len, "ctx_len")
+    R = ctx_len.numel()
+    _need(q.dtype == pages.dtype == out.dtype, "q, pages and out must have one type")
+    _need(out.is_contiguous() and out.shape == (R, num_heads * head_dim), "decode output must be [requests, heads * head_dim]")
+    _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (2, num_kv_heads, page_size, head_dim),
+          "pages have the wrong layout")
+    need = decode_scratch_floats(R, num_heads, head_dim, max_ctx)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+          f"decode scratch must hold {need} float32 values")
+    _call("llmp_decode_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), dtype_code(q.dtype),
+          _ptr(block_tables), block_tables.stride(0), _ptr(ctx_len), R, int(max_ctx), num_heads, num_kv_heads, head_dim,
+          page_size, int(window), float(scale), _ptr(scratch), scratch.numel(), _stream())
     return out
 
 

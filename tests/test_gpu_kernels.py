@@ -160,7 +160,7 @@ def attention_reference(q, k, v, window, scale):
     return torch.einsum("nts,snd->tnd", torch.softmax(scores, dim=-1), vv.double()).float()
 
 
-def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None):
+def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None, decode=False):
     """requests: list of (context_before, new_tokens). Pages are handed out in a scrambled order."""
     k_ = K()
     gen = torch.Generator().manual_seed(seed)
@@ -203,8 +203,13 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)   # noqa: E731
     out = torch.zeros(N, nq * d, dtype=dtype, device=DEV)
     scale = d ** -0.5
-    k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
-                       dev(tile_tok0), nq, nkv, d, page_size, window, scale)
+    if decode:
+        assert all(t == 1 for _, t in requests)
+        k_.decode_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(ctx), max(ctx), nq, nkv, d, page_size,
+                            window, scale)
+    else:
+        k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
+                           dev(tile_tok0), nq, nkv, d, page_size, window, scale)
     want = torch.cat([attention_reference(q[q_start[r]:q_start[r + 1]].float().view(-1, nq, d).cpu(), ks[r].float().cpu(),
                                           vs[r].float().cpu(), window, scale) for r in range(R)])
     return out.float().cpu().view(N, nq, d), want
@@ -216,6 +221,26 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
 def test_paged_attention_mixed_batch(dtype, nq, nkv, d, page):
     got, want = run_paged(dtype, nq, nkv, d, page, [(0, 37), (130, 1), (63, 2), (64, 33), (5, 1), (0, 1)], seed=3)
     assert torch.allclose(got, want, atol=tol(dtype, 2e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (9, 3, 48, 4), (32, 8, 128, 16), (5, 5, 80, 16),
+                                           (40, 2, 64, 32), (16, 1, 256, 16)])
+def test_decode_attention_split_keys(dtype, nq, nkv, d, page):
+    # contexts on both sides of the 256-key ranges and of the 64-key tiles
+    requests = [(0, 1), (255, 1), (256, 1), (700, 1), (63, 1), (64, 1), (1030, 1)]
+    got, want = run_paged(dtype, nq, nkv, d, page, requests, seed=6, decode=True)
+    assert torch.allclose(got, want, atol=tol(dtype, 2e-5, 2e-2))
+    got_w, want_w = run_paged(dtype, nq, nkv, d, page, requests, window=300, seed=6, decode=True)
+    assert torch.allclose(got_w, want_w, atol=tol(dtype, 2e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_attention_finds_one_far_key(dtype):
+    for key_pos in (3, 255, 256, 511, 698):
+        got, want = run_paged(dtype, 8, 2, 64, 16, [(699, 1), (40, 1)], seed=4, boost=(0, key_pos, 5), decode=True)
+        assert torch.allclose(got, want, atol=tol(dtype, 3e-5, 3e-2)), key_pos
+        assert float(want[0, 5].abs().max()) > 0.5
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
