@@ -24,6 +24,17 @@ int llmp_check_launch(const char* what);
         }                                  \
     } while (0)
 
+// Raises a kernel's dynamic shared memory limit once per size (per call site), outside the launch path
+// of later calls. The limit belongs to the current device's context; the library drives one device.
+#define LLMP_ALLOW_SMEM(kernel, smem)                                                              \
+    do {                                                                                           \
+        static size_t allowed_ = 48 * 1024;                                                        \
+        if ((size_t)(smem) > allowed_) {                                                           \
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)); \
+            allowed_ = (size_t)(smem);                                                             \
+        }                                                                                          \
+    } while (0)
+
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ float to_float(float v) { return v; }

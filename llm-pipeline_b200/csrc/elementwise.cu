@@ -14,7 +14,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     const bool ok = id >= 0 && id < V;
     const T* row = table + (size_t)(ok ? id : 0) * H;
     float* dst = out + (size_t)n * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = ok ? to_float(row[c]) : 0.f;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x)
+        dst[c] = ok ? to_float(row[c]) : 0.f;
 }
 
 LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float* out, int N, int H, int V,
@@ -22,10 +23,13 @@ LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float*
     if (N <= 0) return 0;
     LLMP_REQUIRE(H > 0 && V > 0, "embedding: bad sizes H=%d V=%d", H, V);
     const int threads = H >= 1024 ? 256 : 128;
+    int col_blocks = (H + threads - 1) / threads;              // few tokens: spread a row over several blocks
+    if ((long)N * col_blocks > 4096) col_blocks = 1;
+    dim3 grid(N, col_blocks);
     if (dtype == LLMP_F32)
-        embedding_kernel<float><<<N, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+        embedding_kernel<float><<<grid, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
     else
-        embedding_kernel<bf16><<<N, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
+        embedding_kernel<bf16><<<grid, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
     return llmp_check_launch("embedding");
 }
 
@@ -99,14 +103,12 @@ LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* de
     LLMP_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", H, smem);
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == LLMP_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        LLMP_ALLOW_SMEM(add_rmsnorm_kernel<float>, smem);
         add_rmsnorm_kernel<float><<<M, threads, smem, stream>>>(residual, (const float*)delta, delta_bias,
                                                                 bias_dtype == LLMP_BF16, weight,
                                                                 weight_dtype == LLMP_BF16, eps, (float*)out, rows, H);
     } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        LLMP_ALLOW_SMEM(add_rmsnorm_kernel<bf16>, smem);
         add_rmsnorm_kernel<bf16><<<M, threads, smem, stream>>>(residual, (const bf16*)delta, delta_bias,
                                                                bias_dtype == LLMP_BF16, weight,
                                                                weight_dtype == LLMP_BF16, eps, (bf16*)out, rows, H);
@@ -140,7 +142,7 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
     T* row = qkv + (size_t)n * row_width;
     const int half = rotary_dim / 2;
     const int slot = slots ? slots[n] : -1;
-    for (int h = warp; h < heads; h += QKV_WARPS) {
+    for (int h = blockIdx.y * QKV_WARPS + warp; h < heads; h += gridDim.y * QKV_WARPS) {
         const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
         T* src = row + (size_t)h * d;
         float ss = 0.f;
@@ -192,12 +194,17 @@ LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtyp
     LLMP_REQUIRE(!pages || page_size > 0, "qkv_post: bad page size %d", page_size);
     const size_t smem = (size_t)QKV_WARPS * d * sizeof(float);
     LLMP_REQUIRE(smem <= 48 * 1024, "qkv_post: head_dim %d too large", d);
+    // Few tokens: one warp per head so that the heads run side by side; many tokens: a block walks the heads.
+    const int heads = nq + 2 * nkv;
+    int head_blocks = (heads + QKV_WARPS - 1) / QKV_WARPS;
+    if ((long)N * head_blocks > 4096) head_blocks = 1;
+    dim3 grid(N, head_blocks);
     if (dtype == LLMP_F32)
-        qkv_post_kernel<float><<<N, QKV_WARPS * 32, smem, stream>>>(
+        qkv_post_kernel<float><<<grid, QKV_WARPS * 32, smem, stream>>>(
             (float*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
             slots, (float*)pages, nq, nkv, d, page_size);
     else
-        qkv_post_kernel<bf16><<<N, QKV_WARPS * 32, smem, stream>>>(
+        qkv_post_kernel<bf16><<<grid, QKV_WARPS * 32, smem, stream>>>(
             (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
             slots, (bf16*)pages, nq, nkv, d, page_size);
     return llmp_check_launch("qkv_post");

@@ -24,6 +24,8 @@ class StepContext:
         self.q_lens: List[int] = []          # new tokens in this step, per request
         self.max_q_len = 0
         self.max_ctx_len = 0
+        self.num_logit_rows = 0
+        self.table_width = 0
         self.decode_ctx_bound = 0            # when set: the context length the decode kernels size their grid for
         # device side (int32)
         self.token_ids: torch.Tensor = None  # [N]

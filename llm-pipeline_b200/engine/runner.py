@@ -12,12 +12,13 @@ the paged cache that earlier steps left, and computes the output head for the wa
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
 from ..cache import CacheManager
 from ..models.model import Model
+from ..ops import kernels
 from ..parts import LayerCache
 from .context import StepContext
 
@@ -46,8 +47,32 @@ class _CacheViews:
         return LayerCache(pages=pages, group=group, state=self.cache.state_tensor(cache_id), writes=writes)
 
 
+class _DecodeGraph:
+    """A captured decode step for one shape: its static index buffers, context, graph and output."""
+
+    def __init__(self):
+        self.seen = 0
+        self.graph = None
+        self.host = None
+        self.dev = None
+        self.ctx = None
+        self.logits = None
+        self.copied = None
+        self.launches = 0
+
+
 class ModelRunner:
-    def __init__(self, model: Model, cache: CacheManager):
+    """``use_graphs``: steps in which every request brings exactly one token are captured in CUDA
+    graphs, one per (number of requests, wanted rows, block-table width rounded up to
+    ``GRAPH_WIDTH_STEP`` pages), and replayed; the first step of a shape runs eagerly. Models with
+    a mixer that does not declare ``graph_safe`` (a mixer whose step is not repeatable, such as
+    one that updates per-request state) always run eagerly. The logits a replayed step returns
+    live in the graph's static buffer and are valid until the next step of the same shape."""
+
+    GRAPH_WIDTH_STEP = 32
+    MAX_GRAPHS = 64
+
+    def __init__(self, model: Model, cache: CacheManager, use_graphs: bool = True):
         if model.device is None:
             raise RuntimeError("the model has no weights yet: call model.load() first")
         if model.device.type != "cuda":
@@ -59,11 +84,16 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0
+        blocks = getattr(model, "blocks", None)
+        self.use_graphs = bool(use_graphs and blocks is not None
+                               and all(getattr(b.mixer, "graph_safe", False) for b in blocks))
+        self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self.graph_replays = 0
 
-    # -- building the step's index arrays ------------------------------------------------------
-    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    # -- pages for the step's tokens -----------------------------------------------------------
+    def _reserve(self, entries: Sequence[StepEntry]) -> None:
+        """Check the entries, admit new requests and take the pages their tokens need; all or nothing."""
         cache = self.cache
-        ctx = StepContext(self.device, self.dtype)
         seen = set()
         spare = [0] * len(cache.groups)
         admitted = []
@@ -102,14 +132,19 @@ class ModelRunner:
             ok = cache.reserve(e.req_id, cache.length(e.req_id) + len(e.tokens))
             assert ok
 
-        R = len(entries)
-        N = sum(len(e.tokens) for e in entries)
+    # -- the step's index arrays ---------------------------------------------------------------
+    def _fill(self, ctx: StepContext, entries: Sequence[StepEntry], width: Optional[int] = None) -> List[int]:
+        """Host side of the context, and the flat int32 image of its device arrays:
+        token ids, positions, request of each token, q_start, ctx_len, slots, logit rows, then per
+        cache group the slot mapping and the block tables (``width`` entries per request)."""
+        cache = self.cache
         ps = cache.page_size
         token_ids: List[int] = []
         positions: List[int] = []
         token_request: List[int] = []
         q_start = [0]
         ctx_len, slots, rows = [], [], []
+        ctx.req_ids, ctx.starts, ctx.q_lens = [], [], []
         for r, e in enumerate(entries):
             start, n = cache.length(e.req_id), len(e.tokens)
             ctx.req_ids.append(e.req_id)
@@ -122,10 +157,13 @@ class ModelRunner:
             q_start.append(q_start[-1] + n)
             ctx_len.append(start + n)
             slots.append(cache.slot_of(e.req_id))
-        ctx.num_tokens, ctx.num_requests = N, R
+        ctx.num_tokens, ctx.num_requests = q_start[-1], len(entries)
         ctx.max_q_len = max(ctx.q_lens)
         ctx.max_ctx_len = max(ctx_len)
-        width = max(1, -(-ctx.max_ctx_len // ps))
+        ctx.num_logit_rows = len(rows)
+        if width is None:
+            width = max(1, -(-ctx.max_ctx_len // ps))
+        ctx.table_width = width
         flat: List[int] = token_ids + positions + token_request + q_start + ctx_len + slots + rows
         for g in range(len(cache.groups)):
             mapping: List[int] = []
@@ -133,14 +171,22 @@ class ModelRunner:
             for r, e in enumerate(entries):
                 table = cache.block_table(e.req_id, g)
                 start, n = ctx.starts[r], ctx.q_lens[r]
-                for pos in range(start, start + n):
-                    page = table[pos // ps]
-                    mapping.append(-1 if page < 0 else page * ps + pos % ps)
-                tables.extend(table[:width] + [-1] * (width - len(table[:width])))
-            flat += mapping + tables
-        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        self.last_h2d_bytes = host.numel() * 4
+                if n == 1:
+                    page = table[start // ps]
+                    mapping.append(-1 if page < 0 else page * ps + start % ps)
+                else:
+                    for pos in range(start, start + n):
+                        page = table[pos // ps]
+                        mapping.append(-1 if page < 0 else page * ps + pos % ps)
+                tables.extend(table[:width])
+                tables.extend([-1] * (width - min(width, len(table))))
+            flat += mapping
+            flat += tables
+        return flat
+
+    def _bind(self, ctx: StepContext, dev: torch.Tensor) -> None:
+        """Point the context's device arrays at their places in the flat buffer."""
+        N, R, width = ctx.num_tokens, ctx.num_requests, ctx.table_width
         cursor = 0
 
         def take(count: int) -> torch.Tensor:
@@ -151,11 +197,84 @@ class ModelRunner:
 
         ctx.token_ids, ctx.positions, ctx.token_request = take(N), take(N), take(N)
         ctx.q_start, ctx.ctx_len, ctx.slots = take(R + 1), take(R), take(R)
-        ctx.logit_rows = take(len(rows)) if rows else None
-        for g in range(len(cache.groups)):
+        ctx.logit_rows = take(ctx.num_logit_rows) if ctx.num_logit_rows else None
+        ctx.slot_mapping, ctx.block_tables = [], []
+        for _g in range(len(self.cache.groups)):
             ctx.slot_mapping.append(take(N))
             ctx.block_tables.append(take(R * width).view(R, width))
+
+    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages and build the step context with its arrays on the device (one copy)."""
+        self._reserve(entries)
+        ctx = StepContext(self.device, self.dtype)
+        flat = self._fill(ctx, entries)
+        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
+        self._bind(ctx, dev)
         return ctx
+
+    def _run(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        stream = self.model.forward(ctx, self._views)
+        return self.model.logits(ctx, stream, ctx.logit_rows) if ctx.logit_rows is not None else None
+
+    # -- captured decode steps -------------------------------------------------------------------
+    def _decode_graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        cache = self.cache
+        self._reserve(entries)
+        ps = cache.page_size
+        longest = max(cache.length(e.req_id) + 1 for e in entries)
+        step_w = self.GRAPH_WIDTH_STEP
+        width = -(-max(1, -(-longest // ps)) // step_w) * step_w
+        key = (len(entries), tuple(len(e.want) for e in entries), width)
+        slot = self._graphs.get(key)
+        if slot is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            slot = self._graphs[key] = _DecodeGraph()
+        slot.seen += 1
+        if slot.seen == 1:
+            # first step of this shape: run eagerly (this also lets libraries set themselves up)
+            ctx = StepContext(self.device, self.dtype)
+            flat = self._fill(ctx, entries)
+            host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+            self.last_h2d_bytes = host.numel() * 4
+            self._bind(ctx, host.to(self.device, non_blocking=True))
+            return self._finish(ctx, entries, self._run(ctx))
+        if slot.graph is None:
+            slot.ctx = StepContext(self.device, self.dtype)
+            flat = self._fill(slot.ctx, entries, width)
+            slot.host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+            slot.dev = slot.host.to(self.device)
+            self._bind(slot.ctx, slot.dev)
+            slot.ctx.decode_ctx_bound = width * ps
+            slot.copied = torch.cuda.Event()
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count
+            with torch.cuda.graph(graph):
+                slot.logits = self._run(slot.ctx)
+            slot.launches = kernels.launch_count - before
+            kernels.launch_count = before
+            slot.graph = graph
+        else:
+            slot.copied.synchronize()            # the previous copy out of the pinned buffer is done
+            flat = self._fill(slot.ctx, entries, width)
+            slot.host.copy_(torch.tensor(flat, dtype=torch.int32))
+            slot.dev.copy_(slot.host, non_blocking=True)
+        slot.copied.record()
+        self.last_h2d_bytes = slot.host.numel() * 4
+        slot.graph.replay()
+        kernels.launch_count += slot.launches    # every replay launches the captured kernels again
+        self.graph_replays += 1
+        return self._finish(slot.ctx, entries, slot.logits)
+
+    def _finish(self, ctx: StepContext, entries: Sequence[StepEntry], logits):
+        for r, e in enumerate(entries):
+            self.cache.commit(e.req_id, ctx.starts[r] + ctx.q_lens[r])
+        self.steps += 1
+        self.tokens_run += ctx.num_tokens
+        return logits
 
     # -- the step ----------------------------------------------------------------------------
     @torch.no_grad()
@@ -165,15 +284,11 @@ class ModelRunner:
         entries = list(entries)
         if not entries:
             return None
-        ctx = self._prepare(entries)
         with torch.cuda.device(self.device):
-            stream = self.model.forward(ctx, self._views)
-            logits = self.model.logits(ctx, stream, ctx.logit_rows) if ctx.logit_rows is not None else None
-        for r, e in enumerate(entries):
-            self.cache.commit(e.req_id, ctx.starts[r] + ctx.q_lens[r])
-        self.steps += 1
-        self.tokens_run += ctx.num_tokens
-        return logits
+            if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+                return self._decode_graph_step(entries)
+            ctx = self._prepare(entries)
+            return self._finish(ctx, entries, self._run(ctx))
 
     def release(self, req_id: Hashable) -> None:
         """The request is finished: its pages and slot go back to the pool."""

@@ -29,6 +29,8 @@ from .registry import register_mixer
 
 @register_mixer("attention")
 class PagedAttention(Mixer):
+    graph_safe = True      # a step only writes this step's keys and values: repeating it changes nothing
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  scale: float, bias: bool = False, qk_norm: bool = True, qk_norm_eps: float = 1e-6,
                  window: Optional[int] = None, position: Optional[str] = "rope", rotary_dim: Optional[int] = None,
