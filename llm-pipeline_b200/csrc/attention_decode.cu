@@ -8,9 +8,9 @@
 // scratch memory; decode_merge_kernel combines the partials of a row in ascending range order.
 // K and V tiles of DEC_TILE keys go from the pages to shared memory with 16-byte cp.async copies,
 // two tiles in flight (one when two do not fit), so the next tile streams in while this one is used.
+#include "attention_decode.cuh"
 #include "common.cuh"
 
-#define DEC_SPLIT 256
 #define DEC_TILE 64
 #define DEC_THREADS 128
 #define DEC_MAX_HEADS 8      // query heads per block
@@ -210,26 +210,46 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(const Dec
     }
 }
 
+// One block per (query head, request): weights exp(m_s - m) of the ranges once, then each thread sums
+// its columns over the ranges in ascending order.
+#define MERGE_THREADS 128
+#define MERGE_MAX_SPLITS 1024
 template <typename T>
-__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int* __restrict__ ctx_len, T* __restrict__ out, long out_stride, int nq, int d,
-                                    int max_splits) {
+__global__ void __launch_bounds__(MERGE_THREADS)
+decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const int* __restrict__ ctx_len, T* __restrict__ out, long out_stride, int nq, int d,
+                    int max_splits) {
+    __shared__ float wgt[MERGE_MAX_SPLITS];
+    __shared__ float scratch[32];
     const int r = blockIdx.y, h = blockIdx.x;
     const int ctx = ctx_len[r];
     const int nsplits = (ctx + DEC_SPLIT - 1) / DEC_SPLIT;
     const float* ml = part_ml + ((size_t)r * nq + h) * max_splits * 2;
     const float* po = part_o + ((size_t)r * nq + h) * max_splits * d;
     float m = -INFINITY;
-    for (int s = 0; s < nsplits; ++s) m = fmaxf(m, ml[2 * s]);
+    for (int s = threadIdx.x; s < nsplits; s += MERGE_THREADS) m = fmaxf(m, ml[2 * s]);
+    m = block_max(m, scratch);
     float l = 0.f;
-    for (int s = 0; s < nsplits; ++s) l += (ml[2 * s] > -INFINITY) ? ml[2 * s + 1] * expf(ml[2 * s] - m) : 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    for (int s = threadIdx.x; s < nsplits; s += MERGE_THREADS) {
+        const float ms = ml[2 * s];
+        const float w = (ms > -INFINITY) ? expf(ms - m) : 0.f;
+        wgt[s] = w;
+        l += ml[2 * s + 1] * w;
+    }
+    l = block_sum(l, scratch);
+    __syncthreads();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int c = threadIdx.x; c < d; c += MERGE_THREADS) {
         float o = 0.f;
-        for (int s = 0; s < nsplits; ++s)
-            if (ml[2 * s] > -INFINITY) o = fmaf(po[(size_t)s * d + c], expf(ml[2 * s] - m), o);
-        out[(size_t)r * out_stride + (size_t)h * d + c] = from_float<T>(l > 0.f ? o / l : 0.f);
+        for (int s = 0; s < nsplits; ++s) o = fmaf(po[(size_t)s * d + c], wgt[s], o);
+        out[(size_t)r * out_stride + (size_t)h * d + c] = from_float<T>(o * inv);
     }
 }
+
+// The tensor-core variant for bfloat16 pages (attention_decode_mma.cu).
+int llmp_launch_decode_mma(const void* q, long q_stride, const void* pages, const int* block_tables, int table_stride,
+                           const int* ctx_len, int R, int max_splits, int nq, int nkv, int d, int page_size,
+                           int window, float scale, float* part_o, float* part_ml, cudaStream_t stream);
 
 // Scratch floats the decode kernel needs for R rows whose longest context is max_ctx keys.
 LLMP_API long llmp_decode_scratch_floats(int R, int nq, int d, int max_ctx) {
@@ -246,6 +266,7 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
     LLMP_REQUIRE(page_size > 0 && max_ctx > 0, "decode attention: bad page size %d or context %d", page_size, max_ctx);
     LLMP_REQUIRE(R <= 65535, "decode attention: too many rows %d", R);
+    LLMP_REQUIRE((max_ctx + DEC_SPLIT - 1) / DEC_SPLIT <= MERGE_MAX_SPLITS, "decode attention: a context of %d keys is beyond %d", max_ctx, MERGE_MAX_SPLITS * DEC_SPLIT);
     const int esize = dtype == LLMP_F32 ? 4 : 2;
     DecodeParams p;
     const int G = nq / nkv;
@@ -272,12 +293,13 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
     if (dtype == LLMP_F32) {
         LLMP_ALLOW_SMEM(decode_attention_kernel<float>, smem);
         decode_attention_kernel<float><<<grid, DEC_THREADS, smem, stream>>>(p);
-        decode_merge_kernel<float><<<mgrid, 64, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (float*)out, out_stride, nq, d,
+        decode_merge_kernel<float><<<mgrid, MERGE_THREADS, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (float*)out, out_stride, nq, d,
                                                              p.max_splits);
     } else {
-        LLMP_ALLOW_SMEM(decode_attention_kernel<bf16>, smem);
-        decode_attention_kernel<bf16><<<grid, DEC_THREADS, smem, stream>>>(p);
-        decode_merge_kernel<bf16><<<mgrid, 64, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (bf16*)out, out_stride, nq, d,
+        if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,
+                                   page_size, window, scale, p.part_o, p.part_ml, stream))
+            return 1;
+        decode_merge_kernel<bf16><<<mgrid, MERGE_THREADS, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (bf16*)out, out_stride, nq, d,
                                                             p.max_splits);
     }
     return llmp_check_launch("decode_attention");

@@ -94,11 +94,88 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// The same operation for rows of at most 4096 entries whose width is a multiple of 4: one 4-entry
+// piece per thread, held in registers from the first load to the store, so the row makes one trip.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a);
+        raw.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                        const void* __restrict__ delta_bias, int bias_bf16,
+                                        const void* __restrict__ weight, int weight_bf16, float eps,
+                                        T* __restrict__ out, const int* __restrict__ rows, int H) {
+    __shared__ float scratch[32];
+    const int m = blockIdx.x;
+    const int r = rows ? rows[m] : m;
+    const int c = threadIdx.x * 4;
+    const bool active = c < H;
+    float x[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
+        Vec4<float>::load(residual + (size_t)r * H + c, x);
+        if (delta) {
+            float dl[4];
+            Vec4<T>::load(delta + (size_t)r * H + c, dl);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] += dl[i];
+        }
+        if (delta_bias) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] += load_as_float(delta_bias, bias_bf16, c + i);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = load_as_float(weight, weight_bf16, c + i);
+    }
+    const float ss = block_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3], scratch);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (active) {
+        if (rows == nullptr && (delta != nullptr || delta_bias != nullptr)) Vec4<float>::store(residual + (size_t)r * H + c, x);
+        float y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = w[i] * (x[i] * rstd);
+        Vec4<T>::store(out + (size_t)m * H + c, y);
+    }
+}
+
 LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* delta_bias, int bias_dtype,
                               const void* weight, int weight_dtype, float eps, void* out, int dtype,
                               const int* rows, int M, int H, cudaStream_t stream) {
     if (M <= 0) return 0;
     LLMP_REQUIRE(H > 0, "add_rmsnorm: bad width %d", H);
+    if (H % 4 == 0 && H <= 4096) {
+        const int threads = ((H / 4 + 31) / 32) * 32;
+        if (dtype == LLMP_F32)
+            add_rmsnorm_row4_kernel<float><<<M, threads, 0, stream>>>(residual, (const float*)delta, delta_bias,
+                                                                      bias_dtype == LLMP_BF16, weight,
+                                                                      weight_dtype == LLMP_BF16, eps, (float*)out, rows, H);
+        else
+            add_rmsnorm_row4_kernel<bf16><<<M, threads, 0, stream>>>(residual, (const bf16*)delta, delta_bias,
+                                                                     bias_dtype == LLMP_BF16, weight,
+                                                                     weight_dtype == LLMP_BF16, eps, (bf16*)out, rows, H);
+        return llmp_check_launch("add_rmsnorm");
+    }
     const size_t smem = (size_t)H * sizeof(float);
     LLMP_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", H, smem);
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);

@@ -80,10 +80,49 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __r
     if (threadIdx.x == 0) out[blockIdx.x] = r.i < 0 ? 0 : r.i;
 }
 
-LLMP_API int llmp_argmax(const float* logits, long stride, int M, int V, int* out, cudaStream_t stream) {
+// Long rows and few of them: ARG_CHUNKS blocks per row find the best of their slice, a second pass
+// takes the best of the slices (lowest index among equals in both).
+#define ARG_CHUNKS 32
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, long stride, int V,
+                                                             float* __restrict__ part_v, int* __restrict__ part_i) {
+    __shared__ ArgBest scratch[32];
+    const int m = blockIdx.y, chunk = blockIdx.x;
+    const int per = (V + ARG_CHUNKS - 1) / ARG_CHUNKS;
+    const int begin = chunk * per;
+    const int count = begin >= V ? 0 : (begin + per <= V ? per : V - begin);
+    ArgBest r = block_argmax(logits + (size_t)m * stride + begin, count, 1.f, scratch);
+    if (threadIdx.x == 0) {
+        part_v[m * ARG_CHUNKS + chunk] = r.v;
+        part_i[m * ARG_CHUNKS + chunk] = r.i < 0 ? -1 : r.i + begin;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out) {
+    const int m = blockIdx.x, lane = threadIdx.x;
+    ArgBest best = {part_v[m * ARG_CHUNKS + lane], part_i[m * ARG_CHUNKS + lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other;
+        other.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+        best = better(best, other);
+    }
+    if (lane == 0) out[m] = best.i < 0 ? 0 : best.i;
+}
+
+// scratch: M * ARG_CHUNKS floats followed by M * ARG_CHUNKS ints, or null (then one block per row).
+LLMP_API int llmp_argmax(const float* logits, long stride, int M, int V, int* out, void* scratch, cudaStream_t stream) {
     if (M <= 0) return 0;
     LLMP_REQUIRE(V > 0, "argmax: bad vocabulary size %d", V);
-    argmax_kernel<<<M, SAMPLE_THREADS, 0, stream>>>(logits, stride, V, out);
+    static_assert(ARG_CHUNKS == 32, "the final pass is one warp per row");
+    if (scratch && V >= 8192 && M <= 1024) {
+        float* part_v = (float*)scratch;
+        int* part_i = (int*)(part_v + (size_t)M * ARG_CHUNKS);
+        argmax_partial_kernel<<<dim3(ARG_CHUNKS, M), 256, 0, stream>>>(logits, stride, V, part_v, part_i);
+        argmax_final_kernel<<<M, 32, 0, stream>>>(part_v, part_i, out);
+    } else {
+        argmax_kernel<<<M, SAMPLE_THREADS, 0, stream>>>(logits, stride, V, out);
+    }
     return llmp_check_launch("argmax");
 }
 

@@ -41,9 +41,10 @@ _SIGNATURES = {
     "llmp_qkv_post": [_P, _I, _P, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "llmp_swiglu": [_P, _P, _I, _I, _I, _P],
     "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
+    "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
-    "llmp_argmax": [_P, _L, _I, _I, _P, _P],
+    "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
 }
@@ -206,6 +207,19 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
     return out
 
 
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64, bfloat16 operands, bfloat16 or float32 output: the
+    weight-streaming tensor-core kernel of the decode step."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_skinny takes bfloat16 operands")
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm shapes do not match")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
+    _call("llmp_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
+          out.stride(0), _stream())
+    return out
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
                     block_tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
                     tile_req: torch.Tensor, tile_tok0: torch.Tensor, num_heads: int, num_kv_heads: int,
@@ -260,7 +274,9 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: t
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
     _i32(out, "out")
-    _call("llmp_argmax", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _stream())
+    scratch = torch.empty(logits.shape[0] * 64, dtype=torch.int32, device=logits.device)   # slices' best values and indices
+    _call("llmp_argmax", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _ptr(scratch),
+          _stream())
     return out
 
 

@@ -24,6 +24,20 @@ def register_bf16_kernel(fn: Callable) -> None:
     _BF16_KERNELS.append(fn)
 
 
+def _skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The weight-streaming kernel for the few rows of a decode step."""
+    M, K = x.shape
+    if not 0 < M <= 64 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1 or x.stride(0) % 8 or weight.stride(0) % 8:
+        return None
+    if out_dtype not in (torch.bfloat16, torch.float32) or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
+    return kernels.gemm_skinny(x, weight, out)
+
+
+register_bf16_kernel(_skinny)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type)."""

@@ -144,6 +144,26 @@ def test_gemm_simt(dtype, M, N, Kd):
     assert torch.equal(single[0], out[M - 1])
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32], ids=["bf16", "f32out"])
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (7, 100, 1048), (16, 6144, 520), (33, 331, 264),
+                                     (64, 3000, 1032), (5, 20, 8)])
+def test_gemm_skinny(out_dtype, M, N, Kd):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=13), rnd(N, Kd, dtype=torch.bfloat16, seed=14)
+    want = x.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    K().gemm_skinny(x, w, out)
+    scale = float(want.abs().max())
+    assert float((out.double() - want).abs().max()) <= (2e-2 if out_dtype == torch.bfloat16 else 2e-4) * max(1.0, scale)
+    # a row's result does not depend on the other rows, nor on their number
+    for rows in (slice(M - 1, M), slice(0, 1)):
+        single = torch.empty(1, N, dtype=out_dtype, device=DEV)
+        K().gemm_skinny(x[rows], w, single)
+        assert torch.equal(single[0], out[rows][0])
+    with pytest.raises(K().KernelError, match="at most 64"):
+        K().gemm_skinny(rnd(65, 16, dtype=torch.bfloat16), rnd(8, 16, dtype=torch.bfloat16),
+                        torch.empty(65, 8, dtype=out_dtype, device=DEV))
+
+
 def attention_reference(q, k, v, window, scale):
     """q [T, nq, d] at positions P..P+T-1 over keys k, v [S, nkv, d]; S = P + T."""
     T, nq, d = q.shape
