@@ -1,0 +1,320 @@
+// C = A * B^T on the fifth-generation tensor cores: TMA loads, tcgen05.mma with the accumulator in
+// tensor memory, tcgen05.ld for the epilogue. bfloat16 operands, float32 accumulation.
+//
+// Both operands are K-major ([rows, K] row-major). A tile of 128 rows of A and BN rows of B is
+// multiplied per block; K is walked in blocks of 64 elements (128 bytes, one swizzle span). One
+// thread issues the TMA loads of a K block into a ring of STAGES shared-memory buffers (128-byte
+// swizzle), one thread issues four tcgen05.mma (K = 16 each) per K block and frees the buffer with
+// tcgen05.commit, four warps read the finished accumulator from tensor memory and store it.
+// For the few rows of a decode step the roles are swapped: A is the weight matrix (its rows fill the
+// 128-row side of the MMA), B is the activations (BN = 16, 32 or 64 rows, rows beyond M read as
+// zeros by the TMA unit) and the epilogue stores the transpose; nothing is padded in memory and
+// every weight byte is read once. The K order of the additions is the same for every row, so a
+// row's result does not depend on the other rows of the call.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out, the kernel records 1 in *error_flag,
+// leaves its loops, frees its tensor memory and returns; the host reads the flag.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define TC_THREADS 192
+#define TC_BM 128
+#define TC_BK 64
+#define TC_WAIT_LIMIT (1u << 20)
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded wait: false (and *error_flag = 1) when the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_flag) {
+    const uint32_t addr = tc_smem_u32(bar);
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(error_flag) != 0) return false;   // another role gave up
+    }
+    *reinterpret_cast<volatile int*>(error_flag) = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (the stride byte offset); the leading byte offset is not used by this
+// layout and carries its canonical value 1. Bits 46-47: descriptor version 1; bits 61-63: layout 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// BN: rows of B per tile (the N of the MMA). SWAP: store the transpose (Y[b row, a row]).
+template <int BN, int STAGES, bool SWAP, typename TO>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ Y,
+               int rows_a, int rows_b, int K, long ldy, int* __restrict__ error_flag) {
+    extern __shared__ unsigned char tc_raw[];
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t COLS = BN < 32 ? 32 : BN;               // tensor-memory columns (a power of two >= 32)
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_slot;
+
+    // the swizzled tiles want 1024-byte alignment
+    const uint32_t raw_addr = tc_smem_u32(tc_raw);
+    unsigned char* tiles = tc_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * TC_BM, b0 = blockIdx.y * BN;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // producer: TMA loads of K block kb into buffer kb % STAGES
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1, error_flag)) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                tma_load_2d(stage, &map_a, kb * TC_BK, a0, &full_bar[s]);
+                tma_load_2d(stage + A_BYTES, &map_b, kb * TC_BK, b0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // MMA issuer
+            constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1, error_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t a_addr = tc_smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t desc_a = umma_desc(a_addr), desc_b = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)     // 32 bytes along K per MMA: 2 units of 16 bytes
+                    umma_f16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                umma_commit(&empty_bar[s]);              // the buffer is free when these MMAs have read it
+            }
+            if (ok) umma_commit(&accum_bar);             // the accumulator is complete
+        }
+    } else {
+        // epilogue: warp w reads the 32 tensor-memory lanes of its quarter (w % 4)
+        const int quarter = warp & 3;
+        if (mbar_wait(&accum_bar, 0, error_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int arow = a0 + quarter * 32 + lane;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld_16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                if (SWAP) {
+                    // Y[b row, a row]: the lanes of a warp hold consecutive a rows
+                    if (arow < rows_a) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (b0 + c0 + j < rows_b) Y[(size_t)(b0 + c0 + j) * ldy + arow] = from_float<TO>(v[j]);
+                    }
+                } else if (arow < rows_a) {
+                    TO* dst = Y + (size_t)arow * ldy + b0 + c0;
+                    if (b0 + c0 + 16 <= rows_b && ((size_t)dst % 16) == 0) {
+                        if (sizeof(TO) == 4) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 8) {
+                                uint4 pack;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                pack.x = *reinterpret_cast<unsigned*>(&h0);
+                                pack.y = *reinterpret_cast<unsigned*>(&h1);
+                                pack.z = *reinterpret_cast<unsigned*>(&h2);
+                                pack.w = *reinterpret_cast<unsigned*>(&h3);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = pack;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (b0 + c0 + j < rows_b) dst[j] = from_float<TO>(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(COLS) : "memory");
+    }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long rows, k, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& m) const {
+        size_t h = (size_t)m.ptr;
+        h = h * 1000003u ^ (size_t)m.rows;
+        h = h * 1000003u ^ (size_t)m.k;
+        h = h * 1000003u ^ (size_t)m.ld;
+        return h * 1000003u ^ (size_t)m.box_rows;
+    }
+};
+
+// A [rows, K] bfloat16 row-major matrix with row pitch ld, read in boxes of box_rows x 64 elements.
+static int make_map(const void* ptr, long rows, long k, long ld, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex lock;
+    const MapKey key{ptr, rows, k, ld, box_rows};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    LLMP_REQUIRE(fn != nullptr, "gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    LLMP_REQUIRE(rc == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TO>
+static int launch_tc(const void* A, long rows_a, long lda, const void* B, long rows_b, long ldb, TO* Y, int K, long ldy,
+                     int* error_flag, cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    if (make_map(A, rows_a, K, lda, TC_BM, &map_a) || make_map(B, rows_b, K, ldb, BN, &map_b)) return 1;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * 128 + BN * 128) + 1024;
+    auto kernel = gemm_tc_kernel<BN, STAGES, SWAP, TO>;
+    LLMP_ALLOW_SMEM(kernel, smem);
+    dim3 grid((unsigned)((rows_a + TC_BM - 1) / TC_BM), (unsigned)((rows_b + BN - 1) / BN));
+    LLMP_REQUIRE(grid.y <= 65535, "gemm_tc: too many column tiles");
+    kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, Y, (int)rows_a, (int)rows_b, K, ldy, error_flag);
+    return llmp_check_launch("gemm_tc");
+}
+
+template <typename TO>
+static int dispatch_tc(const void* X, const void* W, TO* Y, int M, int N, int K, long ldx, long ldw, long ldy,
+                       int* error_flag, cudaStream_t stream) {
+    if (M <= 16) return launch_tc<16, 10, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    if (M <= 32) return launch_tc<32, 9, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    if (M <= 64) return launch_tc<64, 8, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    return launch_tc<128, 6, false, TO>(X, M, ldx, W, N, ldw, Y, K, ldy, error_flag, stream);
+}
+
+// Y[M, N] = X[M, K] * W[N, K]^T, bfloat16 operands with 16-byte aligned rows (K, ldx, ldw multiples of 8),
+// Y bfloat16 or float32. error_flag: one int in device memory that the kernel sets to 1 when a wait
+// ran out (the host checks it after synchronising).
+LLMP_API int llmp_gemm_tc(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                          long ldy, int* error_flag, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    LLMP_REQUIRE(K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
+                 "gemm_tc: K=%d and the row strides (%ld, %ld) must be multiples of 8", K, ldx, ldw);
+    LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
+    LLMP_REQUIRE(error_flag != nullptr, "gemm_tc: an error flag in device memory is required");
+    if (out_dtype == LLMP_F32) return dispatch_tc<float>(X, W, (float*)Y, M, N, K, ldx, ldw, ldy, error_flag, stream);
+    return dispatch_tc<bf16>(X, W, (bf16*)Y, M, N, K, ldx, ldw, ldy, error_flag, stream);
+}

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "llmp_swiglu": [_P, _P, _I, _I, _I, _P],
     "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
+    "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
@@ -208,7 +209,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64, bfloat16 operands, bfloat16 or float32 output: the
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16, bfloat16 operands, bfloat16 or float32 output: the
     weight-streaming tensor-core kernel of the decode step."""
     M, K = x.shape
     N = w.shape[0]
@@ -217,6 +218,38 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
     _call("llmp_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
           out.stride(0), _stream())
+    return out
+
+
+_error_flag: Optional[torch.Tensor] = None
+
+
+def error_flag() -> torch.Tensor:
+    """One int32 in pinned host memory that kernels with bounded waits set to 1 when a wait ran out.
+    The device writes it through its mapped address; the host may read it after any synchronisation."""
+    global _error_flag
+    if _error_flag is None:
+        _error_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _error_flag
+
+
+def check_error_flag() -> None:
+    if _error_flag is not None and int(_error_flag[0]) != 0:
+        _error_flag[0] = 0
+        raise KernelError("a kernel gave up waiting on one of its barriers (bounded wait ran out); its output is not valid")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA loads, accumulator in tensor
+    memory); bfloat16 operands, bfloat16 or float32 output."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_tc takes bfloat16 operands")
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm shapes do not match")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
+    _need(x.is_cuda and w.is_cuda and out.is_cuda, "gemm_tc takes CUDA tensors")
+    _call("llmp_gemm_tc", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
+          out.stride(0), error_flag().data_ptr(), _stream())
     return out
 
 

@@ -27,7 +27,7 @@ def register_bf16_kernel(fn: Callable) -> None:
 def _skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """The weight-streaming kernel for the few rows of a decode step."""
     M, K = x.shape
-    if not 0 < M <= 64 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1 or x.stride(0) % 8 or weight.stride(0) % 8:
+    if not 0 < M <= 16 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1 or x.stride(0) % 8 or weight.stride(0) % 8:
         return None
     if out_dtype not in (torch.bfloat16, torch.float32) or x.data_ptr() % 16 or weight.data_ptr() % 16:
         return None

@@ -145,8 +145,8 @@ def test_gemm_simt(dtype, M, N, Kd):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32], ids=["bf16", "f32out"])
-@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (7, 100, 1048), (16, 6144, 520), (33, 331, 264),
-                                     (64, 3000, 1032), (5, 20, 8)])
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (7, 100, 1048), (16, 6144, 520), (13, 331, 264),
+                                     (9, 20000, 1032), (3, 17000, 256), (5, 20, 8)])
 def test_gemm_skinny(out_dtype, M, N, Kd):
     x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=13), rnd(N, Kd, dtype=torch.bfloat16, seed=14)
     want = x.double() @ w.double().t()
@@ -159,9 +159,30 @@ def test_gemm_skinny(out_dtype, M, N, Kd):
         single = torch.empty(1, N, dtype=out_dtype, device=DEV)
         K().gemm_skinny(x[rows], w, single)
         assert torch.equal(single[0], out[rows][0])
-    with pytest.raises(K().KernelError, match="at most 64"):
-        K().gemm_skinny(rnd(65, 16, dtype=torch.bfloat16), rnd(8, 16, dtype=torch.bfloat16),
-                        torch.empty(65, 8, dtype=out_dtype, device=DEV))
+    with pytest.raises(K().KernelError, match="at most 16"):
+        K().gemm_skinny(rnd(17, 16, dtype=torch.bfloat16), rnd(8, 16, dtype=torch.bfloat16),
+                        torch.empty(17, 8, dtype=out_dtype, device=DEV))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32], ids=["bf16", "f32out"])
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (7, 100, 1048), (16, 6144, 520), (13, 331, 264),
+                                     (33, 512, 128), (64, 3000, 1032), (128, 256, 64), (200, 331, 520),
+                                     (2048, 1024, 4096), (300, 24, 72)])
+def test_gemm_tcgen05(out_dtype, M, N, Kd):
+    k_ = K()
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=15), rnd(N, Kd, dtype=torch.bfloat16, seed=16)
+    want = x.double() @ w.double().t()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    k_.gemm_tc(x, w, out)
+    torch.cuda.synchronize()
+    k_.check_error_flag()
+    scale = float(want.abs().max())
+    assert float((out.double() - want).abs().max()) <= (2e-2 if out_dtype == torch.bfloat16 else 5e-4) * max(1.0, scale)
+    # a row's result does not depend on the other rows of the call (same kernel variant)
+    if M > 1 and M <= 16:
+        single = torch.empty(1, N, dtype=out_dtype, device=DEV)
+        k_.gemm_tc(x[M - 1:M], w, single)
+        assert torch.equal(single[0], out[M - 1])
 
 
 def attention_reference(q, k, v, window, scale):
