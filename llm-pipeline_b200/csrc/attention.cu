@@ -183,10 +183,19 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_kernel(const Attn
     }
 }
 
-// Number of query tokens one block covers for a given group size; the caller builds the tile
-// list (tile_req, tile_tok0) with this step.
-LLMP_API int llmp_attention_tokens_per_tile(int nq, int nkv) {
+// The tensor-core kernel for bfloat16 pages (attention_prefill_mma.cu).
+int llmp_prefill_mma_tokens_per_tile(int nq, int nkv);
+bool llmp_prefill_mma_supports(int d);
+int llmp_launch_prefill_mma(const void* q, long q_stride, void* out, long out_stride, const void* pages,
+                            const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
+                            const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int d,
+                            int page_size, int window, float scale, cudaStream_t stream);
+
+// Number of query tokens one block covers for a given group size, element type and head size; the
+// caller builds the tile list (tile_req, tile_tok0) with this step.
+LLMP_API int llmp_attention_tokens_per_tile(int nq, int nkv, int dtype, int d) {
     if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+    if (dtype == LLMP_BF16 && llmp_prefill_mma_supports(d)) return llmp_prefill_mma_tokens_per_tile(nq, nkv);
     const int G = nq / nkv;
     const int heads = G < ATT_ROWS ? G : ATT_ROWS;
     return ATT_ROWS / heads;
@@ -196,11 +205,17 @@ LLMP_API int llmp_paged_attention(const void* q, long q_stride, void* out, long 
                                   int dtype, const int* block_tables, int table_stride, const int* q_start,
                                   const int* ctx_len, const int* tile_req, const int* tile_tok0, int num_tiles,
                                   int nq, int nkv, int d, int page_size, int window, float scale,
-                                  cudaStream_t stream) {
+                                  int tokens_per_tile, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads cannot share %d key/value heads", nq, nkv);
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
     LLMP_REQUIRE(page_size > 0, "attention: bad page size %d", page_size);
+    LLMP_REQUIRE(tokens_per_tile == llmp_attention_tokens_per_tile(nq, nkv, dtype, d),
+                 "attention: the tile list was built for %d tokens per tile, the kernel takes %d", tokens_per_tile,
+                 llmp_attention_tokens_per_tile(nq, nkv, dtype, d));
+    if (dtype == LLMP_BF16 && llmp_prefill_mma_supports(d))
+        return llmp_launch_prefill_mma(q, q_stride, out, out_stride, pages, block_tables, table_stride, q_start, ctx_len,
+                                       tile_req, tile_tok0, num_tiles, nq, nkv, d, page_size, window, scale, stream);
     AttnParams p;
     p.q = q; p.out = out; p.pages = pages; p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len;
     p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.q_stride = q_stride; p.out_stride = out_stride;

@@ -69,4 +69,4 @@ class StepContext:
         tile_req, tile_tok0 = self.attention_tiles(mixer.tokens_per_tile)
         kernels.paged_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group], self.q_start,
                                 self.ctx_len, tile_req, tile_tok0, mixer.num_heads, mixer.num_kv_heads,
-                                mixer.head_dim, page_size, mixer.window or 0, mixer.scale)
+                                mixer.head_dim, page_size, mixer.window or 0, mixer.scale, mixer.tokens_per_tile)

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
-    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -95,11 +95,13 @@ def _i32(t: torch.Tensor, name: str) -> None:
     _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
 
 
-def tokens_per_attention_tile(num_heads: int, num_kv_heads: int) -> int:
+def tokens_per_attention_tile(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32,
+                              head_dim: int = 0) -> int:
+    """Query tokens per tile of the general attention kernel that serves this type and head size."""
     fn = library().llmp_attention_tokens_per_tile
-    fn.argtypes = [_I, _I]
+    fn.argtypes = [_I, _I, _I, _I]
     fn.restype = _I
-    n = fn(num_heads, num_kv_heads)
+    n = fn(num_heads, num_kv_heads, dtype_code(dtype), head_dim)
     _need(n > 0, f"{num_heads} query heads cannot share {num_kv_heads} key/value heads")
     return n
 
@@ -256,8 +258,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
                     block_tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
                     tile_req: torch.Tensor, tile_tok0: torch.Tensor, num_heads: int, num_kv_heads: int,
-                    head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
-    """Causal attention of the step's query rows over the paged keys and values (general kernel)."""
+                    head_dim: int, page_size: int, window: int, scale: float, tokens_per_tile: int) -> torch.Tensor:
+    """Causal attention of the step's query rows over the paged keys and values (any portion sizes).
+    ``tokens_per_tile`` is the step the tile list was built with (``tokens_per_attention_tile``)."""
     for name, t in (("block_tables", block_tables), ("q_start", q_start), ("ctx_len", ctx_len),
                     ("tile_req", tile_req), ("tile_tok0", tile_tok0)):
         _i32(t, name)
@@ -268,7 +271,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: to
     _call("llmp_paged_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages),
           dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(q_start), _ptr(ctx_len),
           _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), num_heads, num_kv_heads, head_dim, page_size,
-          int(window), float(scale), _stream())
+          int(window), float(scale), int(tokens_per_tile), _stream())
     return out
 
 

@@ -91,7 +91,8 @@ class PagedAttention(Mixer):
         if cache.pages is None or cache.group is None:
             raise RuntimeError("the attention mixer needs the pages of its cache")
         if self.tokens_per_tile is None:
-            self.tokens_per_tile = kernels.tokens_per_attention_tile(self.num_heads, self.num_kv_heads)
+            self.tokens_per_tile = kernels.tokens_per_attention_tile(self.num_heads, self.num_kv_heads, x.dtype,
+                                                                     self.head_dim)
         page_size = cache.pages.shape[3]
         qkv = linear(x, self.w_qkv)
         cos = sin = None

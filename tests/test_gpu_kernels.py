@@ -235,7 +235,7 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
         vs.append(v)
         q_start.append(q_start[-1] + T)
         ctx.append(S)
-    tpt = k_.tokens_per_attention_tile(nq, nkv)
+    tpt = k_.tokens_per_attention_tile(nq, nkv, dtype, d)
     tile_req, tile_tok0 = [], []
     for r, (_, T) in enumerate(requests):
         for t0 in range(0, T, tpt):
@@ -250,7 +250,7 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
                             window, scale)
     else:
         k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
-                           dev(tile_tok0), nq, nkv, d, page_size, window, scale)
+                           dev(tile_tok0), nq, nkv, d, page_size, window, scale, tpt)
     want = torch.cat([attention_reference(q[q_start[r]:q_start[r + 1]].float().view(-1, nq, d).cpu(), ks[r].float().cpu(),
                                           vs[r].float().cpu(), window, scale) for r in range(R)])
     return out.float().cpu().view(N, nq, d), want
