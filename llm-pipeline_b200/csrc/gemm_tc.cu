@@ -219,6 +219,146 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- split-K for the few rows of a decode step ----------------------------------------------------------
+// With fewer 128-row tiles of the weight matrix than SMs, one tile per block would leave most of the
+// GPU without work and every working SM with more bytes to pull than it can. The blocks of a
+// thread-block cluster (1, 1, splits) therefore share one output tile and each takes a contiguous
+// share of the K blocks. When all of them are done, the blocks of rank 1.. write their float32
+// partial tiles into the shared memory of the rank-0 block (distributed shared memory; its TMA ring
+// is free by then), and rank 0 adds them in rank order and stores. No scratch in global memory, no
+// atomics, and a fixed order of additions.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_smem_addr, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      TO* __restrict__ Y, int rows_a, int rows_b, int K, long ldy, int splits,
+                      int* __restrict__ error_flag) {
+    extern __shared__ unsigned char tc_raw[];
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t COLS = BN < 32 ? 32 : BN;
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = tc_smem_u32(tc_raw);
+    unsigned char* tiles = tc_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * TC_BM, b0 = blockIdx.y * BN;
+    const int rank = (int)cluster_ctarank();
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    const int per = (kblocks + splits - 1) / splits;
+    const int kb0 = rank * per;
+    const int count = kb0 >= kblocks ? 0 : (kb0 + per <= kblocks ? per : kblocks - kb0);
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    float v[BN];                     // this thread's row of the partial tile (epilogue warps only)
+    bool have = false;
+    const int quarter = warp & 3;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < count; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, error_flag)) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                tma_load_2d(stage, &map_a, (kb0 + i) * TC_BK, a0, &full_bar[s]);
+                tma_load_2d(stage + A_BYTES, &map_b, (kb0 + i) * TC_BK, b0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+            bool ok = true;
+            for (int i = 0; i < count; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, error_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t a_addr = tc_smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t desc_a = umma_desc(a_addr), desc_b = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    umma_f16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok && count > 0) umma_commit(&accum_bar);
+        }
+    } else if (count > 0) {
+        if (mbar_wait(&accum_bar, 0, error_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float part[16];
+                tmem_ld_16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, part);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[c0 + j] = part[j];
+            }
+            have = true;
+        }
+    }
+    // every block of the cluster has finished reading its ring: rank 0's ring may now receive partial tiles
+    cluster_sync_all();
+    const int row = quarter * 32 + lane;                 // row of the tile held by an epilogue thread
+    if (warp >= 2 && rank != 0 && have) {
+        const uint32_t base = tc_smem_u32(tiles) + (uint32_t)((rank - 1) * BN * TC_BM + row) * 4u;
+#pragma unroll
+        for (int j = 0; j < BN; ++j) st_cluster_f32(base + (uint32_t)(j * TC_BM) * 4u, 0u, v[j]);
+    }
+    cluster_sync_all();
+    if (warp >= 2 && rank == 0 && have) {
+        const float* slots = reinterpret_cast<const float*>(tiles);
+        const int arow = a0 + row;
+        if (arow < rows_a) {
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                float sum = v[j];
+                for (int r = 1; r < splits; ++r) {
+                    const int rk0 = r * per;
+                    if (rk0 < kblocks) sum += slots[((size_t)(r - 1) * BN + j) * TC_BM + row];     // rank order
+                }
+                if (b0 + j < rows_b) Y[(size_t)(b0 + j) * ldy + arow] = from_float<TO>(sum);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(COLS) : "memory");
+    }
+}
+
 // ---- host side: tensor maps ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -296,12 +436,72 @@ static int launch_tc(const void* A, long rows_a, long lda, const void* B, long r
     return llmp_check_launch("gemm_tc");
 }
 
+// Number of K shares for an output with `tiles` 128-row tiles: the one that fills whole waves of SMs
+// best, with at least 8 K blocks per share, at most 8 shares (portable cluster size) and no more
+// than fit the rank-0 ring as float32 partial tiles.
+static int choose_splits(int tiles, int kblocks, int bn, size_t ring_bytes) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    int best = 1;
+    double best_score = -1.0;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > 1 && (kblocks / s < 8 || (size_t)(s - 1) * bn * TC_BM * 4 > ring_bytes)) break;
+        const int per = (kblocks + s - 1) / s;
+        if ((s - 1) * per >= kblocks) continue;          // the last share would be empty
+        const long ctas = (long)tiles * s;
+        const long waves = (ctas + sms - 1) / sms;
+        const double score = (double)ctas / (double)(waves * sms) - 0.01 * (s - 1);
+        if (score > best_score) {
+            best_score = score;
+            best = s;
+        }
+    }
+    return best;
+}
+
+template <int BN, int STAGES, typename TO>
+static int launch_tc_splitk(const void* A, long rows_a, long lda, const void* B, long rows_b, long ldb, TO* Y, int K,
+                            long ldy, int* error_flag, cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    if (make_map(A, rows_a, K, lda, TC_BM, &map_a) || make_map(B, rows_b, K, ldb, BN, &map_b)) return 1;
+    constexpr size_t ring = (size_t)STAGES * (TC_BM * 128 + BN * 128);
+    constexpr size_t smem = ring + 1024;
+    auto kernel = gemm_tc_splitk_kernel<BN, STAGES, TO>;
+    LLMP_ALLOW_SMEM(kernel, smem);
+    const int tiles = (int)((rows_a + TC_BM - 1) / TC_BM);
+    const int splits = choose_splits(tiles, (K + TC_BK - 1) / TC_BK, BN, ring);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)tiles, (unsigned)((rows_b + BN - 1) / BN), (unsigned)splits);
+    config.blockDim = dim3(TC_THREADS, 1, 1);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)splits;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_a, map_b, Y, (int)rows_a, (int)rows_b, K, ldy, splits,
+                                               error_flag);
+    if (err != cudaSuccess) {
+        llmp_set_error("gemm_tc: cluster launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    return llmp_check_launch("gemm_tc_splitk");
+}
+
 template <typename TO>
 static int dispatch_tc(const void* X, const void* W, TO* Y, int M, int N, int K, long ldx, long ldw, long ldy,
                        int* error_flag, cudaStream_t stream) {
-    if (M <= 16) return launch_tc<16, 10, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
-    if (M <= 32) return launch_tc<32, 9, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
-    if (M <= 64) return launch_tc<64, 8, true, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    if (M <= 16) return launch_tc_splitk<16, 10, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    if (M <= 32) return launch_tc_splitk<32, 9, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
+    if (M <= 64) return launch_tc_splitk<64, 8, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
     return launch_tc<128, 6, false, TO>(X, M, ldx, W, N, ldw, Y, K, ldy, error_flag, stream);
 }
 

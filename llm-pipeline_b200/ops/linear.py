@@ -24,17 +24,35 @@ def register_bf16_kernel(fn: Callable) -> None:
     _BF16_KERNELS.append(fn)
 
 
-def _skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
-    """The weight-streaming kernel for the few rows of a decode step."""
+def _tensor_memory(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The tcgen05 kernel (TMA, accumulator in tensor memory, cluster split-K) for at most 16 rows of a decode
+    step against a long K, where it reads the weights faster than the library product does."""
     M, K = x.shape
-    if not 0 < M <= 16 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1 or x.stride(0) % 8 or weight.stride(0) % 8:
+    if not 0 < M <= 16 or K < 8192 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1:
         return None
-    if out_dtype not in (torch.bfloat16, torch.float32) or x.data_ptr() % 16 or weight.data_ptr() % 16:
+    if x.stride(0) % 8 or weight.stride(0) % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return None
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
+    return kernels.gemm_tc(x, weight, out)
+
+
+def _skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The weight-streaming mma.sync kernel for at most 16 rows against a narrow output (few tiles),
+    where it matches or beats the library product."""
+    M, K = x.shape
+    if not 0 < M <= 16 or weight.shape[0] > 4096 or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1:
+        return None
+    if x.stride(0) % 8 or weight.stride(0) % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return None
+    if out_dtype not in (torch.bfloat16, torch.float32):
         return None
     out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
     return kernels.gemm_skinny(x, weight, out)
 
 
+register_bf16_kernel(_tensor_memory)
 register_bf16_kernel(_skinny)
 
 
