@@ -139,7 +139,7 @@ def build_ours(cfg, layers, batch_cap, dtype):
     config = resolve_config({**cfg, "num_hidden_layers": layers})
     model = build_model(config)
     model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
-    tokens_per_request = CONTEXT + 128
+    tokens_per_request = CONTEXT + 256
     pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
     engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=pages, max_num_seqs=batch_cap,
                               max_num_batched_tokens=PREFILL_TOKENS, max_model_len=tokens_per_request)
@@ -199,7 +199,7 @@ def time_decode(engine, batch, steps, warmup, seed, e2e=True):
     greedy = SamplingConfig(temperature=0.0)
     e2e_prompts = random_prompts(vocab, batch, CONTEXT - 1, seed + 1)
     for p in e2e_prompts:
-        engine.add_request(p, max_tokens=warmup + steps + 2, sampling=greedy, ignore_eos=True)
+        engine.add_request(p, max_tokens=warmup + steps + 2 * batch + 8, sampling=greedy, ignore_eos=True)
     while any(r.num_pending > 1 or not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()                            # prompts, portion by portion
     for _ in range(warmup):

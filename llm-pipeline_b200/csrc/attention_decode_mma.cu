@@ -179,13 +179,11 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
         for (int ks = 0; ks < d16; ++ks) {
             unsigned a[4];
             ldmatrix_x4(a, Qs + (size_t)(lane & 15) * stride + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb) {
-                const bf16* krow = Kg + (size_t)(nb * 8 + g) * stride + ks * 16 + 2 * t;
-                const unsigned b0 = *reinterpret_cast<const unsigned*>(krow);
-                const unsigned b1 = *reinterpret_cast<const unsigned*>(krow + 8);
-                mma_bf16_16816(s[nb], a, b0, b1);
-            }
+            // four 8x8 blocks of K at once: keys 0..7 and 8..15, each with dims ks*16.. and ks*16+8..
+            unsigned kf[4];
+            ldmatrix_x4(kf, Kg + (size_t)((lane >> 4) * 8 + (lane & 7)) * stride + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(s[0], a, kf[0], kf[1]);
+            mma_bf16_16816(s[1], a, kf[2], kf[3]);
         }
         // mask and scale; key of s[nb][c] is grp*16 + nb*8 + 2t + (c & 1), row g + 8*(c >> 1)
         float mx[2] = {-INFINITY, -INFINITY};

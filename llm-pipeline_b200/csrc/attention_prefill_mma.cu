@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
     for (int ks = 0; ks < D16; ++ks)
         pf_ldmatrix_x4(qf[ks], Qs + (size_t)(warp * 16 + (lane & 15)) * STRIDE + ks * 16 + (lane >> 4) * 8);
 
+    const float scale_log2 = p.scale * 1.4426950408889634f;
     const int warp_last_tok = (warp * 16 + 15) / hpc;
     const int warp_hi_pos = pos0 + tok0 + (warp_last_tok < ntok ? warp_last_tok : ntok - 1);
     int buf = 0;
@@ -179,11 +180,12 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
 #pragma unroll
             for (int ks = 0; ks < D16; ++ks) {
 #pragma unroll
-                for (int nb = 0; nb < PF_KEYS / 8; ++nb) {
-                    const bf16* krow = Ks + (size_t)(nb * 8 + g) * STRIDE + ks * 16 + 2 * t;
-                    const unsigned b0 = *reinterpret_cast<const unsigned*>(krow);
-                    const unsigned b1 = *reinterpret_cast<const unsigned*>(krow + 8);
-                    pf_mma(s[nb], qf[ks], b0, b1);
+                for (int nb = 0; nb < PF_KEYS / 8; nb += 2) {
+                    // four 8x8 blocks of K at once: keys nb*8.. and (nb+1)*8.., each with dims ks*16.. and ks*16+8..
+                    unsigned kf[4];
+                    pf_ldmatrix_x4(kf, Ks + (size_t)((nb + (lane >> 4)) * 8 + (lane & 7)) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+                    pf_mma(s[nb], qf[ks], kf[0], kf[1]);
+                    pf_mma(s[nb + 1], qf[ks], kf[2], kf[3]);
                 }
             }
             // mask, scale, running max
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
                     const int pos = row_pos[c >> 1];
                     bool ok = j <= pos;
                     if (p.window > 0 && j < pos - p.window + 1) ok = false;
-                    s[nb][c] = ok ? s[nb][c] * p.scale : -INFINITY;
+                    s[nb][c] = ok ? s[nb][c] * scale_log2 : -INFINITY;     // scores in units of log2: exp(x) = exp2(x * log2 e)
                     mx[c >> 1] = fmaxf(mx[c >> 1], s[nb][c]);
                 }
             }
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
                 mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
                 mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
                 const float m_new = fmaxf(m_run[h2], mx[h2]);
-                alpha[h2] = (m_new > -INFINITY) ? expf(m_run[h2] - m_new) : 1.f;
+                alpha[h2] = (m_new > -INFINITY) ? exp2f(m_run[h2] - m_new) : 1.f;
                 m_run[h2] = m_new;
             }
             float sum[2] = {0.f, 0.f};
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
             for (int nb = 0; nb < PF_KEYS / 8; ++nb) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const float pr = (m_run[c >> 1] > -INFINITY) ? expf(s[nb][c] - m_run[c >> 1]) : 0.f;
+                    const float pr = (m_run[c >> 1] > -INFINITY) ? exp2f(s[nb][c] - m_run[c >> 1]) : 0.f;
                     s[nb][c] = pr;
                     sum[c >> 1] += pr;
                 }

@@ -203,8 +203,46 @@ LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* de
 // Pages are [num_pages, 2 (K,V), nkv, page_size, d];  slot = page * page_size + offset, or -1 to skip.
 // One warp per (token, head); 4 warps per block.
 // ------------------------------------------------------------------------------------------
+// Contiguous pieces of VEC elements as one load or store (VEC = 1, 2 or 4; the address must be aligned to the piece).
+template <typename T, int VEC> struct Piece;
+template <int VEC> struct Piece<float, VEC> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) {
+        if (VEC == 4) { const float4 x = *reinterpret_cast<const float4*>(p); v[0] = x.x; v[1 % VEC] = x.y; v[2 % VEC] = x.z; v[3 % VEC] = x.w; }
+        else if (VEC == 2) { const float2 x = *reinterpret_cast<const float2*>(p); v[0] = x.x; v[1 % VEC] = x.y; }
+        else v[0] = p[0];
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[VEC]) {
+        if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+        else if (VEC == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1 % VEC]);
+        else p[0] = v[0];
+    }
+};
+template <int VEC> struct Piece<bf16, VEC> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[VEC]) {
+        if (VEC == 4) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(p);
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+            v[0] = __low2float(a); v[1 % VEC] = __high2float(a); v[2 % VEC] = __low2float(b); v[3 % VEC] = __high2float(b);
+        } else if (VEC == 2) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(p);
+            v[0] = __low2float(a); v[1 % VEC] = __high2float(a);
+        } else v[0] = __bfloat162float(p[0]);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[VEC]) {
+        if (VEC == 4) {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1 % VEC]), b = __floats2bfloat162_rn(v[2 % VEC], v[3 % VEC]);
+            uint2 raw;
+            raw.x = *reinterpret_cast<const unsigned*>(&a);
+            raw.y = *reinterpret_cast<const unsigned*>(&b);
+            *reinterpret_cast<uint2*>(p) = raw;
+        } else if (VEC == 2) {
+            *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1 % VEC]);
+        } else p[0] = __float2bfloat16_rn(v[0]);
+    }
+};
+
 #define QKV_WARPS 4
-template <typename T>
+template <typename T, int VEC>
 __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bias, int bias_bf16,
                                 const void* __restrict__ q_w, const void* __restrict__ k_w, int w_bf16,
                                 float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -223,11 +261,15 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
         const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
         T* src = row + (size_t)h * d;
         float ss = 0.f;
-        for (int i = lane; i < d; i += 32) {
-            float v = to_float(src[i]);
-            if (bias) v += load_as_float(bias, bias_bf16, (size_t)h * d + i);
-            x[i] = v;
-            ss += v * v;
+        for (int i = lane * VEC; i < d; i += 32 * VEC) {
+            float v[VEC];
+            Piece<T, VEC>::load(src + i, v);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                if (bias) v[e] += load_as_float(bias, bias_bf16, (size_t)h * d + i + e);
+                x[i + e] = v[e];
+                ss += v[e] * v[e];
+            }
         }
         __syncwarp();
         const void* w = is_q ? q_w : k_w;
@@ -247,13 +289,21 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
             }
             __syncwarp();
         }
+        T* dst = nullptr;
         if (is_q) {
-            for (int i = lane; i < d; i += 32) src[i] = from_float<T>(x[i]);
+            dst = src;
         } else if (pages && slot >= 0) {
             const int kvh = is_k ? h - nq : h - nq - nkv;
             const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
-            T* dst = pages + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * d;
-            for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
+            dst = pages + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * d;
+        }
+        if (dst) {
+            for (int i = lane * VEC; i < d; i += 32 * VEC) {
+                float v[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v[e] = x[i + e];
+                Piece<T, VEC>::store(dst + i, v);
+            }
         }
         __syncwarp();
     }
@@ -274,31 +324,38 @@ LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtyp
     // Few tokens: one warp per head so that the heads run side by side; many tokens: a block walks the heads.
     const int heads = nq + 2 * nkv;
     int head_blocks = (heads + QKV_WARPS - 1) / QKV_WARPS;
-    if ((long)N * head_blocks > 4096) head_blocks = 1;
+    if ((long)N * head_blocks > (1L << 18)) head_blocks = 1;
     dim3 grid(N, head_blocks);
-    if (dtype == LLMP_F32)
-        qkv_post_kernel<float><<<grid, QKV_WARPS * 32, smem, stream>>>(
-            (float*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
-            slots, (float*)pages, nq, nkv, d, page_size);
-    else
-        qkv_post_kernel<bf16><<<grid, QKV_WARPS * 32, smem, stream>>>(
-            (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim,
-            slots, (bf16*)pages, nq, nkv, d, page_size);
+    // pieces of 4 elements when every head starts on such a piece in the qkv rows and in the pages, else 2, else 1
+    const int vec = d % 4 == 0 ? 4 : (d % 2 == 0 ? 2 : 1);
+#define QKV_LAUNCH(T, V)                                                                                              \
+    qkv_post_kernel<T, V><<<grid, QKV_WARPS * 32, smem, stream>>>(                                                    \
+        (T*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, rotary_dim, slots, \
+        (T*)pages, nq, nkv, d, page_size)
+    if (dtype == LLMP_F32) {
+        if (vec == 4) QKV_LAUNCH(float, 4); else if (vec == 2) QKV_LAUNCH(float, 2); else QKV_LAUNCH(float, 1);
+    } else {
+        if (vec == 4) QKV_LAUNCH(bf16, 4); else if (vec == 2) QKV_LAUNCH(bf16, 2); else QKV_LAUNCH(bf16, 1);
+    }
+#undef QKV_LAUNCH
     return llmp_check_launch("qkv_post");
 }
 
 // ------------------------------------------------------------------------------------------
 // SwiGLU: out[n, i] = silu(gu[n, i]) * gu[n, I + i],  silu(z) = z / (1 + exp(-z)), float32 inside.
 // ------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
     const int n = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= I) return;
     const T* row = gu + (size_t)n * 2 * I;
-    const float g = to_float(row[i]), u = to_float(row[(size_t)I + i]);
-    const float act = g / (1.f + expf(-g));
-    out[(size_t)n * I + i] = from_float<T>(act * u);
+    float g[VEC], u[VEC], y[VEC];
+    Piece<T, VEC>::load(row + i, g);
+    Piece<T, VEC>::load(row + (size_t)I + i, u);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) y[e] = (g[e] / (1.f + expf(-g[e]))) * u[e];
+    Piece<T, VEC>::store(out + (size_t)n * I + i, y);
 }
 
 LLMP_API int llmp_swiglu(const void* gu, void* out, int dtype, int N, int I, cudaStream_t stream) {
@@ -309,13 +366,19 @@ LLMP_API int llmp_swiglu(const void* gu, void* out, int dtype, int N, int I, cud
     const int max_rows = 65535;
     for (int n0 = 0; n0 < N; n0 += max_rows) {
         const int rows = N - n0 < max_rows ? N - n0 : max_rows;
-        dim3 grid((I + 255) / 256, rows);
-        if (dtype == LLMP_F32)
-            swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu + (size_t)n0 * 2 * I,
-                                                           (float*)out + (size_t)n0 * I, I);
-        else
-            swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu + (size_t)n0 * 2 * I,
-                                                          (bf16*)out + (size_t)n0 * I, I);
+        const int vec = I % 4 == 0 ? 4 : 1;
+        dim3 grid((I / vec + 255) / 256, rows);
+        if (dtype == LLMP_F32) {
+            const float* src = (const float*)gu + (size_t)n0 * 2 * I;
+            float* dst = (float*)out + (size_t)n0 * I;
+            if (vec == 4) swiglu_kernel<float, 4><<<grid, 256, 0, stream>>>(src, dst, I);
+            else swiglu_kernel<float, 1><<<grid, 256, 0, stream>>>(src, dst, I);
+        } else {
+            const bf16* src = (const bf16*)gu + (size_t)n0 * 2 * I;
+            bf16* dst = (bf16*)out + (size_t)n0 * I;
+            if (vec == 4) swiglu_kernel<bf16, 4><<<grid, 256, 0, stream>>>(src, dst, I);
+            else swiglu_kernel<bf16, 1><<<grid, 256, 0, stream>>>(src, dst, I);
+        }
     }
     return llmp_check_launch("swiglu");
 }
