@@ -250,8 +250,16 @@ def run_ours(args):
     engine = build_ours(cfg, layers, max(64, args.batch), dtype)
     clocks = ClockSampler()
     clocks.start()
-    main = time_decode(engine, args.batch, args.steps, args.warmup, seed=1)
+    if args.only == "prefill":
+        clocks.stop()
+        prefill_ms = time_prefill(engine, PREFILL_TOKENS, repeats=2, warmup=3)
+        print(json.dumps({"only": "prefill", "layers": layers, "prefill_ms": round(prefill_ms, 3)}))
+        return 0
+    main = time_decode(engine, args.batch, args.steps, args.warmup, seed=1, e2e=args.only == "all")
     clock_info = clocks.stop()
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(main["ms"], 4)}))
+        return 0
     points = {}
     for b in (1, 64):
         r = time_decode(engine, b, max(5, args.steps // 2), args.warmup, seed=10 + b, e2e=False)
@@ -359,6 +367,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
+                        help="run one part only (for profiler captures on a small case); the line then lacks the other parts")
     args = parser.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
