@@ -6,8 +6,8 @@
 // streams serve all query heads that share the key/value head. Each of the four warps owns 16 rows
 // and keeps their online softmax and output in registers. Keys are walked in tiles of 64 aligned to
 // key 0 (the same operations for a row however the prompt was cut), copied from the pages with
-// 16-byte cp.async into a two-deep ring of shared-memory tiles; tiles entirely above the causal
-// diagonal or below the window are skipped.
+// 16-byte cp.async into one shared-memory tile per block (four blocks share an SM and cover each
+// other's copies); tiles entirely above the causal diagonal or below the window are skipped.
 #include "common.cuh"
 
 #define PF_ROWS 64
@@ -54,6 +54,13 @@ __device__ __forceinline__ void pf_mma(float (&c)[4], const unsigned (&a)[4], un
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x by the special-function unit (relative error about 2^-22; the probabilities are rounded to bfloat16 anyway)
+__device__ __forceinline__ float pf_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ unsigned pf_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&v);
@@ -61,20 +68,22 @@ __device__ __forceinline__ unsigned pf_pack(float lo, float hi) {
 
 // D16: head size / 16 (the K steps of Q K^T; the output has 2 * D16 blocks of 8 columns).
 template <int D16>
-__global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(PF_THREADS, 4) prefill_attention_mma_kernel(const PrefillParams p) {
     extern __shared__ __align__(16) unsigned char pf_smem[];
     constexpr int D = D16 * 16;
     constexpr int STRIDE = D + 8;                                // padded rows: conflict-free ldmatrix
     constexpr int VEC_PER_ROW = D / 8;
     bf16* Qs = reinterpret_cast<bf16*>(pf_smem);                 // [PF_ROWS][STRIDE]
-    bf16* ring = Qs + PF_ROWS * STRIDE;                          // [2][K tile | V tile], each [PF_KEYS][STRIDE]
+    bf16* ring = Qs + PF_ROWS * STRIDE;                          // [K tile | V tile], each [PF_KEYS][STRIDE]
     constexpr int STAGE_ELEMS = 2 * PF_KEYS * STRIDE;
-    __shared__ long long key_off[2][PF_KEYS];
+    __shared__ long long key_off[1][PF_KEYS];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r = p.tile_req[blockIdx.x];
-    const int tok0 = p.tile_tok0[blockIdx.x];
+    // later tiles of a prompt see more keys: start them first so that the long blocks do not form the tail
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int r = p.tile_req[tile];
+    const int tok0 = p.tile_tok0[tile];
     const int kvh = blockIdx.y / p.head_chunks, chunk = blockIdx.y % p.head_chunks;
     const int G = p.nq / p.nkv;
     const int hpc = p.heads_per_cta;
@@ -146,90 +155,96 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
     for (int i = 0; i < 2 * D16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
-    unsigned qf[D16][4];
-
-    const int tile_lo = (lo / PF_KEYS) * PF_KEYS;
-    issue_tile(tile_lo, 0);                                      // hi >= 0 always: a block has at least one token
-    asm volatile("cp.async.wait_group 1;\n" ::: "memory");       // the query rows have landed (the tile may still fly)
-    __syncthreads();
-#pragma unroll
-    for (int ks = 0; ks < D16; ++ks)
-        pf_ldmatrix_x4(qf[ks], Qs + (size_t)(warp * 16 + (lane & 15)) * STRIDE + ks * 16 + (lane >> 4) * 8);
 
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const int warp_last_tok = (warp * 16 + 15) / hpc;
     const int warp_hi_pos = pos0 + tok0 + (warp_last_tok < ntok ? warp_last_tok : ntok - 1);
-    int buf = 0;
+    // lowest position among this warp's rows: keys up to it need no causal mask (rows that do not exist have
+    // zero queries and are never stored, so they need none either)
+    const int warp_first_tok = (warp * 16) / hpc;
+    const int warp_lo_pos = pos0 + tok0 + (warp_first_tok < ntok ? warp_first_tok : ntok - 1);
+    const bf16* Ks = ring;
+    const bf16* Vs = ring + PF_KEYS * STRIDE;
+    const bf16* Qw = Qs + (size_t)(warp * 16 + (lane & 15)) * STRIDE + (lane >> 4) * 8;   // this lane's ldmatrix row of Q
+    const int tile_lo = (lo / PF_KEYS) * PF_KEYS;
     for (int j0 = tile_lo; j0 <= hi; j0 += PF_KEYS) {
-        const bool more = j0 + PF_KEYS <= hi;
-        if (more) {
-            issue_tile(j0 + PF_KEYS, buf ^ 1);
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        }
+        issue_tile(j0, 0);
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         __syncthreads();
-        const bf16* Ks = ring + (size_t)buf * STAGE_ELEMS;
-        const bf16* Vs = Ks + PF_KEYS * STRIDE;
-
-        // this warp's rows may see nothing of the tile (all its positions lie before the tile): skip the math
-        if (j0 <= warp_hi_pos) {
-            float s[PF_KEYS / 8][4];
+        // two halves of 32 keys, so that a half's scores fit 16 registers
 #pragma unroll
-            for (int nb = 0; nb < PF_KEYS / 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+        for (int half = 0; half < 2; ++half) {
+            const int jh = j0 + half * 32;
+            if (jh > warp_hi_pos) continue;          // every row of this warp lies before these keys
+            float s[4][4];
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < D16; ++ks) {
+                unsigned qa[4];
+                pf_ldmatrix_x4(qa, Qw + ks * 16);
 #pragma unroll
-                for (int nb = 0; nb < PF_KEYS / 8; nb += 2) {
+                for (int nb = 0; nb < 4; nb += 2) {
                     // four 8x8 blocks of K at once: keys nb*8.. and (nb+1)*8.., each with dims ks*16.. and ks*16+8..
                     unsigned kf[4];
-                    pf_ldmatrix_x4(kf, Ks + (size_t)((nb + (lane >> 4)) * 8 + (lane & 7)) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
-                    pf_mma(s[nb], qf[ks], kf[0], kf[1]);
-                    pf_mma(s[nb + 1], qf[ks], kf[2], kf[3]);
+                    pf_ldmatrix_x4(kf, Ks + (size_t)(half * 32 + (nb + (lane >> 4)) * 8 + (lane & 7)) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+                    pf_mma(s[nb], qa, kf[0], kf[1]);
+                    pf_mma(s[nb + 1], qa, kf[2], kf[3]);
                 }
             }
-            // mask, scale, running max
+            // mask (only where the causal diagonal or the window edge crosses these keys), running max of raw scores
+            const bool need_mask = (jh + 31 > warp_lo_pos) || (p.window > 0 && jh < warp_hi_pos - p.window + 1);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (need_mask) {
 #pragma unroll
-            for (int nb = 0; nb < PF_KEYS / 8; ++nb) {
+                for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int j = j0 + nb * 8 + 2 * t + (c & 1);
-                    const int pos = row_pos[c >> 1];
-                    bool ok = j <= pos;
-                    if (p.window > 0 && j < pos - p.window + 1) ok = false;
-                    s[nb][c] = ok ? s[nb][c] * scale_log2 : -INFINITY;     // scores in units of log2: exp(x) = exp2(x * log2 e)
-                    mx[c >> 1] = fmaxf(mx[c >> 1], s[nb][c]);
+                    for (int c = 0; c < 4; ++c) {
+                        const int j = jh + nb * 8 + 2 * t + (c & 1);
+                        const int pos = row_pos[c >> 1];
+                        bool ok = j <= pos;
+                        if (p.window > 0 && j < pos - p.window + 1) ok = false;
+                        if (!ok) s[nb][c] = -INFINITY;
+                    }
                 }
             }
-            float alpha[2];
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mx[c >> 1] = fmaxf(mx[c >> 1], s[nb][c]);
+            }
+            // running max and sum live in units of log2 (exp(x * scale) = 2^(x * scale * log2 e))
+            float alpha[2], m_scaled[2];
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
                 mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
                 mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
-                const float m_new = fmaxf(m_run[h2], mx[h2]);
-                alpha[h2] = (m_new > -INFINITY) ? exp2f(m_run[h2] - m_new) : 1.f;
+                const float m_new = fmaxf(m_run[h2], mx[h2] * scale_log2);
+                alpha[h2] = (m_new > -INFINITY) ? pf_ex2(m_run[h2] - m_new) : 1.f;
                 m_run[h2] = m_new;
+                m_scaled[h2] = (m_new > -INFINITY) ? m_new : 0.f;     // a row without any key keeps p = 2^(-inf) = 0
             }
             float sum[2] = {0.f, 0.f};
 #pragma unroll
-            for (int nb = 0; nb < PF_KEYS / 8; ++nb) {
+            for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const float pr = (m_run[c >> 1] > -INFINITY) ? exp2f(s[nb][c] - m_run[c >> 1]) : 0.f;
+                    const float pr = pf_ex2(fmaf(s[nb][c], scale_log2, -m_scaled[c >> 1]));
                     s[nb][c] = pr;
                     sum[c >> 1] += pr;
                 }
             }
             l_run[0] = l_run[0] * alpha[0] + sum[0];
             l_run[1] = l_run[1] * alpha[1] + sum[1];
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-            for (int i = 0; i < 2 * D16; ++i) {
-                o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                for (int i = 0; i < 2 * D16; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
             }
             // O += P V, 16 keys per step
 #pragma unroll
-            for (int kk = 0; kk < PF_KEYS / 16; ++kk) {
+            for (int kk = 0; kk < 2; ++kk) {
                 unsigned pa[4];
                 pa[0] = pf_pack(s[2 * kk][0], s[2 * kk][1]);
                 pa[1] = pf_pack(s[2 * kk][2], s[2 * kk][3]);
@@ -238,14 +253,13 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attention_mma_kernel(const
 #pragma unroll
                 for (int nb2 = 0; nb2 < D16; ++nb2) {
                     unsigned v[4];
-                    pf_ldmatrix_x4_trans(v, Vs + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + nb2 * 16 + (lane >> 4) * 8);
+                    pf_ldmatrix_x4_trans(v, Vs + (size_t)(half * 32 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + nb2 * 16 + (lane >> 4) * 8);
                     pf_mma(o[nb2 * 2], pa, v[0], v[1]);
                     pf_mma(o[nb2 * 2 + 1], pa, v[2], v[3]);
                 }
             }
         }
         __syncthreads();                                         // the tile's buffer may be overwritten now
-        buf ^= 1;
     }
 
     // normalise and store
@@ -292,7 +306,7 @@ int llmp_launch_prefill_mma(const void* q, long q_stride, void* out, long out_st
     p.head_chunks = (G + p.heads_per_cta - 1) / p.heads_per_cta;
     LLMP_REQUIRE((long)nkv * p.head_chunks <= 65535, "attention: too many heads");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 2) == 0, "attention: query rows must be 16-byte aligned");
-    const size_t smem = sizeof(bf16) * ((size_t)PF_ROWS * (d + 8) + (size_t)2 * 2 * PF_KEYS * (d + 8));
+    const size_t smem = sizeof(bf16) * ((size_t)PF_ROWS * (d + 8) + (size_t)2 * PF_KEYS * (d + 8));
     dim3 grid(num_tiles, nkv * p.head_chunks);
 #define PF_CASE(N)                                                               \
     case N:                                                                      \
