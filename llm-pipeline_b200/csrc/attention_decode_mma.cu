@@ -150,87 +150,77 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
     }
-    // Query rows and key group 0 have landed when at most one group (key group 1) is outstanding; the
-    // query rows were written by all warps, hence the block-wide barrier.
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(DM_GROUPS - 1) : "memory");
+    // Everything this warp asked for has landed after wait_group 0; the query rows were written by all
+    // warps, hence the block-wide barrier.
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
 
+    // A warp sees its DM_WARP_KEYS (32) keys at once: scores S[16 heads x 32 keys] as four 16x8 blocks, one
+    // softmax over them, then O = P V. No running rescale is needed inside a warp.
     float o[MAXD8][4];
 #pragma unroll
     for (int i = 0; i < MAXD8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY};      // rows g and g + 8
+    float m_run[2] = {-INFINITY, -INFINITY};      // rows g and g + 8, in units of log2
     float l_run[2] = {0.f, 0.f};                  // this lane's share of the row sums
     const int d8 = d / 8, d16 = d / 16;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
 
+    if (valid != 0u) {
+        float s[4][4];
 #pragma unroll
-    for (int grp = 0; grp < DM_GROUPS; ++grp) {
-        if (grp > 0) {
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-            __syncwarp();
-        }
-        if (((valid >> (grp * 16)) & 0xffffu) == 0u) continue;    // no key of this group is in range
-        const bf16* Kg = Ks + (size_t)(grp * 16) * stride;
-        const bf16* Vg = Vs + (size_t)(grp * 16) * stride;
-
-        // scores S[16 heads x 16 keys] as two 16x8 blocks
-        float s[2][4];
-#pragma unroll
-        for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+        for (int nb = 0; nb < 4; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
         for (int ks = 0; ks < d16; ++ks) {
             unsigned a[4];
             ldmatrix_x4(a, Qs + (size_t)(lane & 15) * stride + ks * 16 + (lane >> 4) * 8);
-            // four 8x8 blocks of K at once: keys 0..7 and 8..15, each with dims ks*16.. and ks*16+8..
-            unsigned kf[4];
-            ldmatrix_x4(kf, Kg + (size_t)((lane >> 4) * 8 + (lane & 7)) * stride + ks * 16 + ((lane >> 3) & 1) * 8);
-            mma_bf16_16816(s[0], a, kf[0], kf[1]);
-            mma_bf16_16816(s[1], a, kf[2], kf[3]);
+#pragma unroll
+            for (int nb = 0; nb < 4; nb += 2) {
+                // four 8x8 blocks of K at once: keys nb*8.. and (nb+1)*8.., each with dims ks*16.. and ks*16+8..
+                unsigned kf[4];
+                ldmatrix_x4(kf, Ks + (size_t)((nb + (lane >> 4)) * 8 + (lane & 7)) * stride + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(s[nb], a, kf[0], kf[1]);
+                mma_bf16_16816(s[nb + 1], a, kf[2], kf[3]);
+            }
         }
-        // mask and scale; key of s[nb][c] is grp*16 + nb*8 + 2t + (c & 1), row g + 8*(c >> 1)
+        // mask keys outside the range; key of s[nb][c] is nb*8 + 2t + (c & 1), row g + 8*(c >> 1)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
+        for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const bool ok = (valid >> (grp * 16 + nb * 8 + 2 * t + (c & 1))) & 1u;
-                s[nb][c] = ok ? s[nb][c] * p.scale : -INFINITY;
+                if (valid != 0xffffffffu && !((valid >> (nb * 8 + 2 * t + (c & 1))) & 1u)) s[nb][c] = -INFINITY;
                 mx[c >> 1] = fmaxf(mx[c >> 1], s[nb][c]);
             }
         }
-        float alpha[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m_run[h], mx[h]);
-            alpha[h] = (m_new > -INFINITY) ? expf(m_run[h] - m_new) : 1.f;
-            m_run[h] = m_new;
+            m_run[h] = mx[h] * scale_log2;         // at least one key is valid, so the maximum is finite
         }
-        unsigned pa[4];
-        {
-            float pr[2][4];
 #pragma unroll
-            for (int nb = 0; nb < 2; ++nb)
+        for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    pr[nb][c] = (m_run[c >> 1] > -INFINITY) ? expf(s[nb][c] - m_run[c >> 1]) : 0.f;
-            l_run[0] = l_run[0] * alpha[0] + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
-            l_run[1] = l_run[1] * alpha[1] + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
-            pa[0] = pack_bf16(pr[0][0], pr[0][1]);     // row g,     keys 2t, 2t+1
-            pa[1] = pack_bf16(pr[0][2], pr[0][3]);     // row g + 8, keys 2t, 2t+1
-            pa[2] = pack_bf16(pr[1][0], pr[1][1]);     // row g,     keys 8+2t, 8+2t+1
-            pa[3] = pack_bf16(pr[1][2], pr[1][3]);     // row g + 8
+            for (int c = 0; c < 4; ++c) {
+                float pr;
+                asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(pr) : "f"(fmaf(s[nb][c], scale_log2, -m_run[c >> 1])));
+                s[nb][c] = pr;
+                l_run[c >> 1] += pr;
+            }
         }
-        // O = O * alpha + P V; two 8-column blocks of V per ldmatrix
 #pragma unroll
-        for (int nb2 = 0; nb2 < MAXD8 / 2; ++nb2) {
-            if (nb2 * 2 < d8) {
-                unsigned v[4];
-                ldmatrix_x4_trans(v, Vg + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + nb2 * 16 + (lane >> 4) * 8);
+        for (int kk = 0; kk < 2; ++kk) {
+            unsigned pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);         // row g,     keys 16kk + 2t, +1
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);         // row g + 8
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]); // row g,     keys 16kk + 8 + 2t, +1
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]); // row g + 8
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    float (&oc)[4] = o[nb2 * 2 + half];
-                    oc[0] *= alpha[0]; oc[1] *= alpha[0]; oc[2] *= alpha[1]; oc[3] *= alpha[1];
-                    mma_bf16_16816(oc, pa, v[half * 2], v[half * 2 + 1]);
+            for (int nb2 = 0; nb2 < MAXD8 / 2; ++nb2) {
+                if (nb2 * 2 < d8) {
+                    unsigned v[4];
+                    ldmatrix_x4_trans(v, Vs + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + nb2 * 16 + (lane >> 4) * 8);
+                    mma_bf16_16816(o[nb2 * 2], pa, v[0], v[1]);
+                    mma_bf16_16816(o[nb2 * 2 + 1], pa, v[2], v[3]);
                 }
             }
         }
@@ -269,7 +259,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
         const float m = fmaxf(fmaxf(mw[0][row], mw[1][row]), fmaxf(mw[2][row], mw[3][row]));
         float wgt[DM_WARPS];
 #pragma unroll
-        for (int w = 0; w < DM_WARPS; ++w) wgt[w] = (mw[w][row] > -INFINITY) ? expf(mw[w][row] - m) : 0.f;
+        for (int w = 0; w < DM_WARPS; ++w) wgt[w] = (mw[w][row] > -INFINITY) ? exp2f(mw[w][row] - m) : 0.f;
         float* dst = p.part_o + (((size_t)r * p.nq + kvh * G + head0 + row) * p.max_splits + split) * d;
         for (int c = lane * 4; c < d; c += 128) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -290,9 +280,9 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
         float l = 0.f;
 #pragma unroll
         for (int w = 0; w < DM_WARPS; ++w)
-            if (mw[w][row] > -INFINITY) l += lw[w][row] * expf(mw[w][row] - m);
+            if (mw[w][row] > -INFINITY) l += lw[w][row] * exp2f(mw[w][row] - m);
         float* ml = p.part_ml + (((size_t)r * p.nq + kvh * G + head0 + row) * p.max_splits + split) * 2;
-        ml[0] = m;
+        ml[0] = m * 0.6931471805599453f;             // the merge kernel works in natural-log units
         ml[1] = l;
     }
 }
