@@ -148,7 +148,48 @@ class Qwen3InferenceEngine:
         return results
 
     def batch_generate(self, prompts, **kwargs):
+        """The reference's batch call (qwen3_engine.py:552-554): a list in, a list out. Here the prompts
+        share steps (continuous batching) instead of one padded rectangle."""
         return self.generate(list(prompts), **kwargs)
+
+    def continuous_batch_generate(self, prompts, **kwargs):
+        """The reference's continuous-batching call (qwen3_engine.py:562-575). This engine always batches
+        continuously, so it is the same as ``generate`` on a list."""
+        return self.generate(list(prompts), **kwargs)
+
+    def stream_generate(self, prompt, max_tokens: Optional[int] = None, temperature: Optional[float] = None,
+                        top_k: Optional[int] = None, top_p: Optional[float] = None, **kwargs):
+        """Yield the generation piece by piece as it is produced (qwen3_engine.py:556-560): decoded text
+        pieces for a string prompt, token ids for a prompt of token ids."""
+        as_text = isinstance(prompt, str)
+        if as_text and self.tokenizer is None:
+            raise ValueError("the model folder has no tokenizer; pass the prompt as a list of token ids")
+        ids = self.tokenizer(prompt)["input_ids"] if as_text else list(prompt)
+        base = self.engine.sampler.config.merged({"temperature": temperature, "top_k": top_k, "top_p": top_p, **kwargs})
+        req_id = self.engine.add_request(ids, max_tokens or self.config.max_new_tokens, base, eos_token_ids=self._eos_ids(),
+                                         ignore_eos=bool(kwargs.get("ignore_eos", False)))
+        request = self.engine._requests[req_id]
+        sent = 0
+        text_so_far = ""
+        while request.status != "finished":
+            self.engine.step()
+            if len(request.output) > sent:
+                if as_text:
+                    text = self.tokenizer.decode(request.output, skip_special_tokens=True)
+                    piece, text_so_far = text[len(text_so_far):], text
+                    if piece:
+                        yield piece
+                else:
+                    for token in request.output[sent:]:
+                        yield token
+                sent = len(request.output)
+        self.engine._requests.pop(req_id, None)
 
     def get_stats(self):
         return self.engine.stats()
+
+    def cleanup(self) -> None:
+        """Abort whatever is still queued or running and give its pages back."""
+        for request in list(self.engine.scheduler.running) + list(self.engine.scheduler.waiting):
+            self.engine.scheduler.abort(request.req_id)
+        self.engine._requests.clear()

@@ -123,6 +123,61 @@ def test_eos_and_stats(tmp_path):
     assert stats["finished"] == 1 and stats["tokens_prefilled"] == 7 and stats["live_requests"] == 0
 
 
+def test_streaming_and_cleanup(tmp_path):
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    engine = engine_for(folder, torch.float32)
+    prompt = H.random_tokens(256, 9, 77)
+    streamed = list(engine.stream_generate(prompt, max_tokens=7, temperature=0.0))
+    assert streamed == plain.greedy_generate(tiny, weights, prompt, 7)
+    assert engine.continuous_batch_generate([prompt], max_tokens=7, temperature=0.0) == [streamed]
+    engine.engine.add_request(prompt, max_tokens=50)
+    engine.engine.step()
+    assert engine.engine.cache.num_live == 1
+    engine.cleanup()
+    assert engine.engine.cache.num_live == 0 and not engine.engine.has_unfinished()
+
+
+def test_real_layer_widths_two_layers():
+    """Two layers with the widths of Qwen3-8B (hidden 4096, 32 query and 8 key/value heads of 128,
+    intermediate 12288) and a vocabulary that is no multiple of anything: the sizes the fast kernels are
+    tuned for, against the plain implementation run on the GPU in float32 (TF32 off)."""
+    from llm_pipeline_b200.cache import CacheManager
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.engine import ModelRunner
+    from llm_pipeline_b200.models import build_model
+    from llm_pipeline_b200.weights import DictSource, random_tensors
+    torch.backends.cuda.matmul.allow_tf32 = False
+    config_json = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 4096,
+                   "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+                   "vocab_size": 10007, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+                   "max_position_embeddings": 4096}
+    config = resolve_config(config_json)
+    source = random_tensors(config, seed=5, dtype=torch.bfloat16, device="cuda:0")
+    weights = {name: source.get(name).float() for name in source.names()}       # bfloat16 values, held in float32
+    requests = {"p": H.random_tokens(10007, 150, 1), "q": H.random_tokens(10007, 67, 2), "s": H.random_tokens(10007, 40, 3)}
+    want = {rid: plain.forward_logits(config_json, weights, toks).cpu() for rid, toks in requests.items()}
+    for dtype in (torch.float32, torch.bfloat16):
+        model = build_model(config).load(DictSource(weights), torch.device("cuda:0"), dtype)
+        cache = CacheManager(model.cache_specs(), page_size=16, num_pages=40, max_requests=4, max_request_tokens=1024,
+                             device=model.device, dtype=dtype)
+        runner = ModelRunner(model, cache)
+        # float32: the absolute bound of the other tests. bfloat16: these logits reach 6.5 where the tiny models'
+        # reach 1.3, so the bound is relative: 2 % of the largest logit (rounding to 8 bits of mantissa at every
+        # matrix-product input gives about 1 % here), and the mean error must stay below 2 % of the mean logit size.
+        scale = max(float(w.abs().max()) for w in want.values())
+        tol = 2e-4 if dtype == torch.float32 else 0.02 * scale
+        if dtype == torch.bfloat16:
+            got = H.replay(runner, H.cut_whole(requests))
+            for rid, ref in want.items():
+                assert float((got[rid] - ref).pow(2).mean().sqrt()) <= 0.02 * float(ref.pow(2).mean().sqrt()), rid
+        H.assert_close(H.replay(runner, H.cut_whole(requests)), want, tol, f"real widths whole {dtype}")
+        H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=32)), want, tol, f"real widths tail {dtype}")
+        H.assert_close(H.replay(runner, H.cut_mixed(requests, (37, 2, 16, 64, 5), max_live=3)), want, tol, f"real widths mixed {dtype}")
+        del runner, cache, model
+        torch.cuda.empty_cache()
+
+
 def write_trace(path, steps):
     with open(path, "w") as f:
         for i, (entries, end) in enumerate(steps):
