@@ -65,8 +65,8 @@ class ModelRunner:
     """``use_graphs``: steps in which every request brings exactly one token are captured in CUDA
     graphs, one per (number of requests, wanted rows, block-table width rounded up to
     ``GRAPH_WIDTH_STEP`` pages), and replayed; the first step of a shape runs eagerly. Models with
-    a mixer that does not declare ``graph_safe`` (a mixer whose step is not repeatable, such as
-    one that updates per-request state) always run eagerly. The logits a replayed step returns
+    a part that does not declare ``graph_safe`` (a mixer that updates per-request state, a
+    feed-forward whose launches depend on the data) always run eagerly. The logits a replayed step returns
     live in the graph's static buffer and are valid until the next step of the same shape."""
 
     GRAPH_WIDTH_STEP = 32
@@ -84,9 +84,8 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0
-        blocks = getattr(model, "blocks", None)
-        self.use_graphs = bool(use_graphs and blocks is not None
-                               and all(getattr(b.mixer, "graph_safe", False) for b in blocks))
+        parts = list(model.parts()) if hasattr(model, "parts") else None
+        self.use_graphs = bool(use_graphs and parts is not None and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
 

@@ -57,6 +57,10 @@ class ResidualStream:
 
 class Part:
     prefix: str = ""
+    # True when the part's work for a step can be captured in a CUDA graph and replayed: fixed launch
+    # shapes for fixed step shapes, no host synchronisation, and running the step twice leaves the same
+    # state. The built-in parts are; a part that does not say so keeps the whole model on eager steps.
+    graph_safe: bool = False
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}

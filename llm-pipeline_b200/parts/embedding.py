@@ -17,6 +17,8 @@ from .registry import register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
+    graph_safe = True
+
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
         self.prefix, self.vocab_size, self.hidden_size = prefix, int(vocab_size), int(hidden_size)
         self.weight: Optional[torch.Tensor] = None
@@ -35,6 +37,8 @@ class TokenEmbedding(Embedding):
 
 @register_head("linear_head")
 class LinearHead(Head):
+    graph_safe = True
+
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
         self.prefix, self.vocab_size, self.hidden_size, self.tied_to = prefix, int(vocab_size), int(hidden_size), tied_to
         self.weight: Optional[torch.Tensor] = None

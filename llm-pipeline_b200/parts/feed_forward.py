@@ -17,6 +17,8 @@ from .registry import register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int):
         self.prefix, self.hidden_size, self.intermediate_size = prefix, int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None

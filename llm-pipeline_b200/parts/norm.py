@@ -19,6 +19,8 @@ from .registry import register_norm
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, prefix: str, size: int, eps: float):
         self.prefix, self.size, self.eps = prefix, int(size), float(eps)
         self.weight: Optional[torch.Tensor] = None

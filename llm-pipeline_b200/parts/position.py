@@ -18,6 +18,8 @@ from .registry import register_position
 
 @register_position("rotary")
 class RotaryPositions(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, prefix: str, rotary_dim: int, theta: float, scaling: float = 1.0):
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {rotary_dim}")

@@ -34,6 +34,7 @@ def test_cuts_match_plain(tmp_path, config, seed, page, lengths, dtype):
     H.assert_close(H.replay(runner, H.cut_portions(requests, (7, 2, 16, 3, 5))), want, tol, "portions")
     H.assert_close(H.replay(runner, H.cut_portions(requests, (1,))), want, tol, "token by token")
     assert runner.cache.num_live == 0
+    assert runner.use_graphs and runner.graph_replays > 0       # single-token steps ran as replayed CUDA graphs
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

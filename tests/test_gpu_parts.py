@@ -302,3 +302,153 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 1e-4, "toy mixed")
     # the windowed group never held more pages per request than the window needs
     assert runner.cache.groups[0].pool.high_water < 32 and runner.cache.pages_reused > 0
+
+
+# ------------------------------------------------------------------------------------------
+# Two more toy parts defined here, not in the framework: a feed-forward with routing (top-1 of a few
+# small SwiGLU experts, router logits in float32) and another position encoding (positions divided by a
+# factor, rotation of only the first half of every head).
+# ------------------------------------------------------------------------------------------
+
+def _register_toy_routing_and_positions():
+    from llm_pipeline_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
+                                          register_architecture)
+    from llm_pipeline_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position
+    from llm_pipeline_b200.weights import ParamSpec
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        def __init__(self, prefix, hidden_size, intermediate_size, num_experts):
+            self.prefix, self.H, self.I, self.E = prefix, hidden_size, intermediate_size, num_experts
+
+        def param_specs(self):
+            specs = {f"{self.prefix}.router.weight": ParamSpec((self.E, self.H))}
+            for e in range(self.E):
+                specs[f"{self.prefix}.experts.{e}.gate_up.weight"] = ParamSpec((2 * self.I, self.H))
+                specs[f"{self.prefix}.experts.{e}.down.weight"] = ParamSpec((self.H, self.I))
+            return specs
+
+        def load(self, get):
+            self.router = get(f"{self.prefix}.router.weight", "matrix").float()
+            self.gate_up = [get(f"{self.prefix}.experts.{e}.gate_up.weight", "matrix") for e in range(self.E)]
+            self.down = [get(f"{self.prefix}.experts.{e}.down.weight", "matrix") for e in range(self.E)]
+
+        def forward(self, x, ctx):
+            from llm_pipeline_b200.ops import kernels
+            from llm_pipeline_b200.ops.linear import linear
+            choice = (x.float() @ self.router.t()).argmax(dim=-1)          # router logits in float32
+            out = torch.zeros_like(x)
+            for e in range(self.E):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                gu = linear(x[rows].contiguous(), self.gate_up[e])          # the framework's own kernels per expert
+                act = torch.empty((rows.numel(), self.I), dtype=x.dtype, device=x.device)
+                kernels.swiglu(gu, act)
+                out[rows] = linear(act, self.down[e])
+            return out, None
+
+    @register_position("toy_scaled_half_rotary")
+    class ScaledHalfRotary(PositionEncoding):
+        def __init__(self, prefix, rotary_dim, theta, factor):
+            self.rotary_dim, self.theta, self.factor = rotary_dim, theta, factor
+
+        def tables(self, ctx):
+            j = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32, device=ctx.device)
+            inv_freq = 1.0 / (self.theta ** (j / self.rotary_dim))
+            angles = (ctx.positions.float() / self.factor)[:, None] * inv_freq[None, :]
+            return angles.cos().contiguous(), angles.sin().contiguous()
+
+    class ToyRoutedConfig(ModelConfig):
+        architecture = "ToyRoutedForCausalLM"
+
+        def __init__(self, data):
+            self.data = data
+
+        @classmethod
+        def from_json(cls, data):
+            return cls(dict(data))
+
+        def to_json(self):
+            return dict(self.data)
+
+        def model_spec(self):
+            d = self.data
+            H, V, hd = d["hidden_size"], d["vocab_size"], d["head_dim"]
+            norm = {"size": H, "eps": d["eps"]}
+            layers = []
+            for i in range(d["layers"]):
+                attn = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"], "head_dim": hd,
+                                              "scale": hd ** -0.5, "qk_norm": True, "qk_norm_eps": d["eps"], "position": "half",
+                                              "rotary_dim": hd // 2}, f"blocks.{i}.attn")
+                ff = PartSpec("toy_top1_experts", {"hidden_size": H, "intermediate_size": d["intermediate_size"],
+                                                   "num_experts": d["experts"]}, f"blocks.{i}.moe")
+                layers.append(LayerSpec("pre_norm_residual", attn, ff, PartSpec("rms_norm", norm, f"blocks.{i}.n1"),
+                                        PartSpec("rms_norm", norm, f"blocks.{i}.n2")))
+            return ModelSpec("ToyRoutedForCausalLM", V, H, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "embed"),
+                             {"half": PartSpec("toy_scaled_half_rotary", {"rotary_dim": hd // 2, "theta": 5000.0, "factor": d["factor"]})},
+                             tuple(layers), tuple(ScheduleEntry(i, i) for i in range(d["layers"])),
+                             PartSpec("rms_norm", norm, "final"), PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tied_to": None}, "head"), 512)
+
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+
+
+TOY_ROUTED = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 64, "vocab_size": 211, "intermediate_size": 48, "heads": 4,
+              "kv_heads": 2, "head_dim": 32, "eps": 1e-5, "layers": 2, "experts": 3, "factor": 4.0}
+
+
+def toy_routed_reference(w, ids):
+    d = TOY_ROUTED
+    T, nh, nkv, hd = len(ids), d["heads"], d["kv_heads"], d["head_dim"]
+    x = w["embed.weight"][torch.tensor(ids)]
+    rd = hd // 2
+    j = torch.arange(0, rd, 2, dtype=torch.float32)
+    angles = (torch.arange(T).float() / d["factor"])[:, None] * (1.0 / (5000.0 ** (j / rd)))[None, :]
+    cos, sin = torch.cat((angles.cos(), angles.cos()), -1), torch.cat((angles.sin(), angles.sin()), -1)
+
+    def rope(t):                                   # t [heads, T, hd]: only the first rd entries rotate
+        head = t[..., :rd]
+        return torch.cat((head * cos[None] + plain.rotate_half(head) * sin[None], t[..., rd:]), dim=-1)
+
+    for i in range(d["layers"]):
+        p = f"blocks.{i}"
+        h = plain.rms_norm(x, w[f"{p}.n1.weight"], d["eps"])
+        q = (h @ w[f"{p}.attn.q_proj.weight"].t()).view(T, nh, hd).transpose(0, 1)
+        k = (h @ w[f"{p}.attn.k_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1)
+        v = (h @ w[f"{p}.attn.v_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1)
+        q = rope(plain.rms_norm(q, w[f"{p}.attn.q_norm.weight"], d["eps"]))
+        k = rope(plain.rms_norm(k, w[f"{p}.attn.k_norm.weight"], d["eps"]))
+        k, v = k.repeat_interleave(nh // nkv, 0), v.repeat_interleave(nh // nkv, 0)
+        pos = torch.arange(T)
+        scores = ((q @ k.transpose(1, 2)) * hd ** -0.5).masked_fill((pos[None, :] > pos[:, None])[None], float("-inf"))
+        a = (torch.softmax(scores, -1) @ v).transpose(0, 1).reshape(T, nh * hd) @ w[f"{p}.attn.o_proj.weight"].t()
+        x = x + a
+        h = plain.rms_norm(x, w[f"{p}.n2.weight"], d["eps"])
+        choice = (h @ w[f"{p}.moe.router.weight"].t()).argmax(-1)
+        out = torch.zeros_like(h)
+        for e in range(d["experts"]):
+            rows = choice == e
+            gu = h[rows] @ w[f"{p}.moe.experts.{e}.gate_up.weight"].t()
+            I = d["intermediate_size"]
+            out[rows] = (torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]) @ w[f"{p}.moe.experts.{e}.down.weight"].t()
+        x = x + out
+    return plain.rms_norm(x, w["final.weight"], d["eps"]) @ w["head.weight"].t()
+
+
+def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
+    """A feed-forward that routes each token to one expert and a position encoding with its own angle
+    formula and partial rotation, both registered from this file, through the unchanged step function:
+    logits do not depend on how tokens are cut or batched (each token's expert depends on the token alone)."""
+    _register_toy_routing_and_positions()
+    from llm_pipeline_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    folder = write_random_model(TOY_ROUTED, seed=21, out_dir=str(tmp_path), dtype=torch.float32, std=0.2)
+    weights = load_file(f"{folder}/model.safetensors")
+    assert "blocks.1.moe.experts.2.down.weight" in weights
+    runner = H.make_runner(folder, torch.float32, page_size=8, num_pages=24, max_request_tokens=256)
+    requests = {f"m{i}": H.random_tokens(TOY_ROUTED["vocab_size"], n, 40 + i) for i, n in enumerate((35, 8, 20, 27))}
+    want = {rid: toy_routed_reference(weights, ids) for rid, ids in requests.items()}
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, 2e-4, "routed whole")
+    H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=6)), want, 2e-4, "routed tail")
+    H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 2e-4, "routed mixed")
+    assert not runner.use_graphs and runner.graph_replays == 0   # the routed feed-forward does not declare graph_safe
