@@ -359,6 +359,145 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 }
 
+// ---- persistent kernel for many rows (prompt portions) -------------------------------------------------
+// One block per SM walks output tiles of 128 x BN (tile t: column block t / m_tiles, row block
+// t % m_tiles, so blocks that run side by side share a weight tile through L2). The TMA ring keeps
+// running across tiles. Two accumulators live in tensor memory: while the four epilogue warps read
+// tile i out of one (tcgen05.ld, convert, store), the MMA thread already fills the other with tile
+// i + 1. Barriers: full/empty per ring stage, accumulator-full/accumulator-empty per accumulator.
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          TO* __restrict__ Y, int rows_a, int rows_b, int K, long ldy, int* __restrict__ error_flag) {
+    extern __shared__ unsigned char tc_raw[];
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t COLS = 2 * BN;                          // two accumulators (BN = 128 or 256: a power of two)
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = tc_smem_u32(tc_raw);
+    unsigned char* tiles = tc_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (rows_a + TC_BM - 1) / TC_BM, n_tiles = (rows_b + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_full[0], 1);
+        mbar_init(&acc_full[1], 1);
+        mbar_init(&acc_empty[0], 4);       // one arrival per epilogue warp
+        mbar_init(&acc_empty[1], 4);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                          // K blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int a0 = (tile % m_tiles) * TC_BM, b0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, error_flag)) { ok = false; break; }
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                    tma_load_2d(stage, &map_a, kb * TC_BK, a0, &full_bar[s]);
+                    tma_load_2d(stage + A_BYTES, &map_b, kb * TC_BK, b0, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
+            int it = 0, n = 0;                                   // K blocks consumed, tiles done
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++n) {
+                const int acc = n & 1;
+                // the epilogue must have drained this accumulator (its use n / 2 - 1)
+                if (n >= 2 && !mbar_wait(&acc_empty[acc], ((n >> 1) - 1) & 1, error_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t d_addr = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, error_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a_addr = tc_smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t desc_a = umma_desc(a_addr), desc_b = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_f16(d_addr, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int n = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++n) {
+            const int acc = n & 1;
+            if (!mbar_wait(&acc_full[acc], (n >> 1) & 1, error_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int a0 = (tile % m_tiles) * TC_BM, b0 = (tile / m_tiles) * BN;
+            const int arow = a0 + quarter * 32 + lane;
+#pragma unroll 4
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld_16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0), v);
+                if (arow < rows_a) {
+                    TO* dst = Y + (size_t)arow * ldy + b0 + c0;
+                    if (b0 + c0 + 16 <= rows_b && ((size_t)dst % 16) == 0) {
+                        if (sizeof(TO) == 4) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 8) {
+                                uint4 pack;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                pack.x = *reinterpret_cast<unsigned*>(&h0);
+                                pack.y = *reinterpret_cast<unsigned*>(&h1);
+                                pack.z = *reinterpret_cast<unsigned*>(&h2);
+                                pack.w = *reinterpret_cast<unsigned*>(&h3);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = pack;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (b0 + c0 + j < rows_b) dst[j] = from_float<TO>(v[j]);
+                    }
+                }
+            }
+            // this warp has read its part of the accumulator: one arrival per warp frees it for the MMA thread
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem_u32(&acc_empty[acc])) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(COLS) : "memory");
+    }
+}
+
 // ---- host side: tensor maps ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -496,13 +635,36 @@ static int launch_tc_splitk(const void* A, long rows_a, long lda, const void* B,
     return llmp_check_launch("gemm_tc_splitk");
 }
 
+template <int BN, int STAGES, typename TO>
+static int launch_tc_persistent(const void* A, long rows_a, long lda, const void* B, long rows_b, long ldb, TO* Y, int K,
+                                long ldy, int* error_flag, cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    if (make_map(A, rows_a, K, lda, TC_BM, &map_a) || make_map(B, rows_b, K, ldb, BN, &map_b)) return 1;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * 128 + BN * 128) + 1024;
+    auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TO>;
+    LLMP_ALLOW_SMEM(kernel, smem);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const long tiles = ((rows_a + TC_BM - 1) / TC_BM) * ((rows_b + BN - 1) / BN);
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, Y, (int)rows_a, (int)rows_b, K, ldy, error_flag);
+    return llmp_check_launch("gemm_tc_persistent");
+}
+
 template <typename TO>
 static int dispatch_tc(const void* X, const void* W, TO* Y, int M, int N, int K, long ldx, long ldw, long ldy,
                        int* error_flag, cudaStream_t stream) {
     if (M <= 16) return launch_tc_splitk<16, 10, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
     if (M <= 32) return launch_tc_splitk<32, 9, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
     if (M <= 64) return launch_tc_splitk<64, 8, TO>(W, N, ldw, X, M, ldx, Y, K, ldy, error_flag, stream);
-    return launch_tc<128, 6, false, TO>(X, M, ldx, W, N, ldw, Y, K, ldy, error_flag, stream);
+    // 128 x 256 tiles do twice the work per byte read from shared memory; 128 x 128 only for narrow outputs
+    if (N >= 256) return launch_tc_persistent<256, 4, TO>(X, M, ldx, W, N, ldw, Y, K, ldy, error_flag, stream);
+    return launch_tc_persistent<128, 6, TO>(X, M, ldx, W, N, ldw, Y, K, ldy, error_flag, stream);
 }
 
 // Y[M, N] = X[M, K] * W[N, K]^T, bfloat16 operands with 16-byte aligned rows (K, ldx, ldw multiples of 8),

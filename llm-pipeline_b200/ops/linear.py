@@ -10,6 +10,7 @@
 
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -52,8 +53,30 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Op
     return kernels.gemm_skinny(x, weight, out)
 
 
+def _tensor_memory_prefill(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The persistent tcgen05 kernel (128 x 256 tiles, two accumulators in tensor memory so that the epilogue
+    of one tile overlaps the products of the next) for the many rows of a prompt portion."""
+    M, K = x.shape
+    if not OWN_PREFILL_GEMM or M < PREFILL_TC_MIN_ROWS or K % 8 or x.stride(1) != 1 or weight.stride(1) != 1:
+        return None
+    if x.stride(0) % 8 or weight.stride(0) % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return None
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
+    return kernels.gemm_tc(x, weight, out)
+
+
+# Measured on a B200 at 2,048 rows (Qwen3-8B shapes): this kernel reaches 1.14-1.44 PFLOP/s, the library product
+# 1.32-1.59, so the library product stays the default for prompt portions; LLMP_B200_OWN_PREFILL_GEMM=1 (or setting
+# this flag) routes portions of at least PREFILL_TC_MIN_ROWS rows through the own kernel. Fewer rows leave too few
+# 128-row tiles to fill the SMs.
+OWN_PREFILL_GEMM = os.environ.get("LLMP_B200_OWN_PREFILL_GEMM", "0") == "1"
+PREFILL_TC_MIN_ROWS = 1024
+
 register_bf16_kernel(_tensor_memory)
 register_bf16_kernel(_skinny)
+register_bf16_kernel(_tensor_memory_prefill)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
