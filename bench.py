@@ -38,6 +38,11 @@ QWEN3_8B = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "attention_bias": False,
     "max_position_embeddings": 4096, "hidden_act": "silu",
 }
+QWEN3_0_6B = {**QWEN3_8B, "num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16, "num_key_value_heads": 8,
+              "intermediate_size": 3072, "tie_word_embeddings": True}
+QWEN3_32B = {**QWEN3_8B, "num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "num_key_value_heads": 8,
+             "intermediate_size": 25600}
+SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 16
@@ -126,7 +131,7 @@ def prefill_flops(cfg, layers, T):
     return layers * (per_token * T + attention) + 2 * V * H
 
 
-def build_ours(cfg, layers, batch_cap, dtype):
+def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256):
     import torch
 
     from llm_pipeline_b200.config import resolve_config
@@ -139,7 +144,6 @@ def build_ours(cfg, layers, batch_cap, dtype):
     config = resolve_config({**cfg, "num_hidden_layers": layers})
     model = build_model(config)
     model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
-    tokens_per_request = CONTEXT + 256
     pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
     engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=pages, max_num_seqs=batch_cap,
                               max_num_batched_tokens=PREFILL_TOKENS, max_model_len=tokens_per_request)
@@ -240,10 +244,47 @@ def time_prefill(engine, tokens, repeats, warmup):
     return times[len(times) // 2]
 
 
+def run_mix(args):
+    """A continuous-batching mix through the Python entry point: 64 requests with prompt lengths uniform in
+    [16, 2048] and 128 decoded tokens each (seeded), context up to 4,096; reports total tokens per second."""
+    import torch
+
+    from llm_pipeline_b200.sampling import SamplingConfig
+
+    name, cfg = SHAPES[args.shape]
+    layers = args.layers or cfg["num_hidden_layers"]
+    engine = build_ours(cfg, layers, 64, torch.bfloat16, tokens_per_request=2048 + 128 + 16)
+    gen = torch.Generator().manual_seed(7)
+    lengths = torch.randint(16, 2049, (64,), generator=gen).tolist()
+    prompts = [random_prompts(cfg["vocab_size"], 1, n, 1000 + i)[0] for i, n in enumerate(lengths)]
+    greedy = SamplingConfig(temperature=0.0)
+    warm = engine.generate([prompts[0][:64]], max_tokens=4, temperature=0.0)      # builds kernels' first-call state
+    del warm
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for p in prompts:
+        engine.add_request(p, max_tokens=128, sampling=greedy, ignore_eos=True)
+    steps = 0
+    while engine.has_unfinished():
+        engine.step()
+        steps += 1
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    total = sum(lengths) + 64 * 128
+    stats = engine.stats()
+    print(json.dumps({"workload": "mix", "model": name, "layers": layers, "requests": 64, "prompt_tokens": sum(lengths),
+                      "decoded_tokens": 64 * 128, "seconds": round(seconds, 3), "tokens_per_s": round(total / seconds, 1),
+                      "decoded_tokens_per_s": round(64 * 128 / seconds, 1), "steps": steps,
+                      "mean_step_ms": round(seconds * 1e3 / steps, 3), "preemptions": stats["preemptions"]}))
+    return 0
+
+
 def run_ours(args):
     import torch
 
-    cfg = QWEN3_8B
+    if args.workload == "mix":
+        return run_mix(args)
+    name, cfg = SHAPES[args.shape]
     layers = args.layers or cfg["num_hidden_layers"]
     peak = peaks()
     dtype = torch.bfloat16
@@ -269,11 +310,11 @@ def run_ours(args):
     step_bytes = weight_bytes(cfg, layers) + args.batch * (CONTEXT + args.warmup + args.steps // 2) * kv_bytes_per_token(cfg, layers)
     achieved = step_bytes / (main["ms"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8, 2,048-token context (Qwen3-8B bf16)",
+        "metric": f"decode tok/s at batch {args.batch}, 2,048-token context ({name.split()[0]} bf16)",
         "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
-        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_model": cfg["num_hidden_layers"],
+        "config": {"model": name, "layers": layers, "layers_of_model": cfg["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
@@ -367,6 +408,9 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--shape", default="8b", choices=tuple(SHAPES), help="layer sizes (default: Qwen3-8B)")
+    parser.add_argument("--workload", default="decode", choices=("decode", "mix"),
+                        help="mix: the continuous-batching mix of 64 requests through the Python entry point")
     parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
                         help="run one part only (for profiler captures on a small case); the line then lacks the other parts")
     args = parser.parse_args()
