@@ -309,6 +309,123 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
     }
 }
 
+// Head size 128 with the whole head rotated: a half-warp per head, 8 elements per lane held in registers.
+// Element j pairs with j + 64, which lane (l ^ 8) of the half-warp holds at the same register index.
+template <typename T> struct Piece8;
+template <> struct Piece8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Piece8<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v[2 * e] = __uint_as_float(w[e] << 16);
+            v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        unsigned w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            w[e] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+#define QKV_UNROLL 3
+template <typename T>
+__global__ void __launch_bounds__(QKV_WARPS * 32)
+qkv_post_d128_kernel(T* __restrict__ qkv, const void* __restrict__ bias, int bias_bf16,
+                     const void* __restrict__ q_w, const void* __restrict__ k_w, int w_bf16, float eps,
+                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
+                     T* __restrict__ pages, int nq, int nkv, int page_size) {
+    constexpr int D = 128;
+    const int n = blockIdx.x;
+    const int hl = threadIdx.x & 15;                               // lane within the half-warp
+    const int half_warp = threadIdx.x >> 4;
+    const int heads = nq + 2 * nkv;
+    T* row = qkv + (size_t)n * heads * D;
+    const int slot = slots ? slots[n] : -1;
+    const int e0 = hl * 8;                                         // first element of this lane
+    float c[8], s[8], wq[8], wk[8];
+    {
+        const float* cp = cos_t + (size_t)n * (D / 2) + (e0 & 63);
+        const float* sp = sin_t + (size_t)n * (D / 2) + (e0 & 63);
+        Piece8<float>::load(cp, c);
+        Piece8<float>::load(sp, s);
+        if (hl < 8) {                                              // y[j] = x[j] cos - x[j + 64] sin
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[e] = -s[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wq[e] = wk[e] = 1.f;
+        if (q_w) { if (w_bf16) Piece8<bf16>::load((const bf16*)q_w + e0, wq); else Piece8<float>::load((const float*)q_w + e0, wq); }
+        if (k_w) { if (w_bf16) Piece8<bf16>::load((const bf16*)k_w + e0, wk); else Piece8<float>::load((const float*)k_w + e0, wk); }
+    }
+    // Heads in rounds of QKV_UNROLL per half-warp: the loads of a round are issued before any of its stores.
+    const int step = gridDim.y * (QKV_WARPS * 2);
+    for (int h0 = blockIdx.y * (QKV_WARPS * 2); h0 < heads; h0 += step * QKV_UNROLL) {  // uniform over the warp
+        float v[QKV_UNROLL][8];
+#pragma unroll
+        for (int u = 0; u < QKV_UNROLL; ++u) {
+            const int h = h0 + u * step + half_warp;
+            const size_t at = (size_t)(h < heads ? h : 0) * D + e0;
+            Piece8<T>::load(row + at, v[u]);
+            if (bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[u][e] += load_as_float(bias, bias_bf16, at + e);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QKV_UNROLL; ++u) {
+            if (h0 + u * step >= heads) break;                     // uniform over the warp
+            const int h = h0 + u * step + half_warp;
+            const bool live = h < heads;
+            const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+            {                                                      // every lane takes part in the shuffles
+                const void* w = is_q ? q_w : (is_k ? k_w : nullptr);
+                float ss = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += v[u][e] * v[u][e];
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (w) {
+                    const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[u][e] = (is_q ? wq[e] : wk[e]) * (v[u][e] * rstd);
+                }
+            }
+            float other[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) other[e] = __shfl_xor_sync(0xffffffffu, v[u][e], 8);
+            if (is_q || is_k) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[u][e] = v[u][e] * c[e] + other[e] * s[e];
+            }
+            T* dst = nullptr;
+            if (is_q) {
+                dst = row + (size_t)h * D + e0;
+            } else if (live && pages && slot >= 0) {
+                const int kvh = is_k ? h - nq : h - nq - nkv;
+                const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+                dst = pages + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * D + e0;
+            }
+            if (dst) Piece8<T>::store(dst, v[u]);
+        }
+    }
+}
+
 LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtype, const void* q_w, const void* k_w,
                            int w_dtype, float eps, const float* cos_t, const float* sin_t, int rotary_dim,
                            const int* slots, void* pages, int N, int nq, int nkv, int d, int page_size,
@@ -325,6 +442,23 @@ LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtyp
     const int heads = nq + 2 * nkv;
     int head_blocks = (heads + QKV_WARPS - 1) / QKV_WARPS;
     if ((long)N * head_blocks > (1L << 18)) head_blocks = 1;
+    const bool aligned16 = (((uintptr_t)qkv | (uintptr_t)pages | (uintptr_t)q_w | (uintptr_t)k_w | (uintptr_t)cos_t |
+                             (uintptr_t)sin_t) & 15) == 0;
+    if (d == 128 && rotary_dim == 128 && aligned16) {
+        // Few tokens: the heads of a token spread over blocks; many: one block walks all heads of its token, so
+        // that the tables and norm weights are read once per token.
+        const int blocks_y = N >= 512 ? 1 : (heads + 2 * QKV_WARPS - 1) / (2 * QKV_WARPS);
+        dim3 grid128(N, blocks_y);
+        if (dtype == LLMP_F32)
+            qkv_post_d128_kernel<float><<<grid128, QKV_WARPS * 32, 0, stream>>>(
+                (float*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, slots,
+                (float*)pages, nq, nkv, page_size);
+        else
+            qkv_post_d128_kernel<bf16><<<grid128, QKV_WARPS * 32, 0, stream>>>(
+                (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, slots,
+                (bf16*)pages, nq, nkv, page_size);
+        return llmp_check_launch("qkv_post");
+    }
     dim3 grid(N, head_blocks);
     // pieces of 4 elements when every head starts on such a piece in the qkv rows and in the pages, else 2, else 1
     const int vec = d % 4 == 0 ? 4 : (d % 2 == 0 ? 2 : 1);
