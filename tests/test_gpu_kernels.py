@@ -121,11 +121,14 @@ def test_qkv_post_norm_rotary_and_page_write(dtype, nq, nkv, d, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_swiglu(dtype):
-    gu = rnd(9, 2 * 300, dtype=dtype, seed=9, scale=2.0)
-    out = torch.empty(9, 300, dtype=dtype, device=DEV)
+@pytest.mark.parametrize("width", [300, 296, 77])
+def test_swiglu(dtype, width):
+    gu = rnd(9, 2 * width, dtype=dtype, seed=9, scale=2.0)
+    gu[0, :4] = torch.tensor([-30.0, 30.0, 0.0, -90.0], dtype=dtype, device=DEV)     # the ends of the sigmoid
+    out = torch.empty(9, width, dtype=dtype, device=DEV)
     K().swiglu(gu, out)
-    g, u = gu.float()[:, :300], gu.float()[:, 300:]
+    g, u = gu.float()[:, :width], gu.float()[:, width:]
+    assert torch.isfinite(out).all()
     assert torch.allclose(out.float(), torch.nn.functional.silu(g) * u, atol=tol(dtype, 1e-6, 3e-2), rtol=tol(dtype, 1e-6, 1e-2))
 
 
