@@ -191,28 +191,44 @@ int llmp_launch_prefill_mma(const void* q, long q_stride, void* out, long out_st
                             const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int d,
                             int page_size, int window, float scale, cudaStream_t stream);
 
-// Number of query tokens one block covers for a given group size, element type and head size; the
-// caller builds the tile list (tile_req, tile_tok0) with this step.
-LLMP_API int llmp_attention_tokens_per_tile(int nq, int nkv, int dtype, int d) {
+// The tcgen05 kernel for bfloat16 pages and head size 128 (attention_prefill_tc.cu).
+bool llmp_prefill_tc_supports(int nq, int nkv, int d, int page_size);
+int llmp_prefill_tc_tokens_per_tile(int nq, int nkv);
+int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
+                           const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
+                           const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int page_size,
+                           int window, float scale, int* error_flag, cudaStream_t stream);
+
+// Number of query tokens one block covers for a given group size, element type, head size and page size (0:
+// not known, which rules out the kernels that depend on it); the caller builds the tile list (tile_req,
+// tile_tok0) with this step.
+LLMP_API int llmp_attention_tokens_per_tile(int nq, int nkv, int dtype, int d, int page_size) {
     if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+    if (dtype == LLMP_BF16 && llmp_prefill_tc_supports(nq, nkv, d, page_size)) return llmp_prefill_tc_tokens_per_tile(nq, nkv);
     if (dtype == LLMP_BF16 && llmp_prefill_mma_supports(d)) return llmp_prefill_mma_tokens_per_tile(nq, nkv);
     const int G = nq / nkv;
     const int heads = G < ATT_ROWS ? G : ATT_ROWS;
     return ATT_ROWS / heads;
 }
 
+// pages: [num_pages, 2, nkv, page_size, d]. error_flag: one int in device-visible memory that a kernel with
+// bounded waits sets to 1 when a wait ran out (the host checks it after synchronising).
 LLMP_API int llmp_paged_attention(const void* q, long q_stride, void* out, long out_stride, const void* pages,
-                                  int dtype, const int* block_tables, int table_stride, const int* q_start,
-                                  const int* ctx_len, const int* tile_req, const int* tile_tok0, int num_tiles,
-                                  int nq, int nkv, int d, int page_size, int window, float scale,
-                                  int tokens_per_tile, cudaStream_t stream) {
+                                  int num_pages, int dtype, const int* block_tables, int table_stride,
+                                  const int* q_start, const int* ctx_len, const int* tile_req, const int* tile_tok0,
+                                  int num_tiles, int nq, int nkv, int d, int page_size, int window, float scale,
+                                  int tokens_per_tile, int* error_flag, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads cannot share %d key/value heads", nq, nkv);
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
-    LLMP_REQUIRE(page_size > 0, "attention: bad page size %d", page_size);
-    LLMP_REQUIRE(tokens_per_tile == llmp_attention_tokens_per_tile(nq, nkv, dtype, d),
+    LLMP_REQUIRE(page_size > 0 && num_pages > 0, "attention: bad page size %d or page count %d", page_size, num_pages);
+    LLMP_REQUIRE(tokens_per_tile == llmp_attention_tokens_per_tile(nq, nkv, dtype, d, page_size),
                  "attention: the tile list was built for %d tokens per tile, the kernel takes %d", tokens_per_tile,
-                 llmp_attention_tokens_per_tile(nq, nkv, dtype, d));
+                 llmp_attention_tokens_per_tile(nq, nkv, dtype, d, page_size));
+    if (dtype == LLMP_BF16 && llmp_prefill_tc_supports(nq, nkv, d, page_size))
+        return llmp_launch_prefill_tc(q, q_stride, out, out_stride, pages, num_pages, block_tables, table_stride, q_start,
+                                      ctx_len, tile_req, tile_tok0, num_tiles, nq, nkv, page_size, window, scale,
+                                      error_flag, stream);
     if (dtype == LLMP_BF16 && llmp_prefill_mma_supports(d))
         return llmp_launch_prefill_mma(q, q_stride, out, out_stride, pages, block_tables, table_stride, q_start, ctx_len,
                                        tile_req, tile_tok0, num_tiles, nq, nkv, d, page_size, window, scale, stream);

@@ -1,0 +1,421 @@
+// Causal attention of prompt portions over bfloat16 pages on the fifth-generation tensor cores, head size 128,
+// with the contract of llmp_paged_attention.
+//
+// A block takes 128 query rows of one request and one key/value head, a row being (token, query head of the
+// group) with the head running fastest, so that the K and V tiles it streams serve every query head that
+// shares the key/value head. Keys are walked in tiles of 128 aligned to key 0 (the same operations for a row
+// however the prompt was cut). Per key tile:
+//   S = Q K^T    one tcgen05.mma chain, Q and K in shared memory (128-byte swizzle, K-major), S in tensor memory
+//   softmax      thread r owns row r: it reads the 128 scores of its row from tensor memory, keeps the running
+//                maximum and sum in float32 and writes the probabilities back as bfloat16 over the first 64
+//                columns of S
+//   O += P V     one tcgen05.mma chain, P read from tensor memory as the A operand, V from shared memory as an
+//                MN-major B operand (the head dimension is contiguous in a page), O in tensor memory
+// The running maximum is only raised when a tile's maximum exceeds it by more than 8 (in log2 units): P then
+// stays below 2^8 and O needs rescaling in the first tiles only; the result is the same softmax. K and V pages
+// arrive by TMA, one box per page and half of the head (64 elements = one 128-byte swizzle span); a table
+// entry that is missing or released is read at an out-of-range page coordinate, which the TMA unit fills with
+// zeros. Two blocks share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one is in
+// its softmax the tensor cores work for the other.
+//
+// Every wait on an mbarrier is bounded: when one runs out the kernel records 1 in *error_flag and goes on
+// without waiting (its output is then wrong; the host reads the flag), so no thread is left behind at a
+// barrier and the tensor memory is always freed.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#define FA_ROWS 128
+#define FA_KEYS 128
+#define FA_D 128
+#define FA_THREADS 128
+#define FA_HALF_BYTES (FA_ROWS * 128)            // 128 rows of 128 bytes
+#define FA_TMEM_COLS 256                         // S (128 columns, P over its first 64) and O (128 columns)
+#define FA_RESCALE_STEP 8.0f
+
+struct FaParams {
+    const bf16* q;
+    bf16* out;
+    const int* block_tables;
+    const int* q_start;
+    const int* ctx_len;
+    const int* tile_req;
+    const int* tile_tok0;
+    long q_stride, out_stride;
+    int table_stride;
+    int nq, nkv, page_size, num_pages, window, tokens_per_cta;
+    float scale;
+    int* error_flag;
+};
+
+__device__ __forceinline__ void fa_tma_load_page(void* smem_dst, const CUtensorMap* map, int x, int kvh, int kv, int page,
+                                                 uint64_t* bar) {
+    const int zero = 0;
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(zero), "r"(kvh), "r"(kv), "r"(page)
+        : "memory");
+}
+
+// Shared-memory descriptor of an MN-major operand in the 128-byte swizzle: rows of 64 contiguous elements of
+// the MN dimension, one row per K index, groups of 8 K indices 1024 bytes apart (stride byte offset), the
+// next 64 elements of the MN dimension 16 KB further (leading byte offset).
+__device__ __forceinline__ uint64_t fa_desc_mn_major(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(FA_HALF_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (bfloat16 pairs per 32-bit column).
+__device__ __forceinline__ void fa_umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+
+// 32 consecutive 32-bit columns of this thread's tensor-memory lane into r[OFF .. OFF + 31] (no wait).
+#define FA_TMEM_LD32(taddr, r, OFF)                                                                                     \
+    asm volatile(                                                                                                       \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, " \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"                      \
+        : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),   \
+          "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]), \
+          "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]),                \
+          "=r"(r[OFF + 17]), "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]),                \
+          "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), "=r"(r[OFF + 24]), "=r"(r[OFF + 25]), "=r"(r[OFF + 26]),                \
+          "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]), "=r"(r[OFF + 30]), "=r"(r[OFF + 31])                 \
+        : "r"(taddr))
+
+// r[OFF .. OFF + 31] into 32 consecutive 32-bit columns of this thread's tensor-memory lane (no wait).
+#define FA_TMEM_ST32(taddr, r, OFF)                                                                                     \
+    asm volatile(                                                                                                       \
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, " \
+        "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};\n"                        \
+        ::"r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),          \
+          "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),        \
+          "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15]), "r"(r[OFF + 16]), "r"(r[OFF + 17]),    \
+          "r"(r[OFF + 18]), "r"(r[OFF + 19]), "r"(r[OFF + 20]), "r"(r[OFF + 21]), "r"(r[OFF + 22]), "r"(r[OFF + 23]),    \
+          "r"(r[OFF + 24]), "r"(r[OFF + 25]), "r"(r[OFF + 26]), "r"(r[OFF + 27]), "r"(r[OFF + 28]), "r"(r[OFF + 29]),    \
+          "r"(r[OFF + 30]), "r"(r[OFF + 31]), "r"(taddr)                                                                \
+        : "memory")
+
+__device__ __forceinline__ void fa_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void fa_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// 2^x by the special-function unit (relative error about 2^-22; the probabilities are rounded to bfloat16 anyway)
+__device__ __forceinline__ float fa_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 2)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const FaParams p) {
+    extern __shared__ unsigned char fa_raw[];
+    __shared__ __align__(8) uint64_t k_full, v_full, s_done, o_done;
+    __shared__ uint32_t tmem_slot;
+    // the swizzled tiles want 1024-byte alignment
+    const uint32_t raw_addr = tc_smem_u32(fa_raw);
+    unsigned char* Qs = fa_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);   // [2 halves][128 rows][128 bytes]
+    unsigned char* Ks = Qs + 2 * FA_HALF_BYTES;
+    unsigned char* Vs = Ks + 2 * FA_HALF_BYTES;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // later tiles of a prompt see more keys: start them first so that the long blocks do not form the tail
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int r = p.tile_req[tile];
+    const int tok0 = p.tile_tok0[tile];
+    const int kvh = blockIdx.y;
+    const int G = p.nq / p.nkv;
+    const int q_begin = p.q_start[r];
+    const int q_len = p.q_start[r + 1] - q_begin;
+    const int ctx = p.ctx_len[r];
+    const int pos0 = ctx - q_len;
+    int ntok = q_len - tok0;
+    if (ntok > p.tokens_per_cta) ntok = p.tokens_per_cta;
+    const int* table = p.block_tables + (size_t)r * p.table_stride;
+
+    if (tid == 0) {
+        mbar_init(&k_full, 1);
+        mbar_init(&v_full, 1);
+        mbar_init(&s_done, 1);
+        mbar_init(&o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+
+    // query rows into shared memory in the layout of a K-major operand: row = token * G + head, 16-byte chunk c
+    // of a row at chunk position (c % 8) ^ (row % 8) of the row's 128-byte line in half c / 8
+    for (int e = tid; e < FA_ROWS * 16; e += FA_THREADS) {
+        const int row = e >> 4, c = e & 15;
+        const int tl = row / G, h = row - tl * G;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (tl < ntok)
+            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + tok0 + tl) * p.q_stride + (size_t)(kvh * G + h) * FA_D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + (c >> 3) * FA_HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + FA_KEYS;
+    const uint32_t lane_field = (uint32_t)(warp * 32) << 16;           // this warp's quarter of the lanes
+
+    // keys this block needs: from the window start of its first token to the position of its last
+    const int hi = pos0 + tok0 + ntok - 1;                             // last key (inclusive)
+    int lo = 0;
+    if (p.window > 0) {
+        lo = pos0 + tok0 - p.window + 1;
+        if (lo < 0) lo = 0;
+    }
+    const int tile_lo = (lo / FA_KEYS) * FA_KEYS;
+    const int num_key_tiles = (hi - tile_lo) / FA_KEYS + 1;
+    const int pages_per_tile = FA_KEYS / p.page_size;
+
+    // warp 0: the boxes of one K or V tile (kv = 0 or 1), one lane per (page, half of the head)
+    auto issue_loads = [&](int j0, int kv, unsigned char* dst, uint64_t* bar) {
+        if (lane == 0) mbar_expect_tx(bar, 2 * FA_HALF_BYTES);
+        __syncwarp();
+        for (int op = lane; op < pages_per_tile * 2; op += 32) {
+            const int pg = op >> 1, half = op & 1;
+            const int j = j0 + pg * p.page_size;
+            int page = p.num_pages;                                    // out of range: the box arrives as zeros
+            if (j <= hi) {
+                const int entry = table[j / p.page_size];
+                if (entry >= 0) page = entry;
+            }
+            fa_tma_load_page(dst + half * FA_HALF_BYTES + pg * p.page_size * 128, &map_pages, half * 64, kvh, kv, page, bar);
+        }
+    };
+    if (warp == 0) {
+        issue_loads(tile_lo, 0, Ks, &k_full);
+        issue_loads(tile_lo, 1, Vs, &v_full);
+    }
+
+    // this thread's row
+    const int my_tl = tid / G;
+    const int my_head = tid - my_tl * G;
+    const int my_pos = my_tl < ntok ? pos0 + tok0 + my_tl : -1;       // -1: the row does not exist
+    const int first_pos = pos0 + tok0;                                 // lowest position among the block's rows
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    float m_used = -INFINITY, l_run = 0.f;
+    constexpr uint32_t idesc_s = umma_idesc(FA_ROWS, FA_KEYS);
+    constexpr uint32_t idesc_o = umma_idesc(FA_ROWS, FA_D) | (1u << 16);     // B is MN-major
+    const uint32_t q_addr = tc_smem_u32(Qs), k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
+
+    for (int j = 0; j < num_key_tiles; ++j) {
+        const int j0 = tile_lo + j * FA_KEYS;
+        const uint32_t parity = (uint32_t)(j & 1);
+        if (warp == 0) {
+            if (lane == 0) {
+                mbar_wait(&k_full, parity, p.error_flag);
+                fa_fence_after();
+#pragma unroll
+                for (int k = 0; k < FA_D / 16; ++k) {
+                    const uint32_t off = (uint32_t)(k >> 2) * FA_HALF_BYTES + (uint32_t)(k & 3) * 32;
+                    umma_f16(tmem_s, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, k != 0 ? 1u : 0u);
+                }
+                umma_commit(&s_done);
+            }
+            __syncwarp();
+        }
+        mbar_wait(&s_done, parity, p.error_flag);
+        fa_fence_after();
+        if (warp == 0 && j + 1 < num_key_tiles) issue_loads(j0 + FA_KEYS, 0, Ks, &k_full);   // S is done: K is free
+
+        // ---- softmax of this thread's row ----
+        uint32_t sr[FA_KEYS];
+        FA_TMEM_LD32(tmem_s + lane_field + 0, sr, 0);
+        FA_TMEM_LD32(tmem_s + lane_field + 32, sr, 32);
+        FA_TMEM_LD32(tmem_s + lane_field + 64, sr, 64);
+        FA_TMEM_LD32(tmem_s + lane_field + 96, sr, 96);
+        fa_tmem_wait_ld();
+        const bool need_mask = (j0 + FA_KEYS - 1 > first_pos) || (p.window > 0 && j0 < hi - p.window + 1);
+        if (need_mask) {
+            int first_ok = 0;
+            if (p.window > 0) first_ok = my_pos - p.window + 1;
+#pragma unroll
+            for (int i = 0; i < FA_KEYS; ++i) {
+                const int key = j0 + i;
+                if (key > my_pos || key < first_ok) sr[i] = 0xff800000u;           // -inf
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < FA_KEYS; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+        const float m_tile = mx * scale_log2;
+        const bool raise = m_tile > m_used + FA_RESCALE_STEP;
+        if (__any_sync(0xffffffffu, raise)) {
+            const float alpha = raise ? fa_ex2(m_used - m_tile) : 1.f;
+            if (raise) m_used = m_tile;
+            l_run *= alpha;
+            if (j > 0) {                                               // O holds the sum of the tiles before
+#pragma unroll
+                for (int c = 0; c < FA_D; c += 32) {
+                    uint32_t orow[32];
+                    FA_TMEM_LD32(tmem_o + lane_field + c, orow, 0);
+                    fa_tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                    FA_TMEM_ST32(tmem_o + lane_field + c, orow, 0);
+                }
+            }
+        }
+        const float m_eff = m_used > -INFINITY ? m_used : 0.f;        // a row without any key keeps p = 2^(-inf) = 0
+        float sum = 0.f;
+        uint32_t pk[FA_KEYS / 2];
+#pragma unroll
+        for (int i = 0; i < FA_KEYS; i += 2) {
+            const float p0 = fa_ex2(fmaf(__uint_as_float(sr[i]), scale_log2, -m_eff));
+            const float p1 = fa_ex2(fmaf(__uint_as_float(sr[i + 1]), scale_log2, -m_eff));
+            sum += p0 + p1;
+            pk[i >> 1] = fa_pack(p0, p1);
+        }
+        l_run += sum;
+        FA_TMEM_ST32(tmem_s + lane_field + 0, pk, 0);
+        FA_TMEM_ST32(tmem_s + lane_field + 32, pk, 32);
+        fa_tmem_wait_st();
+        fa_fence_before();
+        __syncthreads();
+
+        if (warp == 0) {
+            if (lane == 0) {
+                fa_fence_after();
+                mbar_wait(&v_full, parity, p.error_flag);
+                fa_fence_after();
+#pragma unroll
+                for (int k = 0; k < FA_KEYS / 16; ++k)                  // 16 keys per MMA: 8 columns of P, 2 KB of V
+                    fa_umma_a_tmem(tmem_o, tmem_s + (uint32_t)k * 8, fa_desc_mn_major(v_addr + (uint32_t)k * 2048), idesc_o,
+                                   (j | k) != 0 ? 1u : 0u);
+                umma_commit(&o_done);
+                mbar_wait(&o_done, parity, p.error_flag);               // P, V and O are free again
+            }
+            __syncwarp();
+            if (j + 1 < num_key_tiles) issue_loads(j0 + FA_KEYS, 1, Vs, &v_full);
+        }
+    }
+
+    // O is complete when thread 0 has seen the last o_done
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    bf16* dst = p.out + (size_t)(q_begin + tok0 + (my_pos >= 0 ? my_tl : 0)) * p.out_stride + (size_t)(kvh * G + my_head) * FA_D;
+#pragma unroll
+    for (int c = 0; c < FA_D; c += 32) {
+        uint32_t orow[32];
+        FA_TMEM_LD32(tmem_o + lane_field + c, orow, 0);
+        fa_tmem_wait_ld();
+        if (my_pos >= 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 pack;
+                pack.x = fa_pack(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
+                pack.y = fa_pack(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                pack.z = fa_pack(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
+                pack.w = fa_pack(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + c + i) = pack;
+            }
+        }
+    }
+    fa_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fa_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(FA_TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+struct PagesKey {
+    const void* ptr;
+    int nkv, page_size, num_pages;
+    bool operator==(const PagesKey& o) const {
+        return ptr == o.ptr && nkv == o.nkv && page_size == o.page_size && num_pages == o.num_pages;
+    }
+};
+struct PagesKeyHash {
+    size_t operator()(const PagesKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.nkv;
+        h = h * 1000003u ^ (size_t)k.page_size;
+        return h * 1000003u ^ (size_t)k.num_pages;
+    }
+};
+
+// Pages [num_pages, 2, nkv, page_size, 128] of bfloat16, read in boxes of one page of one head and 64 elements.
+static int pages_map(const void* pages, int nkv, int page_size, int num_pages, CUtensorMap* out) {
+    static std::unordered_map<PagesKey, CUtensorMap, PagesKeyHash> cache;
+    static std::mutex lock;
+    const PagesKey key{pages, nkv, page_size, num_pages};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = llmp_tensor_map_encoder();
+    LLMP_REQUIRE(fn != nullptr, "attention: the driver does not provide cuTensorMapEncodeTiled");
+    const cuuint64_t row = FA_D * sizeof(bf16);
+    const cuuint64_t dims[5] = {FA_D, (cuuint64_t)page_size, (cuuint64_t)nkv, 2, (cuuint64_t)num_pages};
+    const cuuint64_t strides[4] = {row, row * page_size, row * page_size * nkv, row * page_size * nkv * 2};
+    const cuuint32_t box[5] = {64, (cuuint32_t)page_size, 1, 1, 1};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(pages), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    LLMP_REQUIRE(rc == CUDA_SUCCESS, "attention: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    if (cache.size() > 1024) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+// Sizes this kernel takes: head size 128, pages of 8, 16, 32, 64 or 128 tokens, groups of up to 128 query heads.
+bool llmp_prefill_tc_supports(int nq, int nkv, int d, int page_size) {
+    if (d != FA_D || nkv <= 0 || nq % nkv != 0 || nq / nkv > FA_ROWS) return false;
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+}
+
+// Query tokens per block for a group size: 128 rows of (token, head).
+int llmp_prefill_tc_tokens_per_tile(int nq, int nkv) { return FA_ROWS / (nq / nkv); }
+
+int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
+                           const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
+                           const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int page_size,
+                           int window, float scale, int* error_flag, cudaStream_t stream) {
+    LLMP_REQUIRE(error_flag != nullptr, "attention: an error flag in device memory is required");
+    LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 8) == 0 && ((size_t)q % 16) == 0 && ((size_t)out % 16) == 0 &&
+                 ((size_t)pages % 16) == 0, "attention: rows must be 16-byte aligned");
+    LLMP_REQUIRE(nkv <= 65535, "attention: too many heads");
+    CUtensorMap map;
+    if (pages_map(pages, nkv, page_size, num_pages, &map)) return 1;
+    FaParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len;
+    p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.q_stride = q_stride; p.out_stride = out_stride;
+    p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages;
+    p.window = window; p.tokens_per_cta = llmp_prefill_tc_tokens_per_tile(nq, nkv); p.scale = scale;
+    p.error_flag = error_flag;
+    const size_t smem = 6 * (size_t)FA_HALF_BYTES + 1024;
+    LLMP_ALLOW_SMEM(prefill_attention_tc_kernel, smem);
+    dim3 grid(num_tiles, nkv);
+    prefill_attention_tc_kernel<<<grid, FA_THREADS, smem, stream>>>(map, p);
+    return llmp_check_launch("prefill_attention_tc");
+}

@@ -20,6 +20,7 @@ import torch
 from ..cache import CacheManager
 from ..config import ModelConfig, load_config
 from ..models import Model, build_model, load_model
+from ..ops import kernels
 from ..sampling import Sampler, SamplingConfig
 from .runner import ModelRunner, StepEntry
 from .scheduler import Request, Scheduler, StepPlan
@@ -113,6 +114,7 @@ class GenerationEngine:
                 [e.request.output if e.request.sampling.repetition_penalty != 1.0 else None for e in due])
             for e, token in zip(due, tokens.tolist()):
                 sampled[e.request.req_id] = token
+            kernels.check_error_flag()                  # after the copy above: the step's kernels have run
         self.steps += 1
         for e in plan.entries:
             if e.count == 1 and e.request.output:

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "llmp_gemm_simt": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
-    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -96,12 +96,13 @@ def _i32(t: torch.Tensor, name: str) -> None:
 
 
 def tokens_per_attention_tile(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32,
-                              head_dim: int = 0) -> int:
-    """Query tokens per tile of the general attention kernel that serves this type and head size."""
+                              head_dim: int = 0, page_size: int = 0) -> int:
+    """Query tokens per tile of the general attention kernel that serves this type, head size and page
+    size (0: not known, which rules out the kernels that depend on the page size)."""
     fn = library().llmp_attention_tokens_per_tile
-    fn.argtypes = [_I, _I, _I, _I]
+    fn.argtypes = [_I, _I, _I, _I, _I]
     fn.restype = _I
-    n = fn(num_heads, num_kv_heads, dtype_code(dtype), head_dim)
+    n = fn(num_heads, num_kv_heads, dtype_code(dtype), head_dim, page_size)
     _need(n > 0, f"{num_heads} query heads cannot share {num_kv_heads} key/value heads")
     return n
 
@@ -268,10 +269,10 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: to
     _need(out.is_contiguous() and out.shape[1] == num_heads * head_dim, "attention output must be [tokens, heads * head_dim]")
     _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (2, num_kv_heads, page_size, head_dim),
           "pages have the wrong layout")
-    _call("llmp_paged_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages),
+    _call("llmp_paged_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), pages.shape[0],
           dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(q_start), _ptr(ctx_len),
           _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), num_heads, num_kv_heads, head_dim, page_size,
-          int(window), float(scale), int(tokens_per_tile), _stream())
+          int(window), float(scale), int(tokens_per_tile), error_flag().data_ptr(), _stream())
     return out
 
 

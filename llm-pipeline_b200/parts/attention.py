@@ -90,10 +90,10 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache):
         if cache.pages is None or cache.group is None:
             raise RuntimeError("the attention mixer needs the pages of its cache")
+        page_size = cache.pages.shape[3]
         if self.tokens_per_tile is None:
             self.tokens_per_tile = kernels.tokens_per_attention_tile(self.num_heads, self.num_kv_heads, x.dtype,
-                                                                     self.head_dim)
-        page_size = cache.pages.shape[3]
+                                                                     self.head_dim, page_size)
         qkv = linear(x, self.w_qkv)
         cos = sin = None
         if self.rotary_dim:

@@ -43,7 +43,7 @@ def main(argv: Optional[Sequence[str]] = None, stdin=None, stdout=None) -> int:
     from .cache import CacheManager
     from .engine import ModelRunner, StepEntry
     from .models import load_model
-    from .ops import build_library
+    from .ops import build_library, kernels
 
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device is visible; this engine has no CPU path", file=sys.stderr)
@@ -73,6 +73,7 @@ def main(argv: Optional[Sequence[str]] = None, stdin=None, stdout=None) -> int:
                 os.path.join(args.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize(model.device)
+        kernels.check_error_flag()                      # a kernel whose bounded wait ran out leaves no valid logits
         for req_id in record.get("end", []):
             runner.release(req_id)
         print(f"done {step}", file=stdout, flush=True)

@@ -238,7 +238,7 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
         vs.append(v)
         q_start.append(q_start[-1] + T)
         ctx.append(S)
-    tpt = k_.tokens_per_attention_tile(nq, nkv, dtype, d)
+    tpt = k_.tokens_per_attention_tile(nq, nkv, dtype, d, page_size)
     tile_req, tile_tok0 = [], []
     for r, (_, T) in enumerate(requests):
         for t0 in range(0, T, tpt):
@@ -294,6 +294,32 @@ def test_paged_attention_finds_one_far_key_among_hundreds(dtype):
         got, want = run_paged(dtype, 8, 2, 64, 16, [(699, 1), (40, 8)], seed=4, boost=(0, key_pos, 5))
         assert torch.allclose(got, want, atol=tol(dtype, 3e-5, 3e-2)), key_pos
         assert float(want[0, 5].abs().max()) > 0.5      # the boosted key dominates: its value shows in the output
+
+
+@pytest.mark.parametrize("nq,nkv,page", [(32, 8, 16), (4, 4, 8), (6, 2, 32), (7, 1, 64), (16, 1, 128), (12, 3, 16)])
+def test_prefill_attention_head_size_128_tensor_memory_kernel(nq, nkv, page):
+    """Head size 128 in bfloat16 takes the tcgen05 kernel: portions that cross several 128-key tiles, a
+    portion that starts in the middle of a tile, single tokens, and a prompt shorter than one tile."""
+    dtype = torch.bfloat16
+    assert K().tokens_per_attention_tile(nq, nkv, dtype, 128, page) == 128 // (nq // nkv)
+    requests = [(0, 300), (515, 130), (127, 2), (128, 1), (0, 1), (250, 7), (0, 129)]
+    got, want = run_paged(dtype, nq, nkv, 128, page, requests, seed=11)
+    assert torch.allclose(got, want, atol=2e-2)
+    got_w, want_w = run_paged(dtype, nq, nkv, 128, page, requests, window=200, seed=12)
+    assert torch.allclose(got_w, want_w, atol=2e-2)
+    K().check_error_flag()
+
+
+def test_prefill_attention_head_size_128_finds_one_far_key():
+    for key_pos in (3, 127, 128, 511, 698):
+        got, want = run_paged(torch.bfloat16, 8, 2, 128, 16, [(600, 100), (40, 8)], seed=4, boost=(0, key_pos, 5))
+        assert torch.allclose(got, want, atol=3e-2), key_pos
+        assert float(want[99, 5].abs().max()) > 0.5
+    for window, offset in ((1, 0), (33, 0), (33, 1), (128, 0), (128, 1), (300, 1)):
+        P, T = 450, 70
+        key_pos = P + T - window - offset                   # offset 0: the oldest key inside; 1: the first outside
+        got, want = run_paged(torch.bfloat16, 8, 2, 128, 16, [(P, T), (20, 5)], window=window, seed=5, boost=(0, key_pos, 1))
+        assert torch.allclose(got, want, atol=3e-2), (window, offset)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
