@@ -12,11 +12,14 @@
 //   O += P V     one tcgen05.mma chain, P read from tensor memory as the A operand, V from shared memory as an
 //                MN-major B operand (the head dimension is contiguous in a page), O in tensor memory
 // The running maximum is only raised when a tile's maximum exceeds it by more than 8 (in log2 units): P then
-// stays below 2^8 and O needs rescaling in the first tiles only; the result is the same softmax. K and V pages
-// arrive by TMA, one box per page and half of the head (64 elements = one 128-byte swizzle span); a table
-// entry that is missing or released is read at an out-of-range page coordinate, which the TMA unit fills with
-// zeros. Two blocks share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one is in
-// its softmax the tensor cores work for the other.
+// stays below 2^8 and O needs rescaling in the first tiles only; the result is the same softmax. The softmax
+// reads its row twice from tensor memory, 32 columns at a time with the next 32 in flight (once for the
+// maximum, once for the probabilities), which keeps it within 168 registers. K and V pages arrive by TMA, one
+// box per page and half of the head (64 elements = one 128-byte swizzle span); a table entry that is missing
+// or released is read at an out-of-range page coordinate, which the TMA unit fills with zeros.
+// Roles: warps 0-3 softmax, warp 4 issues the loads (K of the next tile as soon as S is done, V as soon as
+// P V is done), one thread of warp 5 issues the MMAs. Two blocks share an SM (96 KB of shared memory and 256
+// tensor-memory columns each): while one is in its softmax the tensor cores work for the other.
 //
 // Every wait on an mbarrier is bounded: when one runs out the kernel records 1 in *error_flag and goes on
 // without waiting (its output is then wrong; the host reads the flag), so no thread is left behind at a
@@ -32,7 +35,7 @@
 #define FA_ROWS 128
 #define FA_KEYS 128
 #define FA_D 128
-#define FA_THREADS 128
+#define FA_THREADS 192                           // four softmax warps, one load warp, one MMA warp
 #define FA_HALF_BYTES (FA_ROWS * 128)            // 128 rows of 128 bytes
 #define FA_TMEM_COLS 256                         // S (128 columns, P over its first 64) and O (128 columns)
 #define FA_RESCALE_STEP 8.0f
@@ -123,10 +126,54 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// Applies the causal and window mask of one row to 32 scores that start at key `key0`.
+__device__ __forceinline__ void fa_mask32(uint32_t (&v)[32], int key0, int last_ok, int first_ok) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int key = key0 + i;
+        if (key > last_ok || key < first_ok) v[i] = 0xff800000u;           // -inf
+    }
+}
+
+__device__ __forceinline__ float fa_max32(const uint32_t (&v)[32], float mx) {
+    float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;          // four chains: no serial dependency
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        m0 = fmaxf(m0, __uint_as_float(v[i]));
+        m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+        m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+        m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// 32 scores -> 16 packed bfloat16 pairs of 2^(s * scale - m); returns their float32 sum.
+__device__ __forceinline__ float fa_exp32(const uint32_t (&v)[32], uint32_t (&pk)[16], float scale_log2, float m_eff) {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        const float p0 = fa_ex2(fmaf(__uint_as_float(v[i]), scale_log2, -m_eff));
+        const float p1 = fa_ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_eff));
+        s0 += p0;
+        s1 += p1;
+        pk[i >> 1] = fa_pack(p0, p1);
+    }
+    return s0 + s1;
+}
+
+#define FA_TMEM_ST16(taddr, r)                                                                                          \
+    asm volatile(                                                                                                       \
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, " \
+        "%15};\n"                                                                                                        \
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),  \
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)                            \
+        : "memory")
+
+// Warps 0-3: softmax (thread r owns row r and tensor-memory lane r). Warp 4: TMA loads. Warp 5: MMA issue.
 __global__ void __launch_bounds__(FA_THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const FaParams p) {
     extern __shared__ unsigned char fa_raw[];
-    __shared__ __align__(8) uint64_t k_full, v_full, s_done, o_done;
+    __shared__ __align__(8) uint64_t k_full, v_full, s_done, o_done, p_ready;
     __shared__ uint32_t tmem_slot;
     // the swizzled tiles want 1024-byte alignment
     const uint32_t raw_addr = tc_smem_u32(fa_raw);
@@ -154,9 +201,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
         mbar_init(&v_full, 1);
         mbar_init(&s_done, 1);
         mbar_init(&o_done, 1);
+        mbar_init(&p_ready, FA_ROWS);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -177,7 +225,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     fa_fence_after();
     const uint32_t tmem_base = tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + FA_KEYS;
-    const uint32_t lane_field = (uint32_t)(warp * 32) << 16;           // this warp's quarter of the lanes
 
     // keys this block needs: from the window start of its first token to the position of its last
     const int hi = pos0 + tok0 + ntok - 1;                             // last key (inclusive)
@@ -188,44 +235,47 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     }
     const int tile_lo = (lo / FA_KEYS) * FA_KEYS;
     const int num_key_tiles = (hi - tile_lo) / FA_KEYS + 1;
-    const int pages_per_tile = FA_KEYS / p.page_size;
 
-    // warp 0: the boxes of one K or V tile (kv = 0 or 1), one lane per (page, half of the head)
-    auto issue_loads = [&](int j0, int kv, unsigned char* dst, uint64_t* bar) {
-        if (lane == 0) mbar_expect_tx(bar, 2 * FA_HALF_BYTES);
-        __syncwarp();
-        for (int op = lane; op < pages_per_tile * 2; op += 32) {
-            const int pg = op >> 1, half = op & 1;
-            const int j = j0 + pg * p.page_size;
-            int page = p.num_pages;                                    // out of range: the box arrives as zeros
-            if (j <= hi) {
-                const int entry = table[j / p.page_size];
-                if (entry >= 0) page = entry;
+    if (warp == 4) {
+        // ---- loads: one lane per (page, half of the head) of a K or V tile ----
+        const int pages_per_tile = FA_KEYS / p.page_size;
+        for (int j = 0; j < num_key_tiles; ++j) {
+            const int j0 = tile_lo + j * FA_KEYS;
+            int page[2];                                               // this lane's boxes: ops lane and lane + 32
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+                const int key = j0 + ((lane + 32 * o) >> 1) * p.page_size;
+                page[o] = p.num_pages;                                 // out of range: the box arrives as zeros
+                if (lane + 32 * o < pages_per_tile * 2 && key <= hi) {
+                    const int entry = table[key / p.page_size];
+                    if (entry >= 0) page[o] = entry;
+                }
             }
-            fa_tma_load_page(dst + half * FA_HALF_BYTES + pg * p.page_size * 128, &map_pages, half * 64, kvh, kv, page, bar);
+#pragma unroll
+            for (int kv = 0; kv < 2; ++kv) {
+                // K is free when S of the tile before is done, V when its P V is done
+                if (j > 0) mbar_wait(kv == 0 ? &s_done : &o_done, (uint32_t)((j - 1) & 1), p.error_flag);
+                uint64_t* bar = kv == 0 ? &k_full : &v_full;
+                unsigned char* dst = kv == 0 ? Ks : Vs;
+                if (lane == 0) mbar_expect_tx(bar, 2 * FA_HALF_BYTES);
+                __syncwarp();
+#pragma unroll
+                for (int o = 0; o < 2; ++o) {
+                    const int op = lane + 32 * o;
+                    if (op < pages_per_tile * 2)
+                        fa_tma_load_page(dst + (op & 1) * FA_HALF_BYTES + (op >> 1) * p.page_size * 128, &map_pages, (op & 1) * 64,
+                                         kvh, kv, page[o], bar);
+                }
+            }
         }
-    };
-    if (warp == 0) {
-        issue_loads(tile_lo, 0, Ks, &k_full);
-        issue_loads(tile_lo, 1, Vs, &v_full);
-    }
-
-    // this thread's row
-    const int my_tl = tid / G;
-    const int my_head = tid - my_tl * G;
-    const int my_pos = my_tl < ntok ? pos0 + tok0 + my_tl : -1;       // -1: the row does not exist
-    const int first_pos = pos0 + tok0;                                 // lowest position among the block's rows
-    const float scale_log2 = p.scale * 1.4426950408889634f;
-    float m_used = -INFINITY, l_run = 0.f;
-    constexpr uint32_t idesc_s = umma_idesc(FA_ROWS, FA_KEYS);
-    constexpr uint32_t idesc_o = umma_idesc(FA_ROWS, FA_D) | (1u << 16);     // B is MN-major
-    const uint32_t q_addr = tc_smem_u32(Qs), k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
-
-    for (int j = 0; j < num_key_tiles; ++j) {
-        const int j0 = tile_lo + j * FA_KEYS;
-        const uint32_t parity = (uint32_t)(j & 1);
-        if (warp == 0) {
-            if (lane == 0) {
+    } else if (warp == 5) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(FA_ROWS, FA_KEYS);
+            constexpr uint32_t idesc_o = umma_idesc(FA_ROWS, FA_D) | (1u << 16);     // B is MN-major
+            const uint32_t q_addr = tc_smem_u32(Qs), k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
+            for (int j = 0; j < num_key_tiles; ++j) {
+                const uint32_t parity = (uint32_t)(j & 1);
                 mbar_wait(&k_full, parity, p.error_flag);
                 fa_fence_after();
 #pragma unroll
@@ -234,71 +284,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
                     umma_f16(tmem_s, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, k != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_done);
-            }
-            __syncwarp();
-        }
-        mbar_wait(&s_done, parity, p.error_flag);
-        fa_fence_after();
-        if (warp == 0 && j + 1 < num_key_tiles) issue_loads(j0 + FA_KEYS, 0, Ks, &k_full);   // S is done: K is free
-
-        // ---- softmax of this thread's row ----
-        uint32_t sr[FA_KEYS];
-        FA_TMEM_LD32(tmem_s + lane_field + 0, sr, 0);
-        FA_TMEM_LD32(tmem_s + lane_field + 32, sr, 32);
-        FA_TMEM_LD32(tmem_s + lane_field + 64, sr, 64);
-        FA_TMEM_LD32(tmem_s + lane_field + 96, sr, 96);
-        fa_tmem_wait_ld();
-        const bool need_mask = (j0 + FA_KEYS - 1 > first_pos) || (p.window > 0 && j0 < hi - p.window + 1);
-        if (need_mask) {
-            int first_ok = 0;
-            if (p.window > 0) first_ok = my_pos - p.window + 1;
-#pragma unroll
-            for (int i = 0; i < FA_KEYS; ++i) {
-                const int key = j0 + i;
-                if (key > my_pos || key < first_ok) sr[i] = 0xff800000u;           // -inf
-            }
-        }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < FA_KEYS; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
-        const float m_tile = mx * scale_log2;
-        const bool raise = m_tile > m_used + FA_RESCALE_STEP;
-        if (__any_sync(0xffffffffu, raise)) {
-            const float alpha = raise ? fa_ex2(m_used - m_tile) : 1.f;
-            if (raise) m_used = m_tile;
-            l_run *= alpha;
-            if (j > 0) {                                               // O holds the sum of the tiles before
-#pragma unroll
-                for (int c = 0; c < FA_D; c += 32) {
-                    uint32_t orow[32];
-                    FA_TMEM_LD32(tmem_o + lane_field + c, orow, 0);
-                    fa_tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                    FA_TMEM_ST32(tmem_o + lane_field + c, orow, 0);
-                }
-            }
-        }
-        const float m_eff = m_used > -INFINITY ? m_used : 0.f;        // a row without any key keeps p = 2^(-inf) = 0
-        float sum = 0.f;
-        uint32_t pk[FA_KEYS / 2];
-#pragma unroll
-        for (int i = 0; i < FA_KEYS; i += 2) {
-            const float p0 = fa_ex2(fmaf(__uint_as_float(sr[i]), scale_log2, -m_eff));
-            const float p1 = fa_ex2(fmaf(__uint_as_float(sr[i + 1]), scale_log2, -m_eff));
-            sum += p0 + p1;
-            pk[i >> 1] = fa_pack(p0, p1);
-        }
-        l_run += sum;
-        FA_TMEM_ST32(tmem_s + lane_field + 0, pk, 0);
-        FA_TMEM_ST32(tmem_s + lane_field + 32, pk, 32);
-        fa_tmem_wait_st();
-        fa_fence_before();
-        __syncthreads();
-
-        if (warp == 0) {
-            if (lane == 0) {
-                fa_fence_after();
+                mbar_wait(&p_ready, parity, p.error_flag);
                 mbar_wait(&v_full, parity, p.error_flag);
                 fa_fence_after();
 #pragma unroll
@@ -306,39 +292,117 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
                     fa_umma_a_tmem(tmem_o, tmem_s + (uint32_t)k * 8, fa_desc_mn_major(v_addr + (uint32_t)k * 2048), idesc_o,
                                    (j | k) != 0 ? 1u : 0u);
                 umma_commit(&o_done);
-                mbar_wait(&o_done, parity, p.error_flag);               // P, V and O are free again
             }
-            __syncwarp();
-            if (j + 1 < num_key_tiles) issue_loads(j0 + FA_KEYS, 1, Vs, &v_full);
         }
-    }
+    } else {
+        // ---- softmax: this thread's row ----
+        const uint32_t lane_field = (uint32_t)(warp * 32) << 16;      // this warp's quarter of the lanes
+        const int my_tl = tid / G;
+        const int my_head = tid - my_tl * G;
+        const int my_pos = my_tl < ntok ? pos0 + tok0 + my_tl : -1;   // -1: the row does not exist
+        const int first_ok = p.window > 0 ? my_pos - p.window + 1 : 0;
+        const int first_pos = pos0 + tok0;                             // lowest position among the block's rows
+        const float scale_log2 = p.scale * 1.4426950408889634f;
+        float m_used = -INFINITY, l_run = 0.f;
+        uint32_t a[32], b[32];
+        for (int j = 0; j < num_key_tiles; ++j) {
+            const int j0 = tile_lo + j * FA_KEYS;
+            const bool need_mask = (j0 + FA_KEYS - 1 > first_pos) || (p.window > 0 && j0 < hi - p.window + 1);
+            mbar_wait(&s_done, (uint32_t)(j & 1), p.error_flag);      // also: P V of the tile before is done
+            fa_fence_after();
+            // pass 1: the row's maximum; the load of the next 32 columns is in flight while 32 are reduced
+            float mx = -INFINITY;
+            FA_TMEM_LD32(tmem_s + lane_field + 0, a, 0);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 32, b, 0);
+            if (need_mask) fa_mask32(a, j0, my_pos, first_ok);
+            mx = fa_max32(a, mx);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 64, a, 0);
+            if (need_mask) fa_mask32(b, j0 + 32, my_pos, first_ok);
+            mx = fa_max32(b, mx);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 96, b, 0);
+            if (need_mask) fa_mask32(a, j0 + 64, my_pos, first_ok);
+            mx = fa_max32(a, mx);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 0, a, 0);               // first columns again, for pass 2
+            if (need_mask) fa_mask32(b, j0 + 96, my_pos, first_ok);
+            mx = fa_max32(b, mx);
 
-    // O is complete when thread 0 has seen the last o_done
-    fa_fence_before();
-    __syncthreads();
-    fa_fence_after();
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    bf16* dst = p.out + (size_t)(q_begin + tok0 + (my_pos >= 0 ? my_tl : 0)) * p.out_stride + (size_t)(kvh * G + my_head) * FA_D;
+            const float m_tile = mx * scale_log2;
+            const bool raise = m_tile > m_used + FA_RESCALE_STEP;
+            float alpha = 1.f;
+            if (raise) {
+                alpha = fa_ex2(m_used - m_tile);
+                m_used = m_tile;
+                l_run *= alpha;
+            }
+            fa_tmem_wait_ld();
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {             // O holds the sum of the tiles before
 #pragma unroll
-    for (int c = 0; c < FA_D; c += 32) {
-        uint32_t orow[32];
-        FA_TMEM_LD32(tmem_o + lane_field + c, orow, 0);
-        fa_tmem_wait_ld();
-        if (my_pos >= 0) {
+                for (int c = 0; c < FA_D; c += 32) {
+                    FA_TMEM_LD32(tmem_o + lane_field + c, b, 0);
+                    fa_tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-                uint4 pack;
-                pack.x = fa_pack(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
-                pack.y = fa_pack(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-                pack.z = fa_pack(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
-                pack.w = fa_pack(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
-                *reinterpret_cast<uint4*>(dst + c + i) = pack;
+                    for (int i = 0; i < 32; ++i) b[i] = __float_as_uint(__uint_as_float(b[i]) * alpha);
+                    FA_TMEM_ST32(tmem_o + lane_field + c, b, 0);
+                }
+            }
+            // pass 2: probabilities as bfloat16 pairs over the first 64 columns of S (16 columns per 32 scores:
+            // always columns that were read before)
+            const float m_eff = m_used > -INFINITY ? m_used : 0.f;    // a row without any key keeps p = 2^(-inf) = 0
+            uint32_t pk[16];
+            float sum = 0.f;
+            FA_TMEM_LD32(tmem_s + lane_field + 32, b, 0);
+            if (need_mask) fa_mask32(a, j0, my_pos, first_ok);
+            sum += fa_exp32(a, pk, scale_log2, m_eff);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 64, a, 0);
+            FA_TMEM_ST16(tmem_s + lane_field + 0, pk);
+            if (need_mask) fa_mask32(b, j0 + 32, my_pos, first_ok);
+            sum += fa_exp32(b, pk, scale_log2, m_eff);
+            fa_tmem_wait_ld();
+            FA_TMEM_LD32(tmem_s + lane_field + 96, b, 0);
+            FA_TMEM_ST16(tmem_s + lane_field + 16, pk);
+            if (need_mask) fa_mask32(a, j0 + 64, my_pos, first_ok);
+            sum += fa_exp32(a, pk, scale_log2, m_eff);
+            fa_tmem_wait_ld();
+            FA_TMEM_ST16(tmem_s + lane_field + 32, pk);
+            if (need_mask) fa_mask32(b, j0 + 96, my_pos, first_ok);
+            sum += fa_exp32(b, pk, scale_log2, m_eff);
+            FA_TMEM_ST16(tmem_s + lane_field + 48, pk);
+            l_run += sum;
+            fa_tmem_wait_st();
+            fa_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem_u32(&p_ready)) : "memory");
+        }
+
+        // O is complete when the last P V is done
+        mbar_wait(&o_done, (uint32_t)((num_key_tiles - 1) & 1), p.error_flag);
+        fa_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        bf16* dst = p.out + (size_t)(q_begin + tok0 + (my_pos >= 0 ? my_tl : 0)) * p.out_stride + (size_t)(kvh * G + my_head) * FA_D;
+#pragma unroll
+        for (int c = 0; c < FA_D; c += 32) {
+            FA_TMEM_LD32(tmem_o + lane_field + c, a, 0);
+            fa_tmem_wait_ld();
+            if (my_pos >= 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 pack;
+                    pack.x = fa_pack(__uint_as_float(a[i]) * inv, __uint_as_float(a[i + 1]) * inv);
+                    pack.y = fa_pack(__uint_as_float(a[i + 2]) * inv, __uint_as_float(a[i + 3]) * inv);
+                    pack.z = fa_pack(__uint_as_float(a[i + 4]) * inv, __uint_as_float(a[i + 5]) * inv);
+                    pack.w = fa_pack(__uint_as_float(a[i + 6]) * inv, __uint_as_float(a[i + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c + i) = pack;
+                }
             }
         }
     }
     fa_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 5) {
         fa_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(FA_TMEM_COLS) : "memory");
     }

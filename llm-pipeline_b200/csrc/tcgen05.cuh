@@ -28,7 +28,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(error_flag) != 0) return false;   // another role gave up
+        // another role gave up? (the flag lives in host memory: look rarely, a read takes microseconds)
+        if ((i & 0xFFFFu) == 0xFFFFu && *reinterpret_cast<volatile int*>(error_flag) != 0) return false;
     }
     *reinterpret_cast<volatile int*>(error_flag) = 1;
     return false;
