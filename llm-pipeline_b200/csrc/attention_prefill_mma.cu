@@ -26,7 +26,7 @@ struct PrefillParams {
     long q_stride, out_stride;
     int table_stride;
     int nq, nkv, d, page_size, window;
-    int heads_per_cta, tokens_per_cta, head_chunks;
+    int heads_per_cta, tokens_per_cta, head_chunks, num_tiles;
     float scale;
 };
 
@@ -80,11 +80,14 @@ __global__ void __launch_bounds__(PF_THREADS, 4) prefill_attention_mma_kernel(co
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // later tiles of a prompt see more keys: start them first so that the long blocks do not form the tail
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    // Later tiles of a prompt see more keys. Blocks start in the order of their index: every head of the last tile
+    // first, then those of the tile before, so that the long blocks do not form the tail.
+    const int per_tile = p.nkv * p.head_chunks;
+    const int tile = p.num_tiles - 1 - (int)(blockIdx.x / (unsigned)per_tile);
+    const int in_tile = (int)(blockIdx.x % (unsigned)per_tile);
     const int r = p.tile_req[tile];
     const int tok0 = p.tile_tok0[tile];
-    const int kvh = blockIdx.y / p.head_chunks, chunk = blockIdx.y % p.head_chunks;
+    const int kvh = in_tile / p.head_chunks, chunk = in_tile % p.head_chunks;
     const int G = p.nq / p.nkv;
     const int hpc = p.heads_per_cta;
     const int head0 = chunk * hpc;
@@ -304,10 +307,11 @@ int llmp_launch_prefill_mma(const void* q, long q_stride, void* out, long out_st
     p.heads_per_cta = G < 16 ? G : 16;
     p.tokens_per_cta = PF_ROWS / p.heads_per_cta;
     p.head_chunks = (G + p.heads_per_cta - 1) / p.heads_per_cta;
-    LLMP_REQUIRE((long)nkv * p.head_chunks <= 65535, "attention: too many heads");
+    p.num_tiles = num_tiles;
+    LLMP_REQUIRE((long)num_tiles * nkv * p.head_chunks < (1L << 31), "attention: too many tiles");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 2) == 0, "attention: query rows must be 16-byte aligned");
     const size_t smem = sizeof(bf16) * ((size_t)PF_ROWS * (d + 8) + (size_t)2 * PF_KEYS * (d + 8));
-    dim3 grid(num_tiles, nkv * p.head_chunks);
+    const unsigned grid = (unsigned)(num_tiles * nkv * p.head_chunks);
 #define PF_CASE(N)                                                               \
     case N:                                                                      \
         LLMP_ALLOW_SMEM(prefill_attention_mma_kernel<N>, smem);                   \

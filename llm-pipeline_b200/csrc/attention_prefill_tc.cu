@@ -39,6 +39,7 @@
 #define FA_HALF_BYTES (FA_ROWS * 128)            // 128 rows of 128 bytes
 #define FA_TMEM_COLS 256                         // S (128 columns, P over its first 64) and O (128 columns)
 #define FA_RESCALE_STEP 8.0f
+#define FA_STAGGER_NS 1000
 
 struct FaParams {
     const bf16* q;
@@ -50,7 +51,7 @@ struct FaParams {
     const int* tile_tok0;
     long q_stride, out_stride;
     int table_stride;
-    int nq, nkv, page_size, num_pages, window, tokens_per_cta;
+    int nq, nkv, page_size, num_pages, window, tokens_per_cta, num_sms, num_tiles;
     float scale;
     int* error_flag;
 };
@@ -182,11 +183,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     unsigned char* Vs = Ks + 2 * FA_HALF_BYTES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // later tiles of a prompt see more keys: start them first so that the long blocks do not form the tail
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    // Later tiles of a prompt see more keys. Blocks start in the order of their index: the key/value heads of the
+    // last tile first, then those of the tile before, so that the long blocks do not form the tail.
+    const int tile = p.num_tiles - 1 - (int)(blockIdx.x / (unsigned)p.nkv);
+    const int kvh = (int)(blockIdx.x % (unsigned)p.nkv);
     const int r = p.tile_req[tile];
     const int tok0 = p.tile_tok0[tile];
-    const int kvh = blockIdx.y;
     const int G = p.nq / p.nkv;
     const int q_begin = p.q_start[r];
     const int q_len = p.q_start[r + 1] - q_begin;
@@ -274,9 +276,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
             constexpr uint32_t idesc_s = umma_idesc(FA_ROWS, FA_KEYS);
             constexpr uint32_t idesc_o = umma_idesc(FA_ROWS, FA_D) | (1u << 16);     // B is MN-major
             const uint32_t q_addr = tc_smem_u32(Qs), k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
+            // The two blocks of an SM start together and would stay in step: both on the tensor cores, then both in
+            // their softmax. The second block of each SM starts half a tile later, so that one's MMAs run under the
+            // other's softmax.
+            if ((blockIdx.x / p.num_sms) & 1) __nanosleep(FA_STAGGER_NS);
             for (int j = 0; j < num_key_tiles; ++j) {
                 const uint32_t parity = (uint32_t)(j & 1);
-                mbar_wait(&k_full, parity, p.error_flag);
+                if (j == 0) mbar_wait(&k_full, 0, p.error_flag);       // later tiles: waited for below, ahead of time
                 fa_fence_after();
 #pragma unroll
                 for (int k = 0; k < FA_D / 16; ++k) {
@@ -284,8 +290,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
                     umma_f16(tmem_s, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, k != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_done);
-                mbar_wait(&p_ready, parity, p.error_flag);
+                // V of this tile and K of the next have long been asked for: take these waits while the softmax works
                 mbar_wait(&v_full, parity, p.error_flag);
+                if (j + 1 < num_key_tiles) mbar_wait(&k_full, parity ^ 1u, p.error_flag);
+                mbar_wait(&p_ready, parity, p.error_flag);
                 fa_fence_after();
 #pragma unroll
                 for (int k = 0; k < FA_KEYS / 16; ++k)                  // 16 keys per MMA: 8 columns of P, 2 KB of V
@@ -468,7 +476,6 @@ int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_str
     LLMP_REQUIRE(error_flag != nullptr, "attention: an error flag in device memory is required");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 8) == 0 && ((size_t)q % 16) == 0 && ((size_t)out % 16) == 0 &&
                  ((size_t)pages % 16) == 0, "attention: rows must be 16-byte aligned");
-    LLMP_REQUIRE(nkv <= 65535, "attention: too many heads");
     CUtensorMap map;
     if (pages_map(pages, nkv, page_size, num_pages, &map)) return 1;
     FaParams p;
@@ -477,9 +484,18 @@ int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_str
     p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.tokens_per_cta = llmp_prefill_tc_tokens_per_tile(nq, nkv); p.scale = scale;
     p.error_flag = error_flag;
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    p.num_sms = sms;
+    p.num_tiles = num_tiles;
     const size_t smem = 6 * (size_t)FA_HALF_BYTES + 1024;
     LLMP_ALLOW_SMEM(prefill_attention_tc_kernel, smem);
-    dim3 grid(num_tiles, nkv);
-    prefill_attention_tc_kernel<<<grid, FA_THREADS, smem, stream>>>(map, p);
+    LLMP_REQUIRE((long)num_tiles * nkv < (1L << 31), "attention: too many tiles");
+    prefill_attention_tc_kernel<<<(unsigned)(num_tiles * nkv), FA_THREADS, smem, stream>>>(map, p);
     return llmp_check_launch("prefill_attention_tc");
 }

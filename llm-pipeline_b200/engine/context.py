@@ -45,11 +45,15 @@ class StepContext:
         ``tokens_per_tile`` consecutive new tokens of a request."""
         tiles = self._tiles.get(tokens_per_tile)
         if tiles is None:
-            req, tok0 = [], []
+            # in the order of the keys they see: the kernels start the last tile first, the longest blocks lead
+            found = []
             for r, n in enumerate(self.q_lens):
+                before = self.starts[r]
                 for t in range(0, n, tokens_per_tile):
-                    req.append(r)
-                    tok0.append(t)
+                    found.append((before + min(t + tokens_per_tile, n), r, t))
+            found.sort()
+            req = [f[1] for f in found]
+            tok0 = [f[2] for f in found]
             host = torch.tensor([req, tok0], dtype=torch.int32).pin_memory()
             dev = host.to(self.device, non_blocking=True)
             tiles = (dev[0].contiguous(), dev[1].contiguous())
