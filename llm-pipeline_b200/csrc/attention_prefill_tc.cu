@@ -198,36 +198,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     if (ntok > p.tokens_per_cta) ntok = p.tokens_per_cta;
     const int* table = p.block_tables + (size_t)r * p.table_stride;
 
-    if (tid == 0) {
-        mbar_init(&k_full, 1);
-        mbar_init(&v_full, 1);
-        mbar_init(&s_done, 1);
-        mbar_init(&o_done, 1);
-        mbar_init(&p_ready, FA_ROWS);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-
-    // query rows into shared memory in the layout of a K-major operand: row = token * G + head, 16-byte chunk c
-    // of a row at chunk position (c % 8) ^ (row % 8) of the row's 128-byte line in half c / 8
-    for (int e = tid; e < FA_ROWS * 16; e += FA_THREADS) {
-        const int row = e >> 4, c = e & 15;
-        const int tl = row / G, h = row - tl * G;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (tl < ntok)
-            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + tok0 + tl) * p.q_stride + (size_t)(kvh * G + h) * FA_D + c * 8);
-        *reinterpret_cast<uint4*>(Qs + (c >> 3) * FA_HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
-    }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    fa_fence_before();
-    __syncthreads();
-    fa_fence_after();
-    const uint32_t tmem_base = tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + FA_KEYS;
-
     // keys this block needs: from the window start of its first token to the position of its last
     const int hi = pos0 + tok0 + ntok - 1;                             // last key (inclusive)
     int lo = 0;
@@ -237,39 +207,87 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     }
     const int tile_lo = (lo / FA_KEYS) * FA_KEYS;
     const int num_key_tiles = (hi - tile_lo) / FA_KEYS + 1;
+    const int pages_per_tile = FA_KEYS / p.page_size;
 
-    if (warp == 4) {
-        // ---- loads: one lane per (page, half of the head) of a K or V tile ----
-        const int pages_per_tile = FA_KEYS / p.page_size;
-        for (int j = 0; j < num_key_tiles; ++j) {
-            const int j0 = tile_lo + j * FA_KEYS;
-            int page[2];                                               // this lane's boxes: ops lane and lane + 32
+    // warp 4: the boxes of the K and V tile j, one lane per (page, half of the head)
+    auto load_tile = [&](int j) {
+        const int j0 = tile_lo + j * FA_KEYS;
+        int page[2];                                                   // this lane's boxes: ops lane and lane + 32
 #pragma unroll
-            for (int o = 0; o < 2; ++o) {
-                const int key = j0 + ((lane + 32 * o) >> 1) * p.page_size;
-                page[o] = p.num_pages;                                 // out of range: the box arrives as zeros
-                if (lane + 32 * o < pages_per_tile * 2 && key <= hi) {
-                    const int entry = table[key / p.page_size];
-                    if (entry >= 0) page[o] = entry;
-                }
-            }
-#pragma unroll
-            for (int kv = 0; kv < 2; ++kv) {
-                // K is free when S of the tile before is done, V when its P V is done
-                if (j > 0) mbar_wait(kv == 0 ? &s_done : &o_done, (uint32_t)((j - 1) & 1), p.error_flag);
-                uint64_t* bar = kv == 0 ? &k_full : &v_full;
-                unsigned char* dst = kv == 0 ? Ks : Vs;
-                if (lane == 0) mbar_expect_tx(bar, 2 * FA_HALF_BYTES);
-                __syncwarp();
-#pragma unroll
-                for (int o = 0; o < 2; ++o) {
-                    const int op = lane + 32 * o;
-                    if (op < pages_per_tile * 2)
-                        fa_tma_load_page(dst + (op & 1) * FA_HALF_BYTES + (op >> 1) * p.page_size * 128, &map_pages, (op & 1) * 64,
-                                         kvh, kv, page[o], bar);
-                }
+        for (int o = 0; o < 2; ++o) {
+            const int key = j0 + ((lane + 32 * o) >> 1) * p.page_size;
+            page[o] = p.num_pages;                                     // out of range: the box arrives as zeros
+            if (lane + 32 * o < pages_per_tile * 2 && key <= hi) {
+                const int entry = table[key / p.page_size];
+                if (entry >= 0) page[o] = entry;
             }
         }
+#pragma unroll
+        for (int kv = 0; kv < 2; ++kv) {
+            // K is free when S of the tile before is done, V when its P V is done
+            if (j > 0) mbar_wait(kv == 0 ? &s_done : &o_done, (uint32_t)((j - 1) & 1), p.error_flag);
+            uint64_t* bar = kv == 0 ? &k_full : &v_full;
+            unsigned char* dst = kv == 0 ? Ks : Vs;
+            if (lane == 0) mbar_expect_tx(bar, 2 * FA_HALF_BYTES);
+            __syncwarp();
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+                const int op = lane + 32 * o;
+                if (op < pages_per_tile * 2)
+                    fa_tma_load_page(dst + (op & 1) * FA_HALF_BYTES + (op >> 1) * p.page_size * 128, &map_pages, (op & 1) * 64,
+                                     kvh, kv, page[o], bar);
+            }
+        }
+    };
+
+    if (warp == 4) {
+        // the barriers, and at once the first K and V tiles: they need nothing but the block table
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_pages) : "memory");
+            mbar_init(&k_full, 1);
+            mbar_init(&v_full, 1);
+            mbar_init(&s_done, 1);
+            mbar_init(&o_done, 1);
+            mbar_init(&p_ready, FA_ROWS);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncwarp();
+        load_tile(0);
+    } else if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    } else {
+        // Query rows into shared memory in the layout of a K-major operand: row = token * G + head, 16-byte chunk
+        // c of a row at chunk position (c % 8) ^ (row % 8) of the row's 128-byte line in half c / 8. All loads of
+        // a thread are in flight before its first store.
+        constexpr int PER_THREAD = FA_ROWS * 16 / 128;
+        uint4 v[PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int e = tid + i * 128;
+            const int row = e >> 4, c = e & 15;
+            const int tl = row / G, h = row - tl * G;
+            v[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (tl < ntok)
+                v[i] = *reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + tok0 + tl) * p.q_stride + (size_t)(kvh * G + h) * FA_D + c * 8);
+        }
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int e = tid + i * 128;
+            const int row = e >> 4, c = e & 15;
+            *reinterpret_cast<uint4*>(Qs + (c >> 3) * FA_HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v[i];
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + FA_KEYS;
+
+    if (warp == 4) {
+        // ---- loads of the later tiles ----
+        for (int j = 1; j < num_key_tiles; ++j) load_tile(j);
     } else if (warp == 5) {
         // ---- MMA issue ----
         if (lane == 0) {
