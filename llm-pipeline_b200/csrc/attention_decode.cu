@@ -221,6 +221,8 @@ decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
                     int max_splits) {
     __shared__ float wgt[MERGE_MAX_SPLITS];
     __shared__ float scratch[32];
+    pdl_trigger();                                 // the product that follows may start fetching its weights
+    pdl_wait();                                    // the partials are complete
     const int r = blockIdx.y, h = blockIdx.x;
     const int ctx = ctx_len[r];
     const int nsplits = (ctx + DEC_SPLIT - 1) / DEC_SPLIT;
@@ -299,8 +301,12 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
         if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,
                                    page_size, window, scale, p.part_o, p.part_ml, stream))
             return 1;
-        decode_merge_kernel<bf16><<<mgrid, MERGE_THREADS, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (bf16*)out, out_stride, nq, d,
-                                                            p.max_splits);
+        const cudaError_t launched = llmp_launch_dependent(decode_merge_kernel<bf16>, mgrid, dim3(MERGE_THREADS), 0, stream,
+                                                           p.part_o, p.part_ml, ctx_len, (bf16*)out, out_stride, nq, d, p.max_splits);
+        if (launched != cudaSuccess) {
+            llmp_set_error("decode_merge: launch failed: %s", cudaGetErrorString(launched));
+            return 2;
+        }
     }
     return llmp_check_launch("decode_attention");
 }

@@ -111,13 +111,15 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
     // zero-filled), then the warp's key groups. With a power-of-two row (d = 16 << k) a warp
     // instruction covers 32 / vec_per_row whole rows and the indices are shifts and adds; other head
     // sizes take the general loops.
+    // The kernel before this one wrote the query rows and the newest key and value (position ctx - 1); all
+    // other keys are older. A block whose range holds the newest key waits for that kernel first; the others
+    // ask for their keys and values, then wait, then fetch the query rows.
+    const bool newest_here = hi == ctx;
+    if (newest_here) pdl_wait();
     const bool pow2 = (vec_per_row & (vec_per_row - 1)) == 0;
     if (pow2) {
         const int sub = lane / vec_per_row, c = (lane % vec_per_row) * 8;
         const int rows_per_pass = DM_THREADS / vec_per_row;
-        for (int row = tid / vec_per_row; row < DM_ROWS; row += rows_per_pass)
-            dm_cp_async_16(Qs + row * stride + c, row < heads ? q + (size_t)row * d + c : q, row < heads);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
         const int rows_per_instr = 32 / vec_per_row;
 #pragma unroll
         for (int grp = 0; grp < DM_GROUPS; ++grp) {
@@ -131,12 +133,11 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
-    } else {
-        for (int e = tid; e < DM_ROWS * vec_per_row; e += DM_THREADS) {
-            const int row = e / vec_per_row, c = (e % vec_per_row) * 8;
+        if (!newest_here) pdl_wait();
+        for (int row = tid / vec_per_row; row < DM_ROWS; row += rows_per_pass)
             dm_cp_async_16(Qs + row * stride + c, row < heads ? q + (size_t)row * d + c : q, row < heads);
-        }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
+    } else {
 #pragma unroll
         for (int grp = 0; grp < DM_GROUPS; ++grp) {
             for (int e = lane; e < 16 * vec_per_row; e += 32) {
@@ -149,7 +150,14 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attention_mma_kernel(const 
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
+        if (!newest_here) pdl_wait();
+        for (int e = tid; e < DM_ROWS * vec_per_row; e += DM_THREADS) {
+            const int row = e / vec_per_row, c = (e % vec_per_row) * 8;
+            dm_cp_async_16(Qs + row * stride + c, row < heads ? q + (size_t)row * d + c : q, row < heads);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
+    pdl_trigger();                                               // the merge kernel may take its places
     // Everything this warp asked for has landed after wait_group 0; the query rows were written by all
     // warps, hence the block-wide barrier.
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -307,15 +315,20 @@ int llmp_launch_decode_mma(const void* q, long q_stride, const void* pages, cons
     size_t smem = tiles + qbytes;
     if (smem < merge) smem = merge;
     dim3 grid(max_splits, nkv * p.head_chunks, R);
+    cudaError_t launched = cudaSuccess;
     if (d <= 64) {
         LLMP_ALLOW_SMEM(decode_attention_mma_kernel<8>, smem);
-        decode_attention_mma_kernel<8><<<grid, DM_THREADS, smem, stream>>>(p);
+        launched = llmp_launch_dependent(decode_attention_mma_kernel<8>, grid, dim3(DM_THREADS), smem, stream, p);
     } else if (d <= 128) {
         LLMP_ALLOW_SMEM(decode_attention_mma_kernel<16>, smem);
-        decode_attention_mma_kernel<16><<<grid, DM_THREADS, smem, stream>>>(p);
+        launched = llmp_launch_dependent(decode_attention_mma_kernel<16>, grid, dim3(DM_THREADS), smem, stream, p);
     } else {
         LLMP_ALLOW_SMEM(decode_attention_mma_kernel<32>, smem);
-        decode_attention_mma_kernel<32><<<grid, DM_THREADS, smem, stream>>>(p);
+        launched = llmp_launch_dependent(decode_attention_mma_kernel<32>, grid, dim3(DM_THREADS), smem, stream, p);
+    }
+    if (launched != cudaSuccess) {
+        llmp_set_error("decode_attention_mma: launch failed: %s", cudaGetErrorString(launched));
+        return 2;
     }
     return llmp_check_launch("decode_attention_mma");
 }

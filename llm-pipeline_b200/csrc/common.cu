@@ -1,4 +1,7 @@
 // Error reporting shared by the C entry points.
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 #include <stdarg.h>
@@ -24,3 +27,12 @@ LLMP_API const char* llmp_last_error() { return g_error; }
 
 // Version of the entry-point signatures; the Python bindings refuse a library built from other sources.
 LLMP_API int llmp_abi_version() { return 1; }
+
+bool llmp_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("LLMP_B200_PDL");
+        enabled = (v && strcmp(v, "0") == 0) ? 0 : 1;
+    }
+    return enabled == 1;
+}

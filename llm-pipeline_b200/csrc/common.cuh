@@ -88,3 +88,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     r = warp_max(r);
     return r;
 }
+
+// ---- programmatic dependent launch --------------------------------------------------------------------
+// A kernel launched with llmp_launch_dependent may start while the kernel before it in the stream still
+// runs, once every block of that kernel has called pdl_trigger() or ended. Whatever it reads of that
+// kernel's output, and whatever it writes, comes after pdl_wait(), which returns when the kernel before it
+// has completed and its writes are visible; before it the kernel only fetches what no kernel of the step
+// writes (weights, keys and values of earlier steps). Both calls do nothing in a launch without such a
+// dependency.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// False when the environment variable LLMP_B200_PDL is "0": dependent launches then become plain ones.
+bool llmp_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t llmp_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = llmp_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}

@@ -249,6 +249,7 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
                                 int rotary_dim, const int* __restrict__ slots, T* __restrict__ pages,
                                 int nq, int nkv, int d, int page_size) {
     extern __shared__ float head_smem[];           // [QKV_WARPS][d]
+    pdl_trigger();                                 // the attention kernel may start fetching keys of earlier steps
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* x = head_smem + (size_t)warp * d;
@@ -351,6 +352,7 @@ qkv_post_d128_kernel(T* __restrict__ qkv, const void* __restrict__ bias, int bia
                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
                      T* __restrict__ pages, int nq, int nkv, int page_size) {
     constexpr int D = 128;
+    pdl_trigger();                                 // the attention kernel may start fetching keys of earlier steps
     const int n = blockIdx.x;
     const int hl = threadIdx.x & 15;                               // lane within the half-warp
     const int half_warp = threadIdx.x >> 4;
@@ -486,6 +488,7 @@ template <> __device__ __forceinline__ float silu<bf16>(float z) { return __fdiv
 
 template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+    pdl_trigger();                                 // the product that follows may start fetching its weights
     const int n = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= I) return;
@@ -500,6 +503,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 // bfloat16 rows whose width is a multiple of 8: 16-byte pieces.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I) {
+    pdl_trigger();                                 // the product that follows may start fetching its weights
     const int n = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= I) return;

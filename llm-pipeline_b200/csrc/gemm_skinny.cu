@@ -60,10 +60,9 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
     const int cc = (tid % CPR) * 8;                      // this thread's column inside a chunk
     const int r0 = tid / CPR;
 
-    // the copies of step (tile, chunk) into a ring buffer
-    auto issue = [&](int tile, int chunk, int stage) {
+    // the copies of step (tile, chunk) into a ring buffer: the rows of W, and the rows of X
+    auto issue_w = [&](int tile, int chunk, int stage) {
         bf16* Ws = ring + (size_t)stage * STAGE_ELEMS;
-        bf16* Xs = Ws + ROWS * STRIDE;
         const int n0 = tile * ROWS;
         const int k = chunk * SK_KC + cc;
         const bool kin = k < K;
@@ -72,11 +71,20 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
             const bool ok = kin && (n0 + row) < N;
             sk_cp_async_16(Ws + row * STRIDE + cc, ok ? W + (size_t)(n0 + row) * ldw + k : W, ok);
         }
+    };
+    auto issue_x = [&](int chunk, int stage) {
+        bf16* Xs = ring + (size_t)stage * STAGE_ELEMS + ROWS * STRIDE;
+        const int k = chunk * SK_KC + cc;
+        const bool kin = k < K;
 #pragma unroll
         for (int row = r0; row < XROWS; row += ROWS_PER_PASS) {
             const bool ok = kin && row < M;
             sk_cp_async_16(Xs + row * STRIDE + cc, ok ? X + (size_t)row * ldx + k : X, ok);
         }
+    };
+    auto issue = [&](int tile, int chunk, int stage) {
+        issue_w(tile, chunk, stage);
+        issue_x(chunk, stage);
     };
 
     float acc[MT][NT][4];
@@ -85,11 +93,28 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
 
+    // The first STAGES - 1 steps: their rows of W are asked for at once; X may still be in the making by the
+    // kernel before this one, so its rows follow after pdl_wait(). The first copy group then holds all of
+    // these rows of W, which were asked for first.
     int issue_tile = blockIdx.x, issue_chunk = 0, issued = 0;
+    {
+        int t = issue_tile, c = issue_chunk;
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < total) {
+                issue_w(t, c, s);
+                if (++c == chunks) {
+                    c = 0;
+                    t += gridDim.x;
+                }
+            }
+        }
+    }
+    pdl_wait();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (issued < total) {
-            issue(issue_tile, issue_chunk, s);
+            issue_x(issue_chunk, s);
             ++issued;
             if (++issue_chunk == chunks) {
                 issue_chunk = 0;
@@ -186,7 +211,12 @@ static int launch_skinny(const bf16* X, const bf16* W, TO* Y, int M, int N, int 
     const int tiles = (N + ROWS - 1) / ROWS;
     const int resident = sms * per_sm;
     const int grid = tiles < resident ? tiles : resident;
-    kernel<<<grid, SK_THREADS, smem, stream>>>(X, W, Y, M, N, K, ldx, ldw, ldy);
+    const cudaError_t launched = llmp_launch_dependent(kernel, dim3(grid), dim3(SK_THREADS), smem, stream, X, W, Y, M, N, K,
+                                                       ldx, ldw, ldy);
+    if (launched != cudaSuccess) {
+        llmp_set_error("gemm_skinny: launch failed: %s", cudaGetErrorString(launched));
+        return 2;
+    }
     return llmp_check_launch("gemm_skinny");
 }
 

@@ -216,9 +216,19 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int quarter = warp & 3;
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < count; ++i) {
+            // A holds the weights: the ring is filled with them at once. B, the activations, may still be in the
+            // making by the kernel before this one: its loads follow after pdl_wait().
+            const int ahead = count < STAGES ? count : STAGES;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES, &map_a, (kb0 + i) * TC_BK, a0, &full_bar[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + A_BYTES, &map_b, (kb0 + i) * TC_BK, b0, &full_bar[i]);
+            for (int i = ahead; i < count; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, error_flag)) break;
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, error_flag)) break;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
                 tma_load_2d(stage, &map_a, (kb0 + i) * TC_BK, a0, &full_bar[s]);
@@ -544,13 +554,15 @@ static int launch_tc_splitk(const void* A, long rows_a, long lda, const void* B,
     config.blockDim = dim3(TC_THREADS, 1, 1);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = (unsigned)splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see pdl_wait() in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = 1;
+    config.numAttrs = llmp_pdl_enabled() ? 2 : 1;
     const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_a, map_b, Y, (int)rows_a, (int)rows_b, K, ldy, splits,
                                                error_flag);
     if (err != cudaSuccess) {
