@@ -134,6 +134,12 @@ __global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* _
     const bool active = c < H;
     float x[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
     if (active) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = load_as_float(weight, weight_bf16, c + i);
+    }
+    pdl_wait();                                    // the addend (and the residual of the kernel before) is complete
+    pdl_trigger();
+    if (active) {
         Vec4<float>::load(residual + (size_t)r * H + c, x);
         if (delta) {
             float dl[4];
@@ -145,8 +151,6 @@ __global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* _
 #pragma unroll
             for (int i = 0; i < 4; ++i) x[i] += load_as_float(delta_bias, bias_bf16, c + i);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = load_as_float(weight, weight_bf16, c + i);
     }
     const float ss = block_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3], scratch);
     const float rstd = rsqrtf(ss / (float)H + eps);
@@ -166,14 +170,19 @@ LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* de
     LLMP_REQUIRE(H > 0, "add_rmsnorm: bad width %d", H);
     if (H % 4 == 0 && H <= 4096) {
         const int threads = ((H / 4 + 31) / 32) * 32;
+        cudaError_t launched;
         if (dtype == LLMP_F32)
-            add_rmsnorm_row4_kernel<float><<<M, threads, 0, stream>>>(residual, (const float*)delta, delta_bias,
+            launched = llmp_launch_dependent(add_rmsnorm_row4_kernel<float>, dim3(M), dim3(threads), 0, stream, residual, (const float*)delta, delta_bias,
                                                                       bias_dtype == LLMP_BF16, weight,
                                                                       weight_dtype == LLMP_BF16, eps, (float*)out, rows, H);
         else
-            add_rmsnorm_row4_kernel<bf16><<<M, threads, 0, stream>>>(residual, (const bf16*)delta, delta_bias,
+            launched = llmp_launch_dependent(add_rmsnorm_row4_kernel<bf16>, dim3(M), dim3(threads), 0, stream, residual, (const bf16*)delta, delta_bias,
                                                                      bias_dtype == LLMP_BF16, weight,
                                                                      weight_dtype == LLMP_BF16, eps, (bf16*)out, rows, H);
+        if (launched != cudaSuccess) {
+            llmp_set_error("add_rmsnorm: launch failed: %s", cudaGetErrorString(launched));
+            return 2;
+        }
         return llmp_check_launch("add_rmsnorm");
     }
     const size_t smem = (size_t)H * sizeof(float);
@@ -250,6 +259,7 @@ __global__ void qkv_post_kernel(T* __restrict__ qkv, const void* __restrict__ bi
                                 int nq, int nkv, int d, int page_size) {
     extern __shared__ float head_smem[];           // [QKV_WARPS][d]
     pdl_trigger();                                 // the attention kernel may start fetching keys of earlier steps
+    pdl_wait();                                    // the projection is complete
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* x = head_smem + (size_t)warp * d;
@@ -375,6 +385,7 @@ qkv_post_d128_kernel(T* __restrict__ qkv, const void* __restrict__ bias, int bia
         if (q_w) { if (w_bf16) Piece8<bf16>::load((const bf16*)q_w + e0, wq); else Piece8<float>::load((const float*)q_w + e0, wq); }
         if (k_w) { if (w_bf16) Piece8<bf16>::load((const bf16*)k_w + e0, wk); else Piece8<float>::load((const float*)k_w + e0, wk); }
     }
+    pdl_wait();                                    // the projection is complete (tables and weights were read before)
     // Heads in rounds of QKV_UNROLL per half-warp: the loads of a round are issued before any of its stores.
     const int step = gridDim.y * (QKV_WARPS * 2);
     for (int h0 = blockIdx.y * (QKV_WARPS * 2); h0 < heads; h0 += step * QKV_UNROLL) {  // uniform over the warp
@@ -456,9 +467,9 @@ LLMP_API int llmp_qkv_post(void* qkv, int dtype, const void* bias, int bias_dtyp
                 (float*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, slots,
                 (float*)pages, nq, nkv, page_size);
         else
-            qkv_post_d128_kernel<bf16><<<grid128, QKV_WARPS * 32, 0, stream>>>(
-                (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t, slots,
-                (bf16*)pages, nq, nkv, page_size);
+            llmp_launch_dependent(qkv_post_d128_kernel<bf16>, grid128, dim3(QKV_WARPS * 32), 0, stream,
+                                  (bf16*)qkv, bias, bias_dtype == LLMP_BF16, q_w, k_w, w_dtype == LLMP_BF16, eps, cos_t, sin_t,
+                                  slots, (bf16*)pages, nq, nkv, page_size);
         return llmp_check_launch("qkv_post");
     }
     dim3 grid(N, head_blocks);
@@ -489,6 +500,7 @@ template <> __device__ __forceinline__ float silu<bf16>(float z) { return __fdiv
 template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
     pdl_trigger();                                 // the product that follows may start fetching its weights
+    pdl_wait();                                    // the gate and up projections are complete
     const int n = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= I) return;
@@ -504,6 +516,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // bfloat16 rows whose width is a multiple of 8: 16-byte pieces.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I) {
     pdl_trigger();                                 // the product that follows may start fetching its weights
+    pdl_wait();                                    // the gate and up projections are complete
     const int n = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= I) return;
@@ -535,7 +548,7 @@ LLMP_API int llmp_swiglu(const void* gu, void* out, int dtype, int N, int I, cud
             const bf16* src = (const bf16*)gu + (size_t)n0 * 2 * I;
             bf16* dst = (bf16*)out + (size_t)n0 * I;
             if (I % 8 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0)
-                swiglu_bf16x8_kernel<<<dim3((I / 8 + 255) / 256, rows), 256, 0, stream>>>(src, dst, I);
+                llmp_launch_dependent(swiglu_bf16x8_kernel, dim3((I / 8 + 255) / 256, rows), dim3(256), 0, stream, src, dst, I);
             else if (vec == 4) swiglu_kernel<bf16, 4><<<grid, 256, 0, stream>>>(src, dst, I);
             else swiglu_kernel<bf16, 1><<<grid, 256, 0, stream>>>(src, dst, I);
         }

@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ Y, int M, int N, int K,
                    long ldx, long ldw, long ldy) {
     extern __shared__ __align__(16) unsigned char sk_smem[];
+    pdl_trigger();                                       // the kernel after this one may take its places
     constexpr int STRIDE = SK_KC + SK_PAD;               // elements per shared-memory row
     constexpr int MT = ROWS / 16;                        // 16-row MMA tiles of W
     constexpr int XROWS = NT * 8;

@@ -188,6 +188,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TC_BM, b0 = blockIdx.y * BN;
     const int rank = (int)cluster_ctarank();
+    pdl_trigger();                                   // the kernel after this one may take its places
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     const int per = (kblocks + splits - 1) / splits;
     const int kb0 = rank * per;
