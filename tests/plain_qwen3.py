@@ -319,3 +319,12 @@ TINY_C = {
     "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "attention_bias": True,
     "max_position_embeddings": 2048, "hidden_act": "silu",
 }
+
+# A fourth shape: head_dim 128 (the size that the tcgen05 prefill attention kernel takes in bfloat16), groups of 2.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 160, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 288, "vocab_size": 300, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "attention_bias": False,
+    "max_position_embeddings": 2048, "hidden_act": "silu",
+}
