@@ -253,16 +253,25 @@ int llmp_launch_decode_mma(const void* q, long q_stride, const void* pages, cons
                            const int* ctx_len, int R, int max_splits, int nq, int nkv, int d, int page_size,
                            int window, float scale, float* part_o, float* part_ml, cudaStream_t stream);
 
+// The streaming kernel for head size 128 (attention_decode_tma.cu).
+bool llmp_decode_tma_supports(int nq, int nkv, int d, int page_size);
+int llmp_launch_decode_tma(const void* q, long q_stride, const void* pages, int num_pages, const int* block_tables,
+                           int table_stride, const int* ctx_len, int R, int max_splits, int nq, int nkv, int page_size,
+                           int window, float scale, float* part_o, float* part_ml, int* error_flag, cudaStream_t stream);
+
 // Scratch floats the decode kernel needs for R rows whose longest context is max_ctx keys.
 LLMP_API long llmp_decode_scratch_floats(int R, int nq, int d, int max_ctx) {
     const long splits = (max_ctx + DEC_SPLIT - 1) / DEC_SPLIT;
     return (long)R * nq * (splits > 0 ? splits : 1) * (d + 2);
 }
 
+// pages: [num_pages, 2, nkv, page_size, d]. error_flag: one int in device-visible memory that a kernel with bounded
+// waits sets to 1 when a wait ran out (may be null: the kernels that need it are then not used).
 LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long out_stride, const void* pages,
-                                   int dtype, const int* block_tables, int table_stride, const int* ctx_len, int R,
-                                   int max_ctx, int nq, int nkv, int d, int page_size, int window, float scale,
-                                   float* scratch, long scratch_floats, cudaStream_t stream) {
+                                   int num_pages, int dtype, const int* block_tables, int table_stride,
+                                   const int* ctx_len, int R, int max_ctx, int nq, int nkv, int d, int page_size,
+                                   int window, float scale, float* scratch, long scratch_floats, int* error_flag,
+                                   cudaStream_t stream) {
     if (R <= 0) return 0;
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads cannot share %d key/value heads", nq, nkv);
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
@@ -298,8 +307,12 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
         decode_merge_kernel<float><<<mgrid, MERGE_THREADS, 0, stream>>>(p.part_o, p.part_ml, ctx_len, (float*)out, out_stride, nq, d,
                                                              p.max_splits);
     } else {
-        if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,
-                                   page_size, window, scale, p.part_o, p.part_ml, stream))
+        if (error_flag != nullptr && num_pages > 0 && llmp_decode_tma_supports(nq, nkv, d, page_size)) {
+            if (llmp_launch_decode_tma(q, q_stride, pages, num_pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq,
+                                       nkv, page_size, window, scale, p.part_o, p.part_ml, error_flag, stream))
+                return 1;
+        } else if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,
+                                          page_size, window, scale, p.part_o, p.part_ml, stream))
             return 1;
         const cudaError_t launched = llmp_launch_dependent(decode_merge_kernel<bf16>, mgrid, dim3(MERGE_THREADS), 0, stream,
                                                            p.part_o, p.part_ml, ctx_len, (bf16*)out, out_stride, nq, d, p.max_splits);

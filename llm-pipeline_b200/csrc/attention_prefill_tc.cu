@@ -437,9 +437,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
 // ---- host side ---------------------------------------------------------------------------------------------
 struct PagesKey {
     const void* ptr;
-    int nkv, page_size, num_pages;
+    int nkv, page_size, num_pages, box_tokens, box_kv;
     bool operator==(const PagesKey& o) const {
-        return ptr == o.ptr && nkv == o.nkv && page_size == o.page_size && num_pages == o.num_pages;
+        return ptr == o.ptr && nkv == o.nkv && page_size == o.page_size && num_pages == o.num_pages && box_tokens == o.box_tokens &&
+               box_kv == o.box_kv;
     }
 };
 struct PagesKeyHash {
@@ -447,15 +448,19 @@ struct PagesKeyHash {
         size_t h = (size_t)k.ptr;
         h = h * 1000003u ^ (size_t)k.nkv;
         h = h * 1000003u ^ (size_t)k.page_size;
-        return h * 1000003u ^ (size_t)k.num_pages;
+        h = h * 1000003u ^ (size_t)k.num_pages;
+        h = h * 1000003u ^ (size_t)k.box_tokens;
+        return h * 1000003u ^ (size_t)k.box_kv;
     }
 };
 
-// Pages [num_pages, 2, nkv, page_size, 128] of bfloat16, read in boxes of one page of one head and 64 elements.
-static int pages_map(const void* pages, int nkv, int page_size, int num_pages, CUtensorMap* out) {
+// Pages [num_pages, 2, nkv, page_size, 128] of bfloat16, read in boxes of box_tokens tokens of one page and head
+// and 64 elements (128-byte swizzle); box_kv = 2 takes the keys and the values of these tokens in one box (keys first).
+int llmp_pages_tensor_map(const void* pages, int nkv, int page_size, int num_pages, int box_tokens, int box_kv,
+                          CUtensorMap* out) {
     static std::unordered_map<PagesKey, CUtensorMap, PagesKeyHash> cache;
     static std::mutex lock;
-    const PagesKey key{pages, nkv, page_size, num_pages};
+    const PagesKey key{pages, nkv, page_size, num_pages, box_tokens, box_kv};
     std::lock_guard<std::mutex> guard(lock);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -467,7 +472,7 @@ static int pages_map(const void* pages, int nkv, int page_size, int num_pages, C
     const cuuint64_t row = FA_D * sizeof(bf16);
     const cuuint64_t dims[5] = {FA_D, (cuuint64_t)page_size, (cuuint64_t)nkv, 2, (cuuint64_t)num_pages};
     const cuuint64_t strides[4] = {row, row * page_size, row * page_size * nkv, row * page_size * nkv * 2};
-    const cuuint32_t box[5] = {64, (cuuint32_t)page_size, 1, 1, 1};
+    const cuuint32_t box[5] = {64, (cuuint32_t)box_tokens, 1, (cuuint32_t)box_kv, 1};
     const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
     const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(pages), dims, strides, box, elem,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -495,7 +500,7 @@ int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_str
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 8) == 0 && ((size_t)q % 16) == 0 && ((size_t)out % 16) == 0 &&
                  ((size_t)pages % 16) == 0, "attention: rows must be 16-byte aligned");
     CUtensorMap map;
-    if (pages_map(pages, nkv, page_size, num_pages, &map)) return 1;
+    if (llmp_pages_tensor_map(pages, nkv, page_size, num_pages, page_size, 1, &map)) return 1;
     FaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len;
     p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.q_stride = q_stride; p.out_stride = out_stride;

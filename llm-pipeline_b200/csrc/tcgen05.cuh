@@ -84,3 +84,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn llmp_tensor_map_encoder();
+
+// Tensor map over bfloat16 pages [num_pages, 2, nkv, page_size, 128], cached per tensor: boxes of box_tokens
+// tokens of one page and key/value head and 64 elements, 128-byte swizzle; box_kv = 2 takes keys and values in one
+// box (attention_prefill_tc.cu).
+int llmp_pages_tensor_map(const void* pages, int nkv, int page_size, int num_pages, int box_tokens, int box_kv,
+                          CUtensorMap* out);
+
+// Five-dimensional box of the pages into shared memory: x = first element (0 or 64), token within the page,
+// key/value head, 0 = keys or 1 = values, page. A page index out of range arrives as zeros.
+__device__ __forceinline__ void tma_load_page_box(void* smem_dst, const CUtensorMap* map, int x, int token, int kvh, int kv,
+                                                  int page, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(token), "r"(kvh), "r"(kv), "r"(page)
+        : "memory");
+}

@@ -44,7 +44,7 @@ _SIGNATURES = {
     "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-    "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P],
+    "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -302,9 +302,10 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: t
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
           f"decode scratch must hold {need} float32 values")
-    _call("llmp_decode_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), dtype_code(q.dtype),
-          _ptr(block_tables), block_tables.stride(0), _ptr(ctx_len), R, int(max_ctx), num_heads, num_kv_heads, head_dim,
-          page_size, int(window), float(scale), _ptr(scratch), scratch.numel(), _stream())
+    _call("llmp_decode_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), pages.shape[0],
+          dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(ctx_len), R, int(max_ctx), num_heads,
+          num_kv_heads, head_dim, page_size, int(window), float(scale), _ptr(scratch), scratch.numel(),
+          error_flag().data_ptr(), _stream())
     return out
 
 

@@ -279,6 +279,25 @@ def test_decode_attention_split_keys(dtype, nq, nkv, d, page):
     assert torch.allclose(got_w, want_w, atol=tol(dtype, 2e-5, 2e-2))
 
 
+@pytest.mark.parametrize("nq,nkv,page", [(32, 8, 16), (8, 1, 8), (4, 4, 32), (6, 2, 64), (16, 2, 128)])
+def test_decode_attention_head_size_128_streaming_kernel(nq, nkv, page):
+    """Head size 128 in bfloat16 with up to 8 heads per group takes the persistent TMA kernel: contexts on both
+    sides of the 128-key ranges and of a warp's 32 keys, and enough requests that every block's ring of stages
+    is filled several times over."""
+    dtype = torch.bfloat16
+    contexts = [0, 31, 32, 127, 128, 255, 256, 700, 63, 64, 1030, 5, 129, 511] * 3
+    requests = [(c, 1) for c in contexts]
+    got, want = run_paged(dtype, nq, nkv, 128, page, requests, seed=21, decode=True)
+    assert torch.allclose(got, want, atol=2e-2)
+    got_w, want_w = run_paged(dtype, nq, nkv, 128, page, requests, window=300, seed=22, decode=True)
+    assert torch.allclose(got_w, want_w, atol=2e-2)
+    K().check_error_flag()
+    for key_pos in (3, 127, 128, 511, 698):
+        got, want = run_paged(dtype, 8, 2, 128, 16, [(699, 1), (40, 1)], seed=4, boost=(0, key_pos, 5), decode=True)
+        assert torch.allclose(got, want, atol=3e-2), key_pos
+        assert float(want[0, 5].abs().max()) > 0.5
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_attention_finds_one_far_key(dtype):
     for key_pos in (3, 255, 256, 511, 698):
