@@ -45,7 +45,7 @@ QWEN3_32B = {**QWEN3_8B, "num_hidden_layers": 64, "hidden_size": 5120, "num_atte
 SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 16
+PAGE_SIZE = 32
 
 
 def peaks():
