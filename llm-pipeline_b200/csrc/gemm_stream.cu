@@ -1,0 +1,333 @@
+// Y[M, N] = X[M, K] * W[N, K]^T for the few rows of a decode step (M <= 16), bound by reading W once from HBM:
+// one persistent block per SM streams its share of W through a ring of TMA boxes.
+//
+// The rows of W are dealt out evenly: block b owns the contiguous rows [b * per, (b + 1) * per) and walks them
+// in chunks of RB <= 128 rows; for each chunk it walks K in steps of KB blocks of 64 elements. A ring stage
+// holds one step: a box of W (RB rows x KB x 64 elements, as KB planes of rows of 128 bytes in the 128-byte
+// swizzle) and the matching box of X (8 or 16 rows). A load warp fills the ring as slots come free and runs
+// ahead across chunks; four compute warps take the stages of a chunk in turn (warp w the steps w, w + 4, ...
+// of K), multiply with mma.sync m16n8k16 (the rows of W on the 16-row side, the rows of X on the
+// 8-column side, float32 accumulators in registers) and hand the slot back. At the end of a chunk the four
+// warps' sums are added in warp order in shared memory and stored. The order of the additions depends on K
+// alone, so a row of X gives the same result whatever else is in X.
+//
+// As a dependent launch: W is constant, X may still be in the making by the kernel before this one. The load
+// warp fills the whole ring with boxes of W, then waits for that kernel, then adds the boxes of X.
+//
+// Every wait on an mbarrier is bounded: when one runs out the kernel records 1 in *error_flag and goes on
+// without waiting (its output is then wrong; the host reads the flag).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#define GS_CWARPS 4
+#define GS_THREADS ((GS_CWARPS + 1) * 32)
+#define GS_MAX_RB 128
+#define GS_MAX_STAGES 24
+#define GS_SMEM_BUDGET (200 * 1024)
+
+struct StreamParams {
+    void* Y;
+    long ldy;
+    int M, N, K;
+    int per;              // rows of W per block
+    int RB;               // rows of W per chunk and box
+    int KB;               // 64-element blocks of K per stage
+    int MB;               // rows of the X box: 8 or 16
+    int stages;
+    int out_f32;
+    int* error_flag;
+};
+
+__device__ __forceinline__ void gs_tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+__device__ __forceinline__ void gs_ldmatrix_x4(unsigned (&r)[4], const void* smem_ptr) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+__device__ __forceinline__ void gs_ldmatrix_x2(unsigned (&r)[2], const void* smem_ptr) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+
+__device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 16 bytes of line `line` of a stage (lines of 128 bytes, counted from the stage's 1024-byte aligned start)
+// starting at 16-byte chunk `chunk`: the 128-byte swizzle exchanges the chunk index with the low bits of the line.
+__device__ __forceinline__ const unsigned char* gs_at(const unsigned char* stage, int line, int chunk) {
+    return stage + line * 128 + ((chunk ^ (line & 7)) << 4);
+}
+
+// MT: 16-row tiles of W per chunk (RB <= 16 MT). NT: 8-row tiles of X (M <= 8 NT).
+template <int MT, int NT>
+__global__ void __launch_bounds__(GS_THREADS, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const StreamParams p) {
+    extern __shared__ unsigned char gs_raw[];
+    __shared__ __align__(8) uint64_t full_bar[GS_MAX_STAGES], empty_bar[GS_MAX_STAGES];
+    const uint32_t raw_addr = tc_smem_u32(gs_raw);
+    unsigned char* ring = gs_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);      // 1024-byte aligned stages
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // a stage: KB planes of RB lines of W, then KB planes of MB lines of X, rounded up to 1024 bytes
+    const uint32_t w_bytes = (uint32_t)p.RB * 128 * p.KB, x_bytes = (uint32_t)p.MB * 128 * p.KB;
+    const uint32_t stage_bytes = (w_bytes + x_bytes + 1023u) & ~1023u;
+    float* part = reinterpret_cast<float*>(ring + (size_t)p.stages * stage_bytes);   // [warps][RB][8 NT]
+
+    const int row_begin = blockIdx.x * p.per;
+    int row_end = row_begin + p.per;
+    if (row_end > p.N) row_end = p.N;
+    const int chunks = row_begin < row_end ? (row_end - row_begin + p.RB - 1) / p.RB : 0;
+    const int ksteps = p.K / (64 * p.KB);                       // stages per chunk
+    const int total = chunks * ksteps;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
+    }
+    __syncthreads();
+    pdl_trigger();                                              // the kernel after this one may take its places
+
+    if (warp == GS_CWARPS) {
+        if (lane == 0) {
+            // Stage (chunk, ks) belongs to compute warp w = ks % 4 and is that warp's j-th stage; it lives in slot
+            // 4 (j % S4) + w. A slot is thus filled for one warp only, which sees every phase of its barrier in turn.
+            const int S4 = p.stages / GS_CWARPS;
+            auto slot_of = [&](int chunk, int ks, int& round) {
+                const int w = ks % GS_CWARPS;
+                const int per_chunk = (ksteps - w + GS_CWARPS - 1) / GS_CWARPS;     // stages of warp w in a chunk
+                const int j = chunk * per_chunk + ks / GS_CWARPS;
+                round = j / S4;
+                return GS_CWARPS * (j % S4) + w;
+            };
+            // the first round of every slot is filled with boxes of W at once; the boxes of X follow after pdl_wait()
+            int first_later = total;                             // first stage (in issue order) of a later round
+            for (int i = 0; i < total; ++i) {
+                const int chunk = i / ksteps, ks = i - chunk * ksteps;
+                int round;
+                const int slot = slot_of(chunk, ks, round);
+                if (round > 0) {
+                    first_later = i;
+                    break;
+                }
+                mbar_expect_tx(&full_bar[slot], w_bytes + x_bytes);
+                gs_tma_load_3d(ring + (size_t)slot * stage_bytes, &map_w, 0, row_begin + chunk * p.RB, ks * p.KB, &full_bar[slot]);
+            }
+            pdl_wait();
+            for (int i = 0; i < first_later; ++i) {
+                const int chunk = i / ksteps, ks = i - chunk * ksteps;
+                int round;
+                const int slot = slot_of(chunk, ks, round);
+                gs_tma_load_3d(ring + (size_t)slot * stage_bytes + w_bytes, &map_x, 0, 0, ks * p.KB, &full_bar[slot]);
+            }
+            for (int i = first_later; i < total; ++i) {
+                const int chunk = i / ksteps, ks = i - chunk * ksteps;
+                int round;
+                const int slot = slot_of(chunk, ks, round);
+                if (round > 0) mbar_wait(&empty_bar[slot], (uint32_t)((round - 1) & 1), p.error_flag);
+                mbar_expect_tx(&full_bar[slot], w_bytes + x_bytes);
+                unsigned char* stage = ring + (size_t)slot * stage_bytes;
+                gs_tma_load_3d(stage, &map_w, 0, row_begin + chunk * p.RB, ks * p.KB, &full_bar[slot]);
+                gs_tma_load_3d(stage + w_bytes, &map_x, 0, 0, ks * p.KB, &full_bar[slot]);
+            }
+        }
+    } else {
+        const int g = lane >> 2, t = lane & 3;
+        float acc[MT][NT][4];
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+        const int steps16 = 4 * p.KB;                            // 16-element K steps per stage
+        const int S4 = p.stages / GS_CWARPS;
+        int j = 0;                                               // stages this warp has taken
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+            // warp w takes the chunk's stages w, w + 4, ... whole: a wait and a hand-back per stage and warp
+            for (int ks = warp; ks < ksteps; ks += GS_CWARPS, ++j) {
+                const int slot = GS_CWARPS * (j % S4) + warp;    // this warp's j-th stage: see the load warp
+                mbar_wait(&full_bar[slot], (uint32_t)((j / S4) & 1), p.error_flag);
+                const unsigned char* stage = ring + (size_t)slot * stage_bytes;
+                for (int s = 0; s < steps16; ++s) {
+                    const int w_line = (s >> 2) * p.RB;                              // first line of this 64-element block of W
+                    const int x_line = p.KB * p.RB + (s >> 2) * p.MB;                //                                    and of X
+                    const int chunk16 = (s & 3) * 2;                                // first 16-byte chunk of the K step
+                    unsigned b[NT][2];
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+                        gs_ldmatrix_x2(b[j], gs_at(stage, x_line + j * 8 + (lane & 7), chunk16 + ((lane >> 3) & 1)));
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        if (mt * 16 < p.RB) {
+                            // rows beyond RB in the last tile read the lines that follow (finite data of the stage or of
+                            // the next one); their sums are never stored
+                            unsigned a[4];
+                            gs_ldmatrix_x4(a, gs_at(stage, w_line + mt * 16 + (lane & 15), chunk16 + (lane >> 4)));
+#pragma unroll
+                            for (int j = 0; j < NT; ++j) gs_mma(acc[mt][j], a, b[j][0], b[j][1]);
+                        }
+                    }
+                }
+                // this warp has read the stage
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem_u32(&empty_bar[slot])) : "memory");
+            }
+            // the chunk is complete: the four warps' sums, added in warp order
+            // acc[mt][j] holds W rows mt*16 + g (+8) and X rows j*8 + 2t (+1)
+            asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CWARPS * 32) : "memory");      // the sums of the chunk before are read
+            const int pstride = 8 * NT + 1;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    float* base = part + ((size_t)warp * GS_MAX_RB + mt * 16 + g) * pstride + j * 8 + 2 * t;
+                    base[0] = acc[mt][j][0];
+                    base[1] = acc[mt][j][1];
+                    base[8 * pstride] = acc[mt][j][2];
+                    base[8 * pstride + 1] = acc[mt][j][3];
+                    acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
+                }
+            }
+            asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CWARPS * 32) : "memory");
+            const int n0 = row_begin + chunk * p.RB;
+            int rows = row_end - n0;
+            if (rows > p.RB) rows = p.RB;
+            for (int e = tid; e < rows * p.M; e += GS_CWARPS * 32) {
+                const int m = e / rows, row = e - m * rows;     // consecutive threads store consecutive columns of Y
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * GS_MAX_RB + row) * pstride + m];
+                if (p.out_f32) reinterpret_cast<float*>(p.Y)[(size_t)m * p.ldy + n0 + row] = v;
+                else reinterpret_cast<bf16*>(p.Y)[(size_t)m * p.ldy + n0 + row] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+struct StreamMapKey {
+    const void* ptr;
+    long rows, k, ld;
+    int box_rows, box_kb;
+    bool operator==(const StreamMapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows && box_kb == o.box_kb;
+    }
+};
+struct StreamMapKeyHash {
+    size_t operator()(const StreamMapKey& m) const {
+        size_t h = (size_t)m.ptr;
+        h = h * 1000003u ^ (size_t)m.rows;
+        h = h * 1000003u ^ (size_t)m.k;
+        h = h * 1000003u ^ (size_t)m.ld;
+        h = h * 1000003u ^ (size_t)m.box_rows;
+        return h * 1000003u ^ (size_t)m.box_kb;
+    }
+};
+
+// A [rows, K] bfloat16 row-major matrix with row pitch ld, seen as {64 elements, rows, K / 64 blocks} and read in
+// boxes of {64, box_rows, box_kb}: in shared memory box_kb planes of box_rows lines of 128 bytes.
+static int stream_map(const void* ptr, long rows, long k, long ld, int box_rows, int box_kb, CUtensorMap* out) {
+    static std::unordered_map<StreamMapKey, CUtensorMap, StreamMapKeyHash> cache;
+    static std::mutex lock;
+    const StreamMapKey key{ptr, rows, k, ld, box_rows, box_kb};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = llmp_tensor_map_encoder();
+    LLMP_REQUIRE(fn != nullptr, "gemm_stream: the driver does not provide cuTensorMapEncodeTiled");
+    const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(k / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(bf16), 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_kb};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    LLMP_REQUIRE(rc == CUDA_SUCCESS, "gemm_stream: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+// Shapes this kernel takes.
+LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) {
+    return M > 0 && M <= 16 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+}
+
+// X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; M <= 16, K a multiple of 64.
+LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                              long ldy, int* error_flag, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    LLMP_REQUIRE(llmp_gemm_stream_supports(M, N, K, ldx, ldw), "gemm_stream: M=%d (at most 16), K=%d (a multiple of 64) or the row strides are not taken", M, K);
+    LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_stream: operands must be 16-byte aligned");
+    LLMP_REQUIRE(error_flag != nullptr, "gemm_stream: an error flag in device memory is required");
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    StreamParams p;
+    p.Y = Y; p.ldy = ldy; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == LLMP_F32; p.error_flag = error_flag;
+    // rows per block: an even share
+    int per = (N + sms - 1) / sms;
+    if (per < 8) per = 8;
+    p.per = per;
+    const int grid = (N + per - 1) / per;
+    const int chunks = (per + GS_MAX_RB - 1) / GS_MAX_RB;
+    const int rb = (per + chunks - 1) / chunks;
+    p.RB = rb;
+    p.MB = M <= 8 ? 8 : 16;
+    // blocks of K per stage: stages of about 16 KB, KB a power of two that divides K / 64
+    int kb = 1;
+    while (kb < 8 && (long)(rb + p.MB) * 128 * kb * 2 <= 24 * 1024 && (K / 64) % (kb * 2) == 0) kb *= 2;
+    p.KB = kb;
+    const size_t stage_bytes = ((size_t)(rb + p.MB) * 128 * kb + 1023) / 1024 * 1024;
+    const size_t part_bytes = (size_t)GS_CWARPS * GS_MAX_RB * (8 * (M <= 8 ? 1 : 2) + 1) * sizeof(float);
+    int stages = (int)((GS_SMEM_BUDGET - part_bytes) / stage_bytes);
+    if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
+    stages = stages / GS_CWARPS * GS_CWARPS;                     // every compute warp has its own slots
+    LLMP_REQUIRE(stages >= GS_CWARPS, "gemm_stream: a stage of %zu bytes does not fit %d times", stage_bytes, GS_CWARPS);
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + part_bytes + 2048;      // 1024 for the alignment, 1024 for reads past the last stage
+    CUtensorMap map_w, map_x;
+    if (stream_map(W, N, K, ldw, rb, kb, &map_w) || stream_map(X, M, K, ldx, p.MB, kb, &map_x)) return 1;
+    const int mt = (rb + 15) / 16;
+    cudaError_t launched = cudaSuccess;
+#define GS_LAUNCH(MT, NT)                                                                                     \
+    do {                                                                                                      \
+        LLMP_ALLOW_SMEM((gemm_stream_kernel<MT, NT>), smem);                                                  \
+        launched = llmp_launch_dependent(gemm_stream_kernel<MT, NT>, dim3(grid), dim3(GS_THREADS), smem, stream, \
+                                         map_w, map_x, p);                                                    \
+    } while (0)
+    if (M <= 8) {
+        if (mt <= 2) GS_LAUNCH(2, 1); else if (mt <= 4) GS_LAUNCH(4, 1); else GS_LAUNCH(8, 1);
+    } else {
+        if (mt <= 2) GS_LAUNCH(2, 2); else if (mt <= 4) GS_LAUNCH(4, 2); else GS_LAUNCH(8, 2);
+    }
+#undef GS_LAUNCH
+    if (launched != cudaSuccess) {
+        llmp_set_error("gemm_stream: launch failed: %s", cudaGetErrorString(launched));
+        return 2;
+    }
+    return llmp_check_launch("gemm_stream");
+}

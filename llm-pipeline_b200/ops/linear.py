@@ -25,6 +25,20 @@ def register_bf16_kernel(fn: Callable) -> None:
     _BF16_KERNELS.append(fn)
 
 
+def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The weight-streaming kernel for at most 16 rows of a decode step: one persistent block per SM, the rows
+    of the weight matrix dealt out evenly, a ring of TMA boxes fed by a load warp."""
+    M, K = x.shape
+    if not STREAM_GEMM or not 0 < M <= 16 or x.stride(1) != 1 or weight.stride(1) != 1:
+        return None
+    if x.data_ptr() % 16 or weight.data_ptr() % 16 or out_dtype not in (torch.bfloat16, torch.float32):
+        return None
+    if not kernels.gemm_stream_supports(M, weight.shape[0], K, x.stride(0), weight.stride(0)):
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
+    return kernels.gemm_stream(x, weight, out)
+
+
 def _tensor_memory(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """The tcgen05 kernel (TMA, accumulator in tensor memory, cluster split-K) for at most 16 rows of a decode
     step against a long K, where it reads the weights faster than the library product does."""
@@ -74,6 +88,14 @@ def _tensor_memory_prefill(x: torch.Tensor, weight: torch.Tensor, out_dtype: tor
 OWN_PREFILL_GEMM = os.environ.get("LLMP_B200_OWN_PREFILL_GEMM", "0") == "1"
 PREFILL_TC_MIN_ROWS = 1024
 
+# Measured on a B200 (Qwen3-8B shapes, 8 rows, replayed decode graph): with this kernel for every product of the
+# step 4.21 ms, with the choice below (library, skinny, tcgen05 split-K) 4.23 ms; at 1 and at 16 rows it loses
+# (3.70 against 3.66 ms, 5.37 against 4.91 ms). Alone it reads the weights of the qkv, gate/up and head products
+# somewhat slower than the library and those of the down projection faster (25 against 34 us). It is therefore
+# off by default; LLMP_B200_STREAM_GEMM=1 routes all products of at most 16 rows through it.
+STREAM_GEMM = os.environ.get("LLMP_B200_STREAM_GEMM", "0") == "1"
+
+register_bf16_kernel(_stream)
 register_bf16_kernel(_tensor_memory)
 register_bf16_kernel(_skinny)
 register_bf16_kernel(_tensor_memory_prefill)

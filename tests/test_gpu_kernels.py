@@ -188,6 +188,26 @@ def test_gemm_tcgen05(out_dtype, M, N, Kd):
         assert torch.equal(single[0], out[M - 1])
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (5, 6144, 1024), (16, 1000, 192), (9, 331, 128),
+                                    (3, 24576, 512), (8, 40000, 256), (2, 7, 64)])
+def test_gemm_stream(M, N, Kd, out_dtype):
+    """The weight-streaming kernel: row counts that give ragged shares per block, one and two 8-row tiles of
+    x, several chunks of rows per block (N = 40000), fewer rows than blocks."""
+    k_ = K()
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=30), rnd(N, Kd, dtype=torch.bfloat16, seed=31)
+    want = x.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    k_.gemm_stream(x, w, out)
+    k_.check_error_flag()
+    scale = float(want.abs().max())
+    assert torch.allclose(out.double(), want, atol=(2e-2 if out_dtype == torch.bfloat16 else 2e-4) * scale, rtol=0)
+    # a row's result does not depend on the other rows
+    single = torch.empty(1, N, dtype=out_dtype, device=DEV)
+    k_.gemm_stream(x[M - 1:M], w, single)
+    assert torch.equal(single[0], out[M - 1])
+
+
 def attention_reference(q, k, v, window, scale):
     """q [T, nq, d] at positions P..P+T-1 over keys k, v [S, nkv, d]; S = P + T."""
     T, nq, d = q.shape
