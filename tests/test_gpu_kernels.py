@@ -289,7 +289,7 @@ def test_paged_attention_mixed_batch(dtype, nq, nkv, d, page):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (6, 1, 32, 8), (9, 3, 48, 4), (32, 8, 128, 16), (5, 5, 80, 16),
-                                           (40, 2, 64, 32), (16, 1, 256, 16)])
+                                           (40, 2, 64, 32), (16, 1, 256, 16), (16, 1, 128, 16), (8, 2, 128, 4)])
 def test_decode_attention_split_keys(dtype, nq, nkv, d, page):
     # contexts on both sides of the 256-key ranges and of the 64-key tiles
     requests = [(0, 1), (255, 1), (256, 1), (700, 1), (63, 1), (64, 1), (1030, 1)]
