@@ -35,6 +35,8 @@ def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Op
         return None
     if not kernels.gemm_stream_supports(M, weight.shape[0], K, x.stride(0), weight.stride(0)):
         return None
+    if weight.shape[0] > STREAM_MAX_N:
+        return None
     out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
     return kernels.gemm_stream(x, weight, out)
 
@@ -88,12 +90,16 @@ def _tensor_memory_prefill(x: torch.Tensor, weight: torch.Tensor, out_dtype: tor
 OWN_PREFILL_GEMM = os.environ.get("LLMP_B200_OWN_PREFILL_GEMM", "0") == "1"
 PREFILL_TC_MIN_ROWS = 1024
 
-# Measured on a B200 (Qwen3-8B shapes, 8 rows, replayed decode graph): with this kernel for every product of the
-# step 4.21 ms, with the choice below (library, skinny, tcgen05 split-K) 4.23 ms; at 1 and at 16 rows it loses
-# (3.70 against 3.66 ms, 5.37 against 4.91 ms). Alone it reads the weights of the qkv, gate/up and head products
-# somewhat slower than the library and those of the down projection faster (25 against 34 us). It is therefore
-# off by default; LLMP_B200_STREAM_GEMM=1 routes all products of at most 16 rows through it.
-STREAM_GEMM = os.environ.get("LLMP_B200_STREAM_GEMM", "0") == "1"
+# Measured on a B200 (Qwen3-8B shapes, replayed decode graph, ms per step): the streaming kernel for the output and
+# down projections (4,096 rows of weights each) and the library product for the rest 4.07 at 8 rows, 3.80 at 4,
+# 4.83 at 16; without it (skinny kernel, tcgen05 split-K) 4.23, 3.96, 4.90; the streaming kernel for every product
+# 4.21 at 8 rows: for the qkv, gate/up and head products (6,144 rows and more) the library reads the weights
+# somewhat faster. At the Qwen3-32B shapes (8 rows) the streaming kernel for the output and down projections (5,120
+# rows of weights) takes the step from 16.9 to 14.1 ms; with the qkv and gate/up products through it as well 14.2.
+# Hence the limit on the rows of the weight matrix; LLMP_B200_STREAM_GEMM=0 turns the kernel off,
+# LLMP_B200_STREAM_MAX_N moves the limit.
+STREAM_GEMM = os.environ.get("LLMP_B200_STREAM_GEMM", "1") == "1"
+STREAM_MAX_N = int(os.environ.get("LLMP_B200_STREAM_MAX_N", "5120"))
 
 register_bf16_kernel(_stream)
 register_bf16_kernel(_tensor_memory)
