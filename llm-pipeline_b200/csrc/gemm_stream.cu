@@ -1,10 +1,10 @@
-// Y[M, N] = X[M, K] * W[N, K]^T for the few rows of a decode step (M <= 16), bound by reading W once from HBM:
+// Y[M, N] = X[M, K] * W[N, K]^T for the few rows of a decode step (M <= 64), bound by reading W once from HBM:
 // one persistent block per SM streams its share of W through a ring of TMA boxes.
 //
 // The rows of W are dealt out evenly: block b owns the contiguous rows [b * per, (b + 1) * per) and walks them
 // in chunks of RB <= 128 rows; for each chunk it walks K in steps of KB blocks of 64 elements. A ring stage
 // holds one step: a box of W (RB rows x KB x 64 elements, as KB planes of rows of 128 bytes in the 128-byte
-// swizzle) and the matching box of X (8 or 16 rows). A load warp fills the ring as slots come free and runs
+// swizzle) and the matching box of X (8, 16, 32 or 64 rows). A load warp fills the ring as slots come free and runs
 // ahead across chunks; four compute warps take the stages of a chunk in turn (warp w the steps w, w + 4, ...
 // of K), multiply with mma.sync m16n8k16 (the rows of W on the 16-row side, the rows of X on the
 // 8-column side, float32 accumulators in registers) and hand the slot back. At the end of a chunk the four
@@ -37,7 +37,8 @@ struct StreamParams {
     int per;              // rows of W per block
     int RB;               // rows of W per chunk and box
     int KB;               // 64-element blocks of K per stage
-    int MB;               // rows of the X box: 8 or 16
+    int MB;               // rows of the X box: 8 NT
+    int part_rows;        // rows of W per warp in the buffer of partial sums: 16 MT
     int stages;
     int out_f32;
     int* error_flag;
@@ -84,7 +85,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // a stage: KB planes of RB lines of W, then KB planes of MB lines of X, rounded up to 1024 bytes
     const uint32_t w_bytes = (uint32_t)p.RB * 128 * p.KB, x_bytes = (uint32_t)p.MB * 128 * p.KB;
     const uint32_t stage_bytes = (w_bytes + x_bytes + 1023u) & ~1023u;
-    float* part = reinterpret_cast<float*>(ring + (size_t)p.stages * stage_bytes);   // [warps][RB][8 NT]
+    float* part = reinterpret_cast<float*>(ring + (size_t)p.stages * stage_bytes);   // [warps][16 MT][8 NT + 1]
 
     const int row_begin = blockIdx.x * p.per;
     int row_end = row_begin + p.per;
@@ -196,7 +197,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    float* base = part + ((size_t)warp * GS_MAX_RB + mt * 16 + g) * pstride + j * 8 + 2 * t;
+                    float* base = part + ((size_t)warp * p.part_rows + mt * 16 + g) * pstride + j * 8 + 2 * t;
                     base[0] = acc[mt][j][0];
                     base[1] = acc[mt][j][1];
                     base[8 * pstride] = acc[mt][j][2];
@@ -212,7 +213,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const int m = e / rows, row = e - m * rows;     // consecutive threads store consecutive columns of Y
                 float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * GS_MAX_RB + row) * pstride + m];
+                for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * p.part_rows + row) * pstride + m];
                 if (p.out_f32) reinterpret_cast<float*>(p.Y)[(size_t)m * p.ldy + n0 + row] = v;
                 else reinterpret_cast<bf16*>(p.Y)[(size_t)m * p.ldy + n0 + row] = __float2bfloat16_rn(v);
             }
@@ -267,18 +268,7 @@ static int stream_map(const void* ptr, long rows, long k, long ld, int box_rows,
     return 0;
 }
 
-// Shapes this kernel takes.
-LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) {
-    return M > 0 && M <= 16 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
-}
-
-// X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; M <= 16, K a multiple of 64.
-LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
-                              long ldy, int* error_flag, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    LLMP_REQUIRE(llmp_gemm_stream_supports(M, N, K, ldx, ldw), "gemm_stream: M=%d (at most 16), K=%d (a multiple of 64) or the row strides are not taken", M, K);
-    LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_stream: operands must be 16-byte aligned");
-    LLMP_REQUIRE(error_flag != nullptr, "gemm_stream: an error flag in device memory is required");
+static int gs_sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -286,32 +276,66 @@ LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dty
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
+    return sms;
+}
+
+// How a product is laid out: rows per block and chunk, blocks of K per stage, ring depth. False when the shape is
+// not taken.
+struct StreamPlan {
+    int per, grid, rb, nt, mt, kb, stages;
+    size_t stage_bytes, part_bytes, smem;
+};
+
+static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out) {
+    if (!(M > 0 && M <= 64 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0)) return false;
+    const int sms = gs_sm_count();
+    StreamPlan q;
+    // rows per block: an even share
+    q.per = (N + sms - 1) / sms;
+    if (q.per < 8) q.per = 8;
+    q.grid = (N + q.per - 1) / q.per;
+    const int chunks = (q.per + GS_MAX_RB - 1) / GS_MAX_RB;
+    q.rb = (q.per + chunks - 1) / chunks;
+    q.nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+    q.mt = (q.rb + 15) / 16 <= 2 ? 2 : ((q.rb + 15) / 16 <= 4 ? 4 : 8);       // the kernel's template steps
+    if (q.mt * q.nt > 16) return false;      // more than 128 accumulator registers a thread are not built
+    // blocks of K per stage: stages of about 16 KB, KB a power of two that divides K / 64. KB decides which warp
+    // adds which part of K, so it is chosen from N and K alone: the result of a row of X must not depend on M.
+    q.kb = 1;
+    while (q.kb < 8 && (long)(q.rb + 16) * 128 * q.kb * 2 <= 24 * 1024 && (K / 64) % (q.kb * 2) == 0) q.kb *= 2;
+    q.stage_bytes = ((size_t)(q.rb + 8 * q.nt) * 128 * q.kb + 1023) / 1024 * 1024;
+    q.part_bytes = (size_t)GS_CWARPS * q.mt * 16 * (8 * q.nt + 1) * sizeof(float);
+    int stages = (int)((GS_SMEM_BUDGET - q.part_bytes) / q.stage_bytes);
+    if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
+    q.stages = stages / GS_CWARPS * GS_CWARPS;                   // every compute warp has its own slots
+    if (q.stages < GS_CWARPS) return false;
+    q.smem = (size_t)q.stages * q.stage_bytes + q.part_bytes + 2048;   // 1024 for the alignment, 1024 for reads past the last stage
+    *out = q;
+    return true;
+}
+
+// Shapes this kernel takes: M <= 64 rows of X (more than 16 only for narrow outputs), K a multiple of 64, rows of 16
+// bytes' alignment.
+LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) {
+    StreamPlan q;
+    return stream_plan(M, N, K, ldx, ldw, &q) ? 1 : 0;
+}
+
+// X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; shapes as llmp_gemm_stream_supports says.
+LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                              long ldy, int* error_flag, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    StreamPlan q;
+    LLMP_REQUIRE(stream_plan(M, N, K, ldx, ldw, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
+    LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_stream: operands must be 16-byte aligned");
+    LLMP_REQUIRE(error_flag != nullptr, "gemm_stream: an error flag in device memory is required");
     StreamParams p;
     p.Y = Y; p.ldy = ldy; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == LLMP_F32; p.error_flag = error_flag;
-    // rows per block: an even share
-    int per = (N + sms - 1) / sms;
-    if (per < 8) per = 8;
-    p.per = per;
-    const int grid = (N + per - 1) / per;
-    const int chunks = (per + GS_MAX_RB - 1) / GS_MAX_RB;
-    const int rb = (per + chunks - 1) / chunks;
-    p.RB = rb;
-    p.MB = M <= 8 ? 8 : 16;
-    // blocks of K per stage: stages of about 16 KB, KB a power of two that divides K / 64
-    int kb = 1;
-    while (kb < 8 && (long)(rb + p.MB) * 128 * kb * 2 <= 24 * 1024 && (K / 64) % (kb * 2) == 0) kb *= 2;
-    p.KB = kb;
-    const size_t stage_bytes = ((size_t)(rb + p.MB) * 128 * kb + 1023) / 1024 * 1024;
-    const size_t part_bytes = (size_t)GS_CWARPS * GS_MAX_RB * (8 * (M <= 8 ? 1 : 2) + 1) * sizeof(float);
-    int stages = (int)((GS_SMEM_BUDGET - part_bytes) / stage_bytes);
-    if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
-    stages = stages / GS_CWARPS * GS_CWARPS;                     // every compute warp has its own slots
-    LLMP_REQUIRE(stages >= GS_CWARPS, "gemm_stream: a stage of %zu bytes does not fit %d times", stage_bytes, GS_CWARPS);
-    p.stages = stages;
-    const size_t smem = (size_t)stages * stage_bytes + part_bytes + 2048;      // 1024 for the alignment, 1024 for reads past the last stage
+    p.per = q.per; p.RB = q.rb; p.MB = 8 * q.nt; p.KB = q.kb; p.part_rows = q.mt * 16; p.stages = q.stages;
+    const int grid = q.grid, rb = q.rb, kb = q.kb, nt = q.nt, mt = q.mt;
+    const size_t smem = q.smem;
     CUtensorMap map_w, map_x;
     if (stream_map(W, N, K, ldw, rb, kb, &map_w) || stream_map(X, M, K, ldx, p.MB, kb, &map_x)) return 1;
-    const int mt = (rb + 15) / 16;
     cudaError_t launched = cudaSuccess;
 #define GS_LAUNCH(MT, NT)                                                                                     \
     do {                                                                                                      \
@@ -319,10 +343,12 @@ LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dty
         launched = llmp_launch_dependent(gemm_stream_kernel<MT, NT>, dim3(grid), dim3(GS_THREADS), smem, stream, \
                                          map_w, map_x, p);                                                    \
     } while (0)
-    if (M <= 8) {
-        if (mt <= 2) GS_LAUNCH(2, 1); else if (mt <= 4) GS_LAUNCH(4, 1); else GS_LAUNCH(8, 1);
+    if (mt == 2) {
+        if (nt == 1) GS_LAUNCH(2, 1); else if (nt == 2) GS_LAUNCH(2, 2); else if (nt == 4) GS_LAUNCH(2, 4); else GS_LAUNCH(2, 8);
+    } else if (mt == 4) {
+        if (nt == 1) GS_LAUNCH(4, 1); else if (nt == 2) GS_LAUNCH(4, 2); else GS_LAUNCH(4, 4);
     } else {
-        if (mt <= 2) GS_LAUNCH(2, 2); else if (mt <= 4) GS_LAUNCH(4, 2); else GS_LAUNCH(8, 2);
+        if (nt == 1) GS_LAUNCH(8, 1); else GS_LAUNCH(8, 2);
     }
 #undef GS_LAUNCH
     if (launched != cudaSuccess) {

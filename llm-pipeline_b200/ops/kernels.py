@@ -265,7 +265,7 @@ def gemm_stream_supports(M: int, N: int, K: int, ldx: int, ldw: int) -> bool:
 
 
 def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T for at most 16 rows: one persistent block per SM streams its share of
+    """out[M, N] = x[M, K] @ w[N, K]^T for at most 64 rows (see ``gemm_stream_supports``): one persistent block per SM streams its share of
     ``w`` through a ring of TMA boxes; bfloat16 operands, bfloat16 or float32 output, K a multiple of 64."""
     M, K = x.shape
     N = w.shape[0]

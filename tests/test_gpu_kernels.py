@@ -190,7 +190,8 @@ def test_gemm_tcgen05(out_dtype, M, N, Kd):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (5, 6144, 1024), (16, 1000, 192), (9, 331, 128),
-                                    (3, 24576, 512), (8, 40000, 256), (2, 7, 64)])
+                                    (3, 24576, 512), (8, 40000, 256), (2, 7, 64), (17, 4096, 1024), (32, 5120, 512),
+                                    (33, 1000, 192), (64, 4096, 128), (50, 4736, 128)])
 def test_gemm_stream(M, N, Kd, out_dtype):
     """The weight-streaming kernel: row counts that give ragged shares per block, one and two 8-row tiles of
     x, several chunks of rows per block (N = 40000), fewer rows than blocks."""
@@ -198,6 +199,7 @@ def test_gemm_stream(M, N, Kd, out_dtype):
     x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=30), rnd(N, Kd, dtype=torch.bfloat16, seed=31)
     want = x.double() @ w.double().t()
     out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    assert k_.gemm_stream_supports(M, N, Kd, Kd, Kd)
     k_.gemm_stream(x, w, out)
     k_.check_error_flag()
     scale = float(want.abs().max())
@@ -206,6 +208,15 @@ def test_gemm_stream(M, N, Kd, out_dtype):
     single = torch.empty(1, N, dtype=out_dtype, device=DEV)
     k_.gemm_stream(x[M - 1:M], w, single)
     assert torch.equal(single[0], out[M - 1])
+
+
+def test_gemm_stream_refuses_what_it_does_not_take():
+    k_ = K()
+    for M, N, Kd in [(64, 24576, 4096), (8, 100, 72), (65, 64, 64)]:      # too many accumulators, K no multiple of 64, rows
+        assert not k_.gemm_stream_supports(M, N, Kd, Kd, Kd)
+        x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, seed=2)
+        with pytest.raises(k_.KernelError, match="gemm_stream"):
+            k_.gemm_stream(x, w, torch.empty(M, N, dtype=torch.bfloat16, device=DEV))
 
 
 def attention_reference(q, k, v, window, scale):
