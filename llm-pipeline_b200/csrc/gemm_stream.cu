@@ -29,6 +29,7 @@
 #define GS_MAX_RB 128
 #define GS_MAX_STAGES 24
 #define GS_SMEM_BUDGET (200 * 1024)
+#define GS_STAGE_LIMIT (48 * 1024)                // a stage may grow to half of this before KB stops doubling
 
 struct StreamParams {
     void* Y;
@@ -299,10 +300,12 @@ static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out
     q.nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
     q.mt = (q.rb + 15) / 16 <= 2 ? 2 : ((q.rb + 15) / 16 <= 4 ? 4 : 8);       // the kernel's template steps
     if (q.mt * q.nt > 16) return false;      // more than 128 accumulator registers a thread are not built
-    // blocks of K per stage: stages of about 16 KB, KB a power of two that divides K / 64. KB decides which warp
+    // blocks of K per stage: as many as leave at least four stages (longer pieces of a weight row per box read
+    // DRAM better: the head product went from 5.7 to 6.3 TB/s with two blocks instead of one), KB a power of two
+    // that divides K / 64. KB decides which warp
     // adds which part of K, so it is chosen from N and K alone: the result of a row of X must not depend on M.
     q.kb = 1;
-    while (q.kb < 8 && (long)(q.rb + 16) * 128 * q.kb * 2 <= 24 * 1024 && (K / 64) % (q.kb * 2) == 0) q.kb *= 2;
+    while (q.kb < 8 && (long)(q.rb + 16) * 128 * q.kb * 2 <= GS_STAGE_LIMIT && (K / 64) % (q.kb * 2) == 0) q.kb *= 2;
     q.stage_bytes = ((size_t)(q.rb + 8 * q.nt) * 128 * q.kb + 1023) / 1024 * 1024;
     q.part_bytes = (size_t)GS_CWARPS * q.mt * 16 * (8 * q.nt + 1) * sizeof(float);
     int stages = (int)((GS_SMEM_BUDGET - q.part_bytes) / q.stage_bytes);
