@@ -28,7 +28,7 @@
 #define GS_THREADS ((GS_CWARPS + 1) * 32)
 #define GS_MAX_RB 128
 #define GS_MAX_STAGES 24
-#define GS_SMEM_BUDGET (200 * 1024)
+#define GS_SMEM_BUDGET (223 * 1024)                // ring and partial sums; 2 KB more go to alignment and over-reads
 #define GS_STAGE_LIMIT (48 * 1024)                // a stage may grow to half of this before KB stops doubling
 
 struct StreamParams {
@@ -109,15 +109,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == GS_CWARPS) {
         if (lane == 0) {
-            // Stage (chunk, ks) belongs to compute warp w = ks % 4 and is that warp's j-th stage; it lives in slot
-            // 4 (j % S4) + w. A slot is thus filled for one warp only, which sees every phase of its barrier in turn.
-            const int S4 = p.stages / GS_CWARPS;
+            // Stage (chunk, ks) belongs to compute warp w = ks % 4 and is that warp's j-th stage; warp w owns the ring
+            // slots w, w + 4, ... and the stage lives in the (j mod their number)-th of them. A slot is thus filled for
+            // one warp only, which sees every phase of its barrier in turn.
             auto slot_of = [&](int chunk, int ks, int& round) {
                 const int w = ks % GS_CWARPS;
                 const int per_chunk = (ksteps - w + GS_CWARPS - 1) / GS_CWARPS;     // stages of warp w in a chunk
+                const int mine = (p.stages - w + GS_CWARPS - 1) / GS_CWARPS;        // ring slots of warp w: w, w + 4, ...
                 const int j = chunk * per_chunk + ks / GS_CWARPS;
-                round = j / S4;
-                return GS_CWARPS * (j % S4) + w;
+                round = j / mine;
+                return GS_CWARPS * (j % mine) + w;
             };
             // the first round of every slot is filled with boxes of W at once; the boxes of X follow after pdl_wait()
             int first_later = total;                             // first stage (in issue order) of a later round
@@ -158,13 +159,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
         const int steps16 = 4 * p.KB;                            // 16-element K steps per stage
-        const int S4 = p.stages / GS_CWARPS;
+        const int mine = (p.stages - warp + GS_CWARPS - 1) / GS_CWARPS;      // ring slots of this warp: warp, warp + 4, ...
         int j = 0;                                               // stages this warp has taken
         for (int chunk = 0; chunk < chunks; ++chunk) {
             // warp w takes the chunk's stages w, w + 4, ... whole: a wait and a hand-back per stage and warp
             for (int ks = warp; ks < ksteps; ks += GS_CWARPS, ++j) {
-                const int slot = GS_CWARPS * (j % S4) + warp;    // this warp's j-th stage: see the load warp
-                mbar_wait(&full_bar[slot], (uint32_t)((j / S4) & 1), p.error_flag);
+                const int slot = GS_CWARPS * (j % mine) + warp;  // this warp's j-th stage: see the load warp
+                mbar_wait(&full_bar[slot], (uint32_t)((j / mine) & 1), p.error_flag);
                 const unsigned char* stage = ring + (size_t)slot * stage_bytes;
                 for (int s = 0; s < steps16; ++s) {
                     const int w_line = (s >> 2) * p.RB;                              // first line of this 64-element block of W
@@ -310,8 +311,8 @@ static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out
     q.part_bytes = (size_t)GS_CWARPS * q.mt * 16 * (8 * q.nt + 1) * sizeof(float);
     int stages = (int)((GS_SMEM_BUDGET - q.part_bytes) / q.stage_bytes);
     if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
-    q.stages = stages / GS_CWARPS * GS_CWARPS;                   // every compute warp has its own slots
-    if (q.stages < GS_CWARPS) return false;
+    q.stages = stages;
+    if (q.stages < GS_CWARPS) return false;                      // every compute warp has slots of its own
     q.smem = (size_t)q.stages * q.stage_bytes + q.part_bytes + 2048;   // 1024 for the alignment, 1024 for reads past the last stage
     *out = q;
     return true;

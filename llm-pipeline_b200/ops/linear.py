@@ -35,7 +35,7 @@ def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Op
         return None
     if not kernels.gemm_stream_supports(M, weight.shape[0], K, x.stride(0), weight.stride(0)):
         return None
-    if weight.shape[0] > STREAM_MAX_N:
+    if M > 8 and weight.shape[0] > STREAM_MAX_N:
         return None
     out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
     return kernels.gemm_stream(x, weight, out)
@@ -90,14 +90,13 @@ def _tensor_memory_prefill(x: torch.Tensor, weight: torch.Tensor, out_dtype: tor
 OWN_PREFILL_GEMM = os.environ.get("LLMP_B200_OWN_PREFILL_GEMM", "0") == "1"
 PREFILL_TC_MIN_ROWS = 1024
 
-# Measured on a B200 (Qwen3-8B shapes, replayed decode graph, ms per step): the streaming kernel for the output and
-# down projections (4,096 rows of weights each) and the library product for the rest 4.07 at 8 rows, 3.80 at 4,
-# 4.83 at 16; without it (skinny kernel, tcgen05 split-K) 4.23, 3.96, 4.90; the streaming kernel for every product
-# 4.21 at 8 rows: for the qkv, gate/up and head products (6,144 rows and more) the library reads the weights
-# somewhat faster. At the Qwen3-32B shapes (8 rows) the streaming kernel for the output and down projections (5,120
-# rows of weights) takes the step from 16.9 to 14.1 ms; with the qkv and gate/up products through it as well 14.2.
-# Hence the limit on the rows of the weight matrix; LLMP_B200_STREAM_GEMM=0 turns the kernel off,
-# LLMP_B200_STREAM_MAX_N moves the limit.
+# Measured on a B200 (Qwen3-8B shapes, replayed decode graph, ms per step): every product of the step through the
+# streaming kernel 3.34 at 1 row, 3.64 at 4, 3.95 at 8; the streaming kernel only for the output and down projections
+# (5,120 weight rows at most) and the library product for qkv, gate/up and the head 3.53, 3.82, 4.10; without the
+# streaming kernel (skinny kernel, tcgen05 split-K, library) 3.66, 3.96, 4.23. At 16 rows the wide products are
+# faster through the library (4.67 against 4.84 all streaming). Qwen3-32B shapes at 8 rows: 13.9 all streaming, 14.3
+# narrow products only, 16.9 without; Qwen3-0.6B: 1.32, 1.40, 1.35. Hence: up to 8 rows every product streams, from 9
+# to 16 rows those with at most STREAM_MAX_N weight rows. LLMP_B200_STREAM_GEMM=0 turns the kernel off.
 STREAM_GEMM = os.environ.get("LLMP_B200_STREAM_GEMM", "1") == "1"
 STREAM_MAX_N = int(os.environ.get("LLMP_B200_STREAM_MAX_N", "5120"))
 # More than 16 rows make the kernel compute-bound on its four mma.sync warps (batch 64: 9.57 ms per step against 7.72
