@@ -8,8 +8,9 @@
 // ahead across chunks; four compute warps take the stages of a chunk in turn (warp w the steps w, w + 4, ...
 // of K), multiply with mma.sync m16n8k16 (the rows of W on the 16-row side, the rows of X on the
 // 8-column side, float32 accumulators in registers) and hand the slot back. At the end of a chunk the four
-// warps' sums are added in warp order in shared memory and stored. The order of the additions depends on K
-// alone, so a row of X gives the same result whatever else is in X.
+// warps' sums are added in warp order in shared memory and stored. A ring slot belongs to one compute warp (warp
+// w owns the slots w, w + 4, ...), so a warp sees every phase of its barriers in turn. The order of the additions
+// depends on N and K alone, so a row of X gives the same result whatever else is in X.
 //
 // As a dependent launch: W is constant, X may still be in the making by the kernel before this one. The load
 // warp fills the whole ring with boxes of W, then waits for that kernel, then adds the boxes of X.
