@@ -39,7 +39,10 @@ def load_reference(root: str):
 
 
 def main() -> int:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        print("usage: make_golden.py <checkout of DavidAkinpelu/llm-pipeline>", file=sys.stderr)
+        return 2
+    root = sys.argv[1]
     ref = load_reference(root)
     torch.manual_seed(0)
     summary = {}
