@@ -255,9 +255,9 @@ int llmp_launch_decode_mma(const void* q, long q_stride, const void* pages, cons
 
 // The streaming kernel for head size 128 (attention_decode_tma.cu).
 bool llmp_decode_tma_supports(int nq, int nkv, int d, int page_size);
-int llmp_launch_decode_tma(const void* q, long q_stride, const void* pages, int num_pages, const int* block_tables,
-                           int table_stride, const int* ctx_len, int R, int max_splits, int nq, int nkv, int page_size,
-                           int window, float scale, float* part_o, float* part_ml, int* error_flag, cudaStream_t stream);
+int llmp_launch_decode_tma(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
+                           const int* block_tables, int table_stride, const int* ctx_len, int R, int max_splits, int nq,
+                           int nkv, int page_size, int window, float scale, int* error_flag, cudaStream_t stream);
 
 // Scratch floats the decode kernel needs for R rows whose longest context is max_ctx keys.
 LLMP_API long llmp_decode_scratch_floats(int R, int nq, int d, int max_ctx) {
@@ -308,9 +308,9 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
                                                              p.max_splits);
     } else {
         if (error_flag != nullptr && num_pages > 0 && llmp_decode_tma_supports(nq, nkv, d, page_size)) {
-            if (llmp_launch_decode_tma(q, q_stride, pages, num_pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq,
-                                       nkv, page_size, window, scale, p.part_o, p.part_ml, error_flag, stream))
-                return 1;
+            // the streaming kernel writes the finished output itself: no partial results, no merge
+            return llmp_launch_decode_tma(q, q_stride, out, out_stride, pages, num_pages, block_tables, table_stride, ctx_len, R,
+                                          p.max_splits, nq, nkv, page_size, window, scale, error_flag, stream);
         } else if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,
                                           page_size, window, scale, p.part_o, p.part_ml, stream))
             return 1;
