@@ -12,6 +12,10 @@
 // w owns the slots w, w + 4, ...), so a warp sees every phase of its barriers in turn. The order of the additions
 // depends on N and K alone, so a row of X gives the same result whatever else is in X.
 //
+// With glu_rows = I the matrix holds the I gate rows and then the I up rows of a SwiGLU feed-forward: a block owns
+// the same rows of both halves, walks its gate chunks, then its up chunks, keeps the gate sums in shared memory
+// and stores silu(gate) * up (float32 inside): the activation never goes through global memory as two halves.
+//
 // As a dependent launch: W is constant, X may still be in the making by the kernel before this one. The load
 // warp fills the whole ring with boxes of W, then waits for that kernel, then adds the boxes of X.
 //
@@ -43,6 +47,7 @@ struct StreamParams {
     int part_rows;        // rows of W per warp in the buffer of partial sums: 16 MT
     int stages;
     int out_f32;
+    int glu_rows;         // 0, or I: W is [gate rows; up rows] of I rows each and Y[m, i] = silu(gate_i . x_m) * (up_i . x_m)
     int* error_flag;
 };
 
@@ -89,12 +94,18 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t stage_bytes = (w_bytes + x_bytes + 1023u) & ~1023u;
     float* part = reinterpret_cast<float*>(ring + (size_t)p.stages * stage_bytes);   // [warps][16 MT][8 NT + 1]
 
+    // the rows of this block: [row_begin, row_end) of W, or with glu_rows of each of its two halves
+    const int row_limit = p.glu_rows ? p.glu_rows : p.N;
     const int row_begin = blockIdx.x * p.per;
     int row_end = row_begin + p.per;
-    if (row_end > p.N) row_end = p.N;
-    const int chunks = row_begin < row_end ? (row_end - row_begin + p.RB - 1) / p.RB : 0;
+    if (row_end > row_limit) row_end = row_limit;
+    const int half_chunks = row_begin < row_end ? (row_end - row_begin + p.RB - 1) / p.RB : 0;
+    const int chunks = p.glu_rows ? 2 * half_chunks : half_chunks;
     const int ksteps = p.K / (64 * p.KB);                       // stages per chunk
     const int total = chunks * ksteps;
+    // first row of W of chunk c: the up chunks follow the gate chunks
+    auto chunk_row = [&](int c) { return c < half_chunks ? row_begin + c * p.RB : p.glu_rows + row_begin + (c - half_chunks) * p.RB; };
+    float* gate = part + (size_t)GS_CWARPS * p.part_rows * (8 * NT + 1);     // [rows of the block][8 NT]: the gate sums (glu_rows only)
 
     if (tid == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -132,7 +143,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     break;
                 }
                 mbar_expect_tx(&full_bar[slot], w_bytes + x_bytes);
-                gs_tma_load_3d(ring + (size_t)slot * stage_bytes, &map_w, 0, row_begin + chunk * p.RB, ks * p.KB, &full_bar[slot]);
+                gs_tma_load_3d(ring + (size_t)slot * stage_bytes, &map_w, 0, chunk_row(chunk), ks * p.KB, &full_bar[slot]);
             }
             pdl_wait();
             for (int i = 0; i < first_later; ++i) {
@@ -148,7 +159,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (round > 0) mbar_wait(&empty_bar[slot], (uint32_t)((round - 1) & 1), p.error_flag);
                 mbar_expect_tx(&full_bar[slot], w_bytes + x_bytes);
                 unsigned char* stage = ring + (size_t)slot * stage_bytes;
-                gs_tma_load_3d(stage, &map_w, 0, row_begin + chunk * p.RB, ks * p.KB, &full_bar[slot]);
+                gs_tma_load_3d(stage, &map_w, 0, chunk_row(chunk), ks * p.KB, &full_bar[slot]);
                 gs_tma_load_3d(stage + w_bytes, &map_x, 0, 0, ks * p.KB, &full_bar[slot]);
             }
         }
@@ -209,7 +220,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
             }
             asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CWARPS * 32) : "memory");
-            const int n0 = row_begin + chunk * p.RB;
+            const int sub = chunk < half_chunks ? chunk : chunk - half_chunks;
+            const int n0 = row_begin + sub * p.RB;               // first column of Y of this chunk
             int rows = row_end - n0;
             if (rows > p.RB) rows = p.RB;
             for (int e = tid; e < rows * p.M; e += GS_CWARPS * 32) {
@@ -217,6 +229,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * p.part_rows + row) * pstride + m];
+                if (p.glu_rows) {
+                    float* kept = gate + (size_t)(sub * p.RB + row) * (8 * NT) + m;
+                    if (chunk < half_chunks) {                   // a gate chunk: kept for the up chunk of the same rows
+                        *kept = v;
+                        continue;
+                    }
+                    const float z = *kept;
+                    v = (z / (1.f + expf(-z))) * v;
+                }
                 if (p.out_f32) reinterpret_cast<float*>(p.Y)[(size_t)m * p.ldy + n0 + row] = v;
                 else reinterpret_cast<bf16*>(p.Y)[(size_t)m * p.ldy + n0 + row] = __float2bfloat16_rn(v);
             }
@@ -289,14 +310,16 @@ struct StreamPlan {
     size_t stage_bytes, part_bytes, smem;
 };
 
-static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out) {
+static bool stream_plan(int M, int N, int K, long ldx, long ldw, int glu_rows, StreamPlan* out) {
     if (!(M > 0 && M <= 64 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0)) return false;
+    if (glu_rows && (N != 2 * glu_rows || M > 16)) return false;
     const int sms = gs_sm_count();
     StreamPlan q;
-    // rows per block: an even share
-    q.per = (N + sms - 1) / sms;
+    // rows per block: an even share (of each half with glu_rows)
+    const int share = glu_rows ? glu_rows : N;
+    q.per = (share + sms - 1) / sms;
     if (q.per < 8) q.per = 8;
-    q.grid = (N + q.per - 1) / q.per;
+    q.grid = (share + q.per - 1) / q.per;
     const int chunks = (q.per + GS_MAX_RB - 1) / GS_MAX_RB;
     q.rb = (q.per + chunks - 1) / chunks;
     q.nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
@@ -310,6 +333,7 @@ static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out
     while (q.kb < 8 && (long)(q.rb + 16) * 128 * q.kb * 2 <= GS_STAGE_LIMIT && (K / 64) % (q.kb * 2) == 0) q.kb *= 2;
     q.stage_bytes = ((size_t)(q.rb + 8 * q.nt) * 128 * q.kb + 1023) / 1024 * 1024;
     q.part_bytes = (size_t)GS_CWARPS * q.mt * 16 * (8 * q.nt + 1) * sizeof(float);
+    if (glu_rows) q.part_bytes += (size_t)chunks * q.rb * 8 * q.nt * sizeof(float);        // the gate sums of the block's rows
     int stages = (int)((GS_SMEM_BUDGET - q.part_bytes) / q.stage_bytes);
     if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
     q.stages = stages;
@@ -323,19 +347,40 @@ static bool stream_plan(int M, int N, int K, long ldx, long ldw, StreamPlan* out
 // bytes' alignment.
 LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) {
     StreamPlan q;
-    return stream_plan(M, N, K, ldx, ldw, &q) ? 1 : 0;
+    return stream_plan(M, N, K, ldx, ldw, 0, &q) ? 1 : 0;
 }
 
 // X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; shapes as llmp_gemm_stream_supports says.
+static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                              long ldy, int glu_rows, int* error_flag, cudaStream_t stream);
+
 LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
                               long ldy, int* error_flag, cudaStream_t stream) {
+    return gemm_stream_launch(X, W, Y, out_dtype, M, N, K, ldx, ldw, ldy, 0, error_flag, stream);
+}
+
+// W holds the I gate rows and then the I up rows of a SwiGLU feed-forward (N = 2 I rows of K):
+// Y[m, i] = silu(W[i] . X[m]) * (W[I + i] . X[m]), Y being [M, I]. M <= 16.
+LLMP_API int llmp_gemm_stream_swiglu_supports(int M, int I, int K, long ldx, long ldw) {
+    StreamPlan q;
+    return stream_plan(M, 2 * I, K, ldx, ldw, I, &q) ? 1 : 0;
+}
+
+LLMP_API int llmp_gemm_stream_swiglu(const void* X, const void* W, void* Y, int out_dtype, int M, int I, int K, long ldx,
+                                     long ldw, long ldy, int* error_flag, cudaStream_t stream) {
+    return gemm_stream_launch(X, W, Y, out_dtype, M, 2 * I, K, ldx, ldw, ldy, I, error_flag, stream);
+}
+
+static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                              long ldy, int glu_rows, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     StreamPlan q;
-    LLMP_REQUIRE(stream_plan(M, N, K, ldx, ldw, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
+    LLMP_REQUIRE(stream_plan(M, N, K, ldx, ldw, glu_rows, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
     LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_stream: operands must be 16-byte aligned");
     LLMP_REQUIRE(error_flag != nullptr, "gemm_stream: an error flag in device memory is required");
     StreamParams p;
     p.Y = Y; p.ldy = ldy; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == LLMP_F32; p.error_flag = error_flag;
+    p.glu_rows = glu_rows;
     p.per = q.per; p.RB = q.rb; p.MB = 8 * q.nt; p.KB = q.kb; p.part_rows = q.mt * 16; p.stages = q.stages;
     const int grid = q.grid, rb = q.rb, kb = q.kb, nt = q.nt, mt = q.mt;
     const size_t smem = q.smem;

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "llmp_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
+    "llmp_gemm_stream_swiglu": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
@@ -275,6 +276,27 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "gemm_stream takes CUDA tensors")
     _call("llmp_gemm_stream", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
           out.stride(0), error_flag().data_ptr(), _stream())
+    return out
+
+
+def gemm_stream_swiglu_supports(M: int, I: int, K: int, ldx: int, ldw: int) -> bool:
+    fn = library().llmp_gemm_stream_swiglu_supports
+    fn.argtypes = [_I, _I, _I, _L, _L]
+    fn.restype = _I
+    return bool(fn(M, I, K, ldx, ldw))
+
+
+def gemm_stream_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[m, i] = silu(x[m] . w[i]) * (x[m] . w[I + i]) for ``w_gate_up`` = [gate rows; up rows] ([2 I, K]): the
+    gate/up product of a SwiGLU feed-forward and its activation in one streaming kernel (at most 16 rows of x)."""
+    M, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    _need(x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16, "gemm_stream_swiglu takes bfloat16 operands")
+    _need(w_gate_up.shape == (2 * I, K) and out.shape == (M, I), "gemm_stream_swiglu shapes do not match")
+    _need(x.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
+    _need(x.is_cuda and w_gate_up.is_cuda and out.is_cuda, "gemm_stream_swiglu takes CUDA tensors")
+    _call("llmp_gemm_stream_swiglu", _ptr(x), _ptr(w_gate_up), _ptr(out), dtype_code(out.dtype), M, I, K, x.stride(0),
+          w_gate_up.stride(0), out.stride(0), error_flag().data_ptr(), _stream())
     return out
 
 

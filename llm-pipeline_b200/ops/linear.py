@@ -41,6 +41,22 @@ def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Op
     return kernels.gemm_stream(x, weight, out)
 
 
+def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """silu(x gate^T) * (x up^T) for ``w_gate_up`` = [gate rows; up rows] in one streaming kernel, where that kernel
+    serves the gate/up product anyway (bfloat16, at most 8 rows); None otherwise: the caller then takes the product
+    and the activation kernel."""
+    M, K = x.shape
+    if not STREAM_GEMM or x.dtype != torch.bfloat16 or not 0 < M <= 8 or x.stride(1) != 1 or w_gate_up.stride(1) != 1:
+        return None
+    if x.data_ptr() % 16 or w_gate_up.data_ptr() % 16 or w_gate_up.shape[0] % 2:
+        return None
+    I = w_gate_up.shape[0] // 2
+    if not kernels.gemm_stream_swiglu_supports(M, I, K, x.stride(0), w_gate_up.stride(0)):
+        return None
+    out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    return kernels.gemm_stream_swiglu(x, w_gate_up, out)
+
+
 def _tensor_memory(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """The tcgen05 kernel (TMA, accumulator in tensor memory, cluster split-K) for at most 16 rows of a decode
     step against a long K, where it reads the weights faster than the library product does."""

@@ -9,7 +9,7 @@ from typing import Dict
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import gate_up_swiglu, linear
 from ..weights.source import ParamSpec
 from .base import FeedForward, TensorGetter
 from .registry import register_feed_forward
@@ -35,7 +35,9 @@ class SwiGLU(FeedForward):
         self.w_down = get(f"{p}.down_proj.weight", "matrix").contiguous()
 
     def forward(self, x: torch.Tensor, ctx):
-        gate_up = linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.swiglu(gate_up, act)
+        act = gate_up_swiglu(x, self.w_gate_up)          # the few rows of a decode step: product and activation in one kernel
+        if act is None:
+            gate_up = linear(x, self.w_gate_up)
+            act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.swiglu(gate_up, act)
         return linear(act, self.w_down), None

@@ -210,6 +210,24 @@ def test_gemm_stream(M, N, Kd, out_dtype):
     assert torch.equal(single[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,I,Kd", [(1, 100, 64), (8, 12288, 4096), (5, 331, 128), (16, 3072, 1024), (3, 25600, 256)])
+def test_gemm_stream_swiglu(M, I, Kd):
+    """The fused gate/up product and activation: ragged shares per block, several chunks of rows per half."""
+    k_ = K()
+    x = rnd(M, Kd, dtype=torch.bfloat16, seed=40)
+    w = rnd(2 * I, Kd, dtype=torch.bfloat16, seed=41, scale=0.5)
+    assert k_.gemm_stream_swiglu_supports(M, I, Kd, Kd, Kd)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    k_.gemm_stream_swiglu(x, w, out)
+    k_.check_error_flag()
+    y = x.double() @ w.double().t()
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    assert torch.allclose(out.double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
+    single = torch.empty(1, I, dtype=torch.bfloat16, device=DEV)
+    k_.gemm_stream_swiglu(x[M - 1:M], w, single)
+    assert torch.equal(single[0], out[M - 1])
+
+
 def test_gemm_stream_refuses_what_it_does_not_take():
     k_ = K()
     for M, N, Kd in [(64, 24576, 4096), (8, 100, 72), (65, 64, 64)]:      # too many accumulators, K no multiple of 64, rows
