@@ -267,7 +267,7 @@ struct StreamMapKeyHash {
 
 // A [rows, K] bfloat16 row-major matrix with row pitch ld, seen as {64 elements, rows, K / 64 blocks} and read in
 // boxes of {64, box_rows, box_kb}: in shared memory box_kb planes of box_rows lines of 128 bytes.
-static int stream_map(const void* ptr, long rows, long k, long ld, int box_rows, int box_kb, CUtensorMap* out) {
+int llmp_stream_tensor_map(const void* ptr, long rows, long k, long ld, int box_rows, int box_kb, CUtensorMap* out) {
     static std::unordered_map<StreamMapKey, CUtensorMap, StreamMapKeyHash> cache;
     static std::mutex lock;
     const StreamMapKey key{ptr, rows, k, ld, box_rows, box_kb};
@@ -292,7 +292,7 @@ static int stream_map(const void* ptr, long rows, long k, long ld, int box_rows,
     return 0;
 }
 
-static int gs_sm_count() {
+int llmp_sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -313,7 +313,7 @@ struct StreamPlan {
 static bool stream_plan(int M, int N, int K, long ldx, long ldw, int glu_rows, StreamPlan* out) {
     if (!(M > 0 && M <= 64 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0)) return false;
     if (glu_rows && (N != 2 * glu_rows || M > 16)) return false;
-    const int sms = gs_sm_count();
+    const int sms = llmp_sm_count();
     StreamPlan q;
     // rows per block: an even share (of each half with glu_rows)
     const int share = glu_rows ? glu_rows : N;
@@ -385,7 +385,7 @@ static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dty
     const int grid = q.grid, rb = q.rb, kb = q.kb, nt = q.nt, mt = q.mt;
     const size_t smem = q.smem;
     CUtensorMap map_w, map_x;
-    if (stream_map(W, N, K, ldw, rb, kb, &map_w) || stream_map(X, M, K, ldx, p.MB, kb, &map_x)) return 1;
+    if (llmp_stream_tensor_map(W, N, K, ldw, rb, kb, &map_w) || llmp_stream_tensor_map(X, M, K, ldx, p.MB, kb, &map_x)) return 1;
     cudaError_t launched = cudaSuccess;
 #define GS_LAUNCH(MT, NT)                                                                                     \
     do {                                                                                                      \

@@ -117,3 +117,18 @@ __device__ __forceinline__ void tma_load_page_box(void* smem_dst, const CUtensor
         ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(token), "r"(kvh), "r"(kv), "r"(page)
         : "memory");
 }
+
+// Tensor map over a [rows, K] bfloat16 row-major matrix with row pitch ld, seen as {64 elements, rows, K / 64
+// blocks} and read in boxes of {64, box_rows, box_kb}: in shared memory box_kb planes of box_rows lines of 128 bytes
+// in the 128-byte swizzle; cached per matrix (gemm_stream.cu).
+int llmp_stream_tensor_map(const void* ptr, long rows, long k, long ld, int box_rows, int box_kb, CUtensorMap* out);
+
+// Number of SMs of the current device (gemm_stream.cu).
+int llmp_sm_count();
+
+// Three-dimensional box into shared memory.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}

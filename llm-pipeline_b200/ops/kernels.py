@@ -45,6 +45,7 @@ _SIGNATURES = {
     "llmp_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream_swiglu": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
+    "llmp_gemm_stream_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
@@ -275,6 +276,27 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "gemm_stream takes CUDA tensors")
     _call("llmp_gemm_stream", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
+          out.stride(0), error_flag().data_ptr(), _stream())
+    return out
+
+
+def gemm_stream_tc_supports(M: int, N: int, K: int, ldx: int, ldw: int) -> bool:
+    fn = library().llmp_gemm_stream_tc_supports
+    fn.argtypes = [_I, _I, _I, _L, _L]
+    fn.restype = _I
+    return bool(fn(M, N, K, ldx, ldw))
+
+
+def gemm_stream_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for at most 64 rows: the weight stream of ``gemm_stream`` with the
+    products by tcgen05.mma and the accumulator in tensor memory; bfloat16 operands, K a multiple of 64."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_stream_tc takes bfloat16 operands")
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm shapes do not match")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands must be row-major")
+    _need(x.is_cuda and w.is_cuda and out.is_cuda, "gemm_stream_tc takes CUDA tensors")
+    _call("llmp_gemm_stream_tc", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
           out.stride(0), error_flag().data_ptr(), _stream())
     return out
 

@@ -41,6 +41,23 @@ def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Op
     return kernels.gemm_stream(x, weight, out)
 
 
+def _stream_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The weight stream with tcgen05 products, for 9 to 32 rows against a very tall weight matrix (the output
+    head), where a block's share of rows fills most of the 128-row side of the MMA. Measured on a B200 against
+    the head of Qwen3-8B (151,936 x 4,096): 197 us at 16 rows and 211 at 32 (library 213 and 215); at 64 rows, and
+    for the layer's products at any row count (28 to 167 weight rows per block, so most of the 128 rows that the
+    MMA reads from shared memory are padding), it is slower than the library and is not used."""
+    M, K = x.shape
+    if not STREAM_GEMM or not 8 < M <= 32 or weight.shape[0] < STREAM_TC_MIN_N or x.stride(1) != 1 or weight.stride(1) != 1:
+        return None
+    if x.data_ptr() % 16 or weight.data_ptr() % 16 or out_dtype not in (torch.bfloat16, torch.float32):
+        return None
+    if not kernels.gemm_stream_tc_supports(M, weight.shape[0], K, x.stride(0), weight.stride(0)):
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=out_dtype, device=x.device)
+    return kernels.gemm_stream_tc(x, weight, out)
+
+
 def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
     """silu(x gate^T) * (x up^T) for ``w_gate_up`` = [gate rows; up rows] in one streaming kernel, where that kernel
     serves the gate/up product anyway (bfloat16, at most 8 rows); None otherwise: the caller then takes the product
@@ -119,7 +136,10 @@ STREAM_MAX_N = int(os.environ.get("LLMP_B200_STREAM_MAX_N", "5120"))
 # with the library product), so the limit on the rows of x stays at 16 although the kernel takes up to 64.
 STREAM_MAX_M = int(os.environ.get("LLMP_B200_STREAM_MAX_M", "16"))
 
+STREAM_TC_MIN_N = 32768
+
 register_bf16_kernel(_stream)
+register_bf16_kernel(_stream_tc)
 register_bf16_kernel(_tensor_memory)
 register_bf16_kernel(_skinny)
 register_bf16_kernel(_tensor_memory_prefill)

@@ -228,6 +228,26 @@ def test_gemm_stream_swiglu(M, I, Kd):
     assert torch.equal(single[0], out[M - 1])
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,Kd", [(1, 130, 64), (8, 4096, 4096), (17, 6144, 1024), (16, 1000, 192), (33, 331, 128),
+                                    (64, 24576, 512), (40, 40000, 256), (2, 7, 64), (64, 4096, 12288), (50, 5120, 256)])
+def test_gemm_stream_tc(M, N, Kd, out_dtype):
+    """The tcgen05 weight stream: row counts that leave a plane of W off the 1024-byte swizzle pattern (its
+    descriptor carries the phase), 16, 32 and 64 rows of x, several chunks of rows per block."""
+    k_ = K()
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=50), rnd(N, Kd, dtype=torch.bfloat16, seed=51)
+    want = x.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    assert k_.gemm_stream_tc_supports(M, N, Kd, Kd, Kd)
+    k_.gemm_stream_tc(x, w, out)
+    k_.check_error_flag()
+    scale = float(want.abs().max())
+    assert torch.allclose(out.double(), want, atol=(2e-2 if out_dtype == torch.bfloat16 else 2e-4) * scale, rtol=0)
+    single = torch.empty(1, N, dtype=out_dtype, device=DEV)
+    k_.gemm_stream_tc(x[M - 1:M], w, single)
+    assert torch.equal(single[0], out[M - 1])
+
+
 def test_gemm_stream_refuses_what_it_does_not_take():
     k_ = K()
     for M, N, Kd in [(64, 24576, 4096), (8, 100, 72), (65, 64, 64)]:      # too many accumulators, K no multiple of 64, rows
