@@ -53,6 +53,7 @@ struct DecodeTmaParams {
     int table_stride;
     int R, nq, nkv, page_size, num_pages, box_tokens, window, max_splits;
     int cluster;             // blocks per row group
+    int group_begin, group_count;   // the row groups of this launch: group_begin .. group_begin + group_count - 1
     int rounds;              // rounds of 4 * cluster key ranges that cover max_splits
     float scale;
     int* error_flag;
@@ -114,7 +115,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_pages, const
     const int G = p.nq / p.nkv;
     const int C = p.cluster;
     const int rank = C > 1 ? (int)cluster_ctarank() : 0;
-    const int num_groups = p.R * p.nkv;
+    const int num_groups = p.group_count;                        // groups are numbered from 0 within the launch
     // row groups of this block: with a cluster its own one, else blockIdx.x, blockIdx.x + grid, ...
     const int first_group = C > 1 ? (int)(blockIdx.x / (unsigned)C) : (int)blockIdx.x;
     const int group_step = C > 1 ? num_groups : (int)gridDim.x;      // a cluster has one row group only
@@ -146,7 +147,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_pages, const
             const int group = first_group + t * group_step;
             ctx_next = 0;
             if (group >= num_groups) return;
-            const int r = group / p.nkv;
+            const int r = (p.group_begin + group) / p.nkv;
             const int c = (j * C + rank) * DT_CWARPS + wi;
             ctx_next = p.ctx_len[r];
             const int* table = p.block_tables + (size_t)r * p.table_stride;
@@ -161,7 +162,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_pages, const
         unsigned v = 0;
         for (int t = 0; first_group + t * group_step < num_groups; ++t) {
             const int group = first_group + t * group_step;
-            const int kvh = group % p.nkv;
+            const int kvh = (p.group_begin + group) % p.nkv;
             for (int j = 0; j < p.rounds; ++j, ++v) {
                 const int c = (j * C + rank) * DT_CWARPS + wi;
                 const int ctx = ctx_next;
@@ -223,7 +224,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_pages, const
             const int group = first_group + t * group_step;
             ctx_next = 0;
             if (group >= num_groups) return;
-            const int r = group / p.nkv, kvh = group % p.nkv;
+            const int r = (p.group_begin + group) / p.nkv, kvh = (p.group_begin + group) % p.nkv;
             ctx_next = p.ctx_len[r];
             const bf16* q = p.q + (size_t)r * p.q_stride + (size_t)(kvh * G) * DT_D;
 #pragma unroll
@@ -234,7 +235,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_pages, const
         unsigned v = 0;
         for (int t = 0; first_group + t * group_step < num_groups; ++t) {
             const int group = first_group + t * group_step;
-            const int r = group / p.nkv, kvh = group % p.nkv;
+            const int r = (p.group_begin + group) / p.nkv, kvh = (p.group_begin + group) % p.nkv;
             const int ctx = ctx_next;
             // the query rows of the group: rows of 128 elements, piece i of the group at row i / 16
 #pragma unroll
@@ -424,47 +425,63 @@ int llmp_launch_decode_tma(const void* q, long q_stride, void* out, long out_str
     }
     const long groups = (long)R * nkv;
     LLMP_REQUIRE(groups * DT_MAX_CLUSTER < (1L << 31), "decode attention: too many rows");
-    // blocks per row group: as many (a power of two, at most 8) as keep the grid within the SMs and give every
-    // block at least one round of four key ranges
-    int cluster = 1;
-    while (cluster < DT_MAX_CLUSTER && groups * cluster * 2 <= sms && cluster * 2 * DT_CWARPS <= max_splits + DT_CWARPS - 1) cluster *= 2;
     DecodeTmaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.block_tables = block_tables; p.ctx_len = ctx_len;
     p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride; p.R = R; p.nq = nq; p.nkv = nkv;
     p.page_size = page_size; p.num_pages = num_pages; p.box_tokens = page_size < DT_STAGE_KEYS ? page_size : DT_STAGE_KEYS;
-    p.window = window; p.max_splits = max_splits; p.cluster = cluster;
-    p.rounds = (max_splits + cluster * DT_CWARPS - 1) / (cluster * DT_CWARPS);
-    p.scale = scale; p.error_flag = error_flag;
+    p.window = window; p.max_splits = max_splits; p.scale = scale; p.error_flag = error_flag;
     CUtensorMap map;
     if (llmp_pages_tensor_map(pages, nkv, page_size, num_pages, p.box_tokens, 2, &map)) return 1;
     const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + (size_t)(DT_CWARPS + 1) * DT_MAX_HEADS * DT_QSTRIDE * sizeof(bf16) +
                         (size_t)DT_CWARPS * DT_MAX_HEADS * DT_D * sizeof(float) + 1024;
     LLMP_ALLOW_SMEM(decode_attention_tma_kernel, smem);
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)(cluster > 1 ? groups * cluster : (groups < sms ? groups : sms)));
-    config.blockDim = dim3(DT_THREADS);
-    config.dynamicSmemBytes = smem;
-    config.stream = stream;
-    cudaLaunchAttribute attr[2];
-    int n = 0;
-    if (llmp_pdl_enabled()) {
-        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see pdl_wait() in the kernel
-        attr[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
-    }
-    if (cluster > 1) {
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = (unsigned)cluster;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
-        ++n;
-    }
-    config.attrs = attr;
-    config.numAttrs = n;
-    const cudaError_t launched = cudaLaunchKernelEx(&config, decode_attention_tma_kernel, map, p);
-    if (launched != cudaSuccess) {
-        llmp_set_error("decode_attention_tma: launch failed: %s", cudaGetErrorString(launched));
-        return 2;
+    // One launch takes `count` row groups from `begin`: with blocks enough for all SMs one block per SM walks its
+    // groups one after the other, else a cluster of 2, 4 or 8 blocks (as many as keep the grid within the SMs and
+    // give every block at least one round of four key ranges) shares each group.
+    auto launch = [&](long begin, long count) -> int {
+        int cluster = 1;
+        while (cluster < DT_MAX_CLUSTER && count * cluster * 2 <= sms && cluster * 2 * DT_CWARPS <= max_splits + DT_CWARPS - 1) cluster *= 2;
+        p.cluster = cluster;
+        p.rounds = (max_splits + cluster * DT_CWARPS - 1) / (cluster * DT_CWARPS);
+        p.group_begin = (int)begin;
+        p.group_count = (int)count;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3((unsigned)(cluster > 1 ? count * cluster : (count < sms ? count : sms)));
+        config.blockDim = dim3(DT_THREADS);
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n = 0;
+        if (llmp_pdl_enabled()) {
+            attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see pdl_wait() in the kernel
+            attr[n].val.programmaticStreamSerializationAllowed = 1;
+            ++n;
+        }
+        if (cluster > 1) {
+            attr[n].id = cudaLaunchAttributeClusterDimension;
+            attr[n].val.clusterDim.x = (unsigned)cluster;
+            attr[n].val.clusterDim.y = 1;
+            attr[n].val.clusterDim.z = 1;
+            ++n;
+        }
+        config.attrs = attr;
+        config.numAttrs = n;
+        const cudaError_t launched = cudaLaunchKernelEx(&config, decode_attention_tma_kernel, map, p);
+        if (launched != cudaSuccess) {
+            llmp_set_error("decode_attention_tma: launch failed: %s", cudaGetErrorString(launched));
+            return 2;
+        }
+        return 0;
+    };
+    // Row groups all take the same time, so a count that is no multiple of the SMs leaves SMs idle for up to a whole
+    // group (512 groups on 148 SMs: 4 rounds for 3.46 rounds of work). The groups beyond the last full multiple go
+    // to a second launch, where clusters share them: 3 rounds and half a round.
+    const long rest = groups % sms;
+    if (groups > sms && rest != 0 && rest * 2 <= sms) {
+        if (int rc = launch(0, groups - rest)) return rc;
+        if (int rc = launch(groups - rest, rest)) return rc;
+    } else if (int rc = launch(0, groups)) {
+        return rc;
     }
     return llmp_check_launch("decode_attention_tma");
 }
