@@ -191,12 +191,15 @@ class CacheManager:
             out.append(max(0, want - len(table)))
         return out
 
-    def can_reserve(self, req_id: Hashable, new_length: int, spare: Optional[List[int]] = None) -> bool:
+    def can_reserve(self, req_id: Hashable, new_length: int, spare: Optional[List[int]] = None,
+                    short: Optional[List[int]] = None) -> bool:
         """True when every group has the pages; ``spare`` (one count per group) is subtracted from
-        the free pages first, for callers that plan several reservations before making them."""
+        the free pages first, for callers that plan several reservations before making them.
+        ``short``: the result of ``pages_short`` for the same arguments, when the caller has it."""
         if new_length > self.max_request_tokens:
             return False
-        short = self.pages_short(req_id, new_length)
+        if short is None:
+            short = self.pages_short(req_id, new_length)
         for g, group in enumerate(self.groups):
             if short[g] > group.pool.num_free - (spare[g] if spare else 0):
                 return False
@@ -208,9 +211,11 @@ class CacheManager:
             raise CacheError(f"request {req_id!r} is not live")
         if new_length > self.max_request_tokens:
             raise CacheError(f"request {req_id!r} would hold {new_length} tokens, the limit is {self.max_request_tokens}")
-        if not self.can_reserve(req_id, new_length):
-            return False
         short = self.pages_short(req_id, new_length)
+        if not any(short):
+            return True                                   # the pages it holds cover the new length
+        if not self.can_reserve(req_id, new_length, None, short):
+            return False
         for g, group in enumerate(self.groups):
             pages = group.pool.alloc(short[g])
             assert pages is not None

@@ -59,6 +59,9 @@ class _DecodeGraph:
         self.logits = None
         self.copied = None
         self.launches = 0
+        self.host_np = None          # the pinned buffer as a numpy array (same memory)
+        self.req_ids = None          # the requests of the last step, in row order
+        self.table_lens = None       # per cache group and row: pages of the block table already in the buffer
 
 
 class ModelRunner:
@@ -118,11 +121,12 @@ class ModelRunner:
                 if start + n > cache.max_request_tokens:
                     raise OutOfPages(f"request {e.req_id!r} would hold {start + n} tokens; the cache was made for "
                                      f"{cache.max_request_tokens} per request")
-                if not cache.can_reserve(e.req_id, start + n, spare):
+                short = cache.pages_short(e.req_id, start + n)
+                if not cache.can_reserve(e.req_id, start + n, spare, short):
                     raise OutOfPages(f"no pages left for {n} more tokens of request {e.req_id!r} "
                                      f"(free pages per group: {[g.pool.num_free for g in cache.groups]})")
-                short = cache.pages_short(e.req_id, start + n)
-                spare = [a + b for a, b in zip(spare, short)]
+                if any(short):
+                    spare = [a + b for a, b in zip(spare, short)]
         except Exception:
             for req_id in admitted:
                 cache.free(req_id)
@@ -244,6 +248,8 @@ class ModelRunner:
             slot.ctx = StepContext(self.device, self.dtype)
             flat = self._fill(slot.ctx, entries, width)
             slot.host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+            slot.host_np = slot.host.numpy()
+            self._remember(slot, entries)
             slot.dev = slot.host.to(self.device)
             self._bind(slot.ctx, slot.dev)
             slot.ctx.decode_ctx_bound = width * ps
@@ -258,8 +264,12 @@ class ModelRunner:
             slot.graph = graph
         else:
             slot.copied.synchronize()            # the previous copy out of the pinned buffer is done
-            flat = self._fill(slot.ctx, entries, width)
-            slot.host.copy_(torch.tensor(flat, dtype=torch.int32))
+            if slot.req_ids == [e.req_id for e in entries]:
+                self._refill(slot, entries, width)
+            else:
+                flat = self._fill(slot.ctx, entries, width)
+                slot.host_np[:len(flat)] = flat
+                self._remember(slot, entries)
             slot.dev.copy_(slot.host, non_blocking=True)
         slot.copied.record()
         self.last_h2d_bytes = slot.host.numel() * 4
@@ -267,6 +277,42 @@ class ModelRunner:
         kernels.launch_count += slot.launches    # every replay launches the captured kernels again
         self.graph_replays += 1
         return self._finish(slot.ctx, entries, slot.logits)
+
+    def _remember(self, slot: _DecodeGraph, entries: Sequence[StepEntry]) -> None:
+        slot.req_ids = [e.req_id for e in entries]
+        slot.table_lens = [[len(self.cache.block_table(e.req_id, g)) for e in entries] for g in range(len(self.cache.groups))]
+
+    def _refill(self, slot: _DecodeGraph, entries: Sequence[StepEntry], width: int) -> None:
+        """The same requests as in the slot's last step, one token further: only what moves is written into the
+        pinned buffer (token ids, positions, context lengths, the new token's slot, block-table rows that grew or
+        belong to a windowed group, whose entries can change in place)."""
+        cache, ctx, buf = self.cache, slot.ctx, slot.host_np
+        ps = cache.page_size
+        R = len(entries)
+        starts = [cache.length(e.req_id) for e in entries]
+        ctx.starts = starts
+        ctx.max_ctx_len = max(starts) + 1
+        buf[0:R] = [int(e.tokens[0]) for e in entries]
+        buf[R:2 * R] = starts
+        at = 3 * R + R + 1                                   # token ids, positions, request of each token, q_start
+        buf[at:at + R] = [s + 1 for s in starts]             # ctx_len
+        at += 2 * R + ctx.num_logit_rows                     # ctx_len, slots, logit rows
+        for g, group in enumerate(cache.groups):
+            tables = [cache.block_table(e.req_id, g) for e in entries]
+            mapping = []
+            for table, start in zip(tables, starts):
+                page = table[start // ps]
+                mapping.append(-1 if page < 0 else page * ps + start % ps)
+            buf[at:at + R] = mapping
+            at += R
+            lens = slot.table_lens[g]
+            windowed = group.spec.window is not None
+            for r, table in enumerate(tables):
+                if windowed or len(table) != lens[r]:
+                    n = min(width, len(table))
+                    buf[at + r * width:at + r * width + n] = table[:n]
+                    lens[r] = len(table)
+            at += R * width
 
     def _finish(self, ctx: StepContext, entries: Sequence[StepEntry], logits):
         for r, e in enumerate(entries):

@@ -28,7 +28,7 @@ from ..cache import CacheManager
 from ..sampling import SamplingConfig
 
 
-@dataclass
+@dataclass(eq=False)          # a request is itself: lists of requests are searched by identity, not by comparing fields
 class Request:
     req_id: Hashable
     prompt: List[int]
@@ -132,10 +132,11 @@ class Scheduler:
             if count <= 0:
                 return False
             new_length = request.computed + count
-            if not self.cache.can_reserve(request.req_id, new_length, spare):
-                return False
             short = self.cache.pages_short(request.req_id, new_length)
-            spare = [a + b for a, b in zip(spare, short)]
+            if not self.cache.can_reserve(request.req_id, new_length, spare, short):
+                return False
+            if any(short):
+                spare = [a + b for a, b in zip(spare, short)]
             budget -= count
             plan.entries.append(PlannedEntry(request, request.computed, count, request.computed + count ==
                                              len(request.prompt) + len(request.output)))
@@ -144,7 +145,7 @@ class Scheduler:
         # 1. running requests: those that decode first, then those still in their prompt
         order = [r for r in self.running if r.num_pending == 1] + [r for r in self.running if r.num_pending > 1]
         for request in order:
-            if request not in self.running:      # preempted while planning an earlier one
+            if request.status != "running":      # preempted while planning an earlier one
                 continue
             while budget > 0:
                 limit = 1 if request.num_pending == 1 else self.max_prefill_chunk
