@@ -203,11 +203,13 @@ def time_decode(engine, batch, steps, warmup, seed, e2e=True):
     greedy = SamplingConfig(temperature=0.0)
     e2e_prompts = random_prompts(vocab, batch, CONTEXT - 1, seed + 1)
     for p in e2e_prompts:
-        engine.add_request(p, max_tokens=warmup + steps + 2 * batch + 8, sampling=greedy, ignore_eos=True)
+        engine.add_request(p, max_tokens=warmup + steps + 2 * batch + 16, sampling=greedy, ignore_eos=True)
     while any(r.num_pending > 1 or not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()                            # prompts, portion by portion
+    for _ in range(8):
+        engine.step()                            # set-up: the first decode steps of a shape run eagerly, then are captured
     for _ in range(warmup):
-        engine.step()                            # decode steps before the clock starts (graphs are captured here)
+        engine.step()                            # the untimed warm-up steps
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(steps):
