@@ -290,7 +290,9 @@ def run_ours(args):
     layers = args.layers or cfg["num_hidden_layers"]
     peak = peaks()
     dtype = torch.bfloat16
-    engine = build_ours(cfg, layers, max(64, args.batch), dtype)
+    # room per request: the context, the set-up, warm-up and timed decode steps, in whole pages
+    room = -(-(CONTEXT + 64 + args.warmup + args.steps) // 256) * 256
+    engine = build_ours(cfg, layers, max(64, args.batch), dtype, tokens_per_request=max(CONTEXT + 256, room))
     clocks = ClockSampler()
     clocks.start()
     if args.only == "prefill":
