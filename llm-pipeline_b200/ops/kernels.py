@@ -85,7 +85,14 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream of the current device as a raw handle (the fast accessor where torch has it:
+    ``torch.cuda.current_stream()`` costs about 15 microseconds a call, several milliseconds per eager step)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
