@@ -259,19 +259,37 @@ int llmp_launch_decode_tma(const void* q, long q_stride, void* out, long out_str
                            const int* block_tables, int table_stride, const int* ctx_len, int R, int max_splits, int nq,
                            int nkv, int page_size, int window, float scale, int* error_flag, cudaStream_t stream);
 
+// The streaming kernel that deals the key ranges of all requests out evenly (attention_decode_list.cu).
+int llmp_decode_list_max_rows();
+long llmp_decode_list_scratch_floats();
+int llmp_decode_list_counters();
+int llmp_launch_decode_list(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
+                            const int* block_tables, int table_stride, const int* ctx_len, int R, int nq, int nkv,
+                            int page_size, int window, float scale, float* scratch, unsigned* counters, int* error_flag,
+                            cudaStream_t stream);
+
 // Scratch floats the decode kernel needs for R rows whose longest context is max_ctx keys.
 LLMP_API long llmp_decode_scratch_floats(int R, int nq, int d, int max_ctx) {
     const long splits = (max_ctx + DEC_SPLIT - 1) / DEC_SPLIT;
-    return (long)R * nq * (splits > 0 ? splits : 1) * (d + 2);
+    const long ranges = (long)R * nq * (splits > 0 ? splits : 1) * (d + 2);
+    const long stream = llmp_decode_list_scratch_floats();
+    return ranges > stream ? ranges : stream;
 }
+
+// Counters (unsigned, zero before the first launch; every launch leaves them zero) that the streaming kernel needs.
+// Launches that may run at the same time need counters and scratch of their own.
+LLMP_API int llmp_decode_counters() { return llmp_decode_list_counters(); }
 
 // pages: [num_pages, 2, nkv, page_size, d]. error_flag: one int in device-visible memory that a kernel with bounded
 // waits sets to 1 when a wait ran out (may be null: the kernels that need it are then not used).
+// counters: llmp_decode_counters() zeroed unsigned values for the kernel that deals key ranges out evenly (may be
+// null in the same way). uneven: the caller's word that the requests' contexts differ much or are too many for one
+// block each, which is when that kernel is the faster one; the result does not depend on it beyond rounding.
 LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long out_stride, const void* pages,
                                    int num_pages, int dtype, const int* block_tables, int table_stride,
                                    const int* ctx_len, int R, int max_ctx, int nq, int nkv, int d, int page_size,
-                                   int window, float scale, float* scratch, long scratch_floats, int* error_flag,
-                                   cudaStream_t stream) {
+                                   int window, float scale, float* scratch, long scratch_floats, unsigned* counters,
+                                   int uneven, int* error_flag, cudaStream_t stream) {
     if (R <= 0) return 0;
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads cannot share %d key/value heads", nq, nkv);
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
@@ -308,7 +326,11 @@ LLMP_API int llmp_decode_attention(const void* q, long q_stride, void* out, long
                                                              p.max_splits);
     } else {
         if (error_flag != nullptr && num_pages > 0 && llmp_decode_tma_supports(nq, nkv, d, page_size)) {
-            // the streaming kernel writes the finished output itself: no partial results, no merge
+            // the streaming kernels write the finished output themselves: no merge kernel
+            if (uneven && counters != nullptr && R <= llmp_decode_list_max_rows())
+                return llmp_launch_decode_list(q, q_stride, out, out_stride, pages, num_pages, block_tables, table_stride,
+                                               ctx_len, R, nq, nkv, page_size, window, scale, scratch, counters, error_flag,
+                                               stream);
             return llmp_launch_decode_tma(q, q_stride, out, out_stride, pages, num_pages, block_tables, table_stride, ctx_len, R,
                                           p.max_splits, nq, nkv, page_size, window, scale, error_flag, stream);
         } else if (llmp_launch_decode_mma(q, q_stride, pages, block_tables, table_stride, ctx_len, R, p.max_splits, nq, nkv, d,

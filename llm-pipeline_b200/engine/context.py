@@ -27,6 +27,7 @@ class StepContext:
         self.num_logit_rows = 0
         self.table_width = 0
         self.decode_ctx_bound = 0            # when set: the context length the decode kernels size their grid for
+        self.contexts_uneven = False         # decode steps: one request is much longer than the average
         # device side (int32)
         self.token_ids: torch.Tensor = None  # [N]
         self.positions: torch.Tensor = None  # [N]
@@ -68,7 +69,8 @@ class StepContext:
             # every request brings one token: row r is request r
             kernels.decode_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group],
                                      self.ctx_len, self.decode_ctx_bound or self.max_ctx_len, mixer.num_heads,
-                                     mixer.num_kv_heads, mixer.head_dim, page_size, mixer.window or 0, mixer.scale)
+                                     mixer.num_kv_heads, mixer.head_dim, page_size, mixer.window or 0, mixer.scale,
+                                     uneven=self.contexts_uneven or kernels.decode_rows_uneven(self.num_requests, mixer.num_kv_heads))
             return
         tile_req, tile_tok0 = self.attention_tiles(mixer.tokens_per_tile)
         kernels.paged_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group], self.q_start,

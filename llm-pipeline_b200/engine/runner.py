@@ -163,6 +163,7 @@ class ModelRunner:
         ctx.num_tokens, ctx.num_requests = q_start[-1], len(entries)
         ctx.max_q_len = max(ctx.q_lens)
         ctx.max_ctx_len = max(ctx_len)
+        ctx.contexts_uneven = ctx.max_q_len == 1 and kernels.decode_contexts_uneven(ctx_len)
         ctx.num_logit_rows = len(rows)
         if width is None:
             width = max(1, -(-ctx.max_ctx_len // ps))
@@ -226,10 +227,12 @@ class ModelRunner:
         cache = self.cache
         self._reserve(entries)
         ps = cache.page_size
-        longest = max(cache.length(e.req_id) + 1 for e in entries)
+        lengths = [cache.length(e.req_id) + 1 for e in entries]
+        longest = max(lengths)
         step_w = self.GRAPH_WIDTH_STEP
         width = -(-max(1, -(-longest // ps)) // step_w) * step_w
-        key = (len(entries), tuple(len(e.want) for e in entries), width)
+        # a graph holds the decode kernel that was chosen when it was captured: even and uneven batches have their own
+        key = (len(entries), tuple(len(e.want) for e in entries), width, kernels.decode_contexts_uneven(lengths))
         slot = self._graphs.get(key)
         if slot is None:
             if len(self._graphs) >= self.MAX_GRAPHS:

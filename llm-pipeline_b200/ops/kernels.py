@@ -9,7 +9,8 @@ tensor that is not on a CUDA device is an error.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+import os
+from typing import Optional, Sequence
 
 import torch
 
@@ -47,7 +48,7 @@ _SIGNATURES = {
     "llmp_gemm_stream_swiglu": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-    "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _P],
+    "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _I, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -356,13 +357,62 @@ def decode_scratch_floats(rows: int, num_heads: int, head_dim: int, max_ctx: int
     return int(fn(rows, num_heads, head_dim, max_ctx))
 
 
+_decode_counters: dict = {}
+_DECODE_LIST = os.environ.get("LLMP_B200_DECODE_LIST", "")
+
+
+_sm_count: Optional[int] = None
+
+
+def sm_count() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+def decode_contexts_uneven(ctx_lens: Sequence[int]) -> bool:
+    """Whether one request of a decode step is much longer than the average: its blocks would still be reading
+    when the others are done, unless the key ranges of all requests are dealt out evenly."""
+    longest, total, rows = max(ctx_lens), sum(ctx_lens), len(ctx_lens)
+    return longest * rows > 2 * total + 512 * rows
+
+
+def decode_rows_uneven(rows: int, num_kv_heads: int) -> bool:
+    """Many more (request, key/value head) pairs than SMs: whole pairs per block leave SMs idle in the last round,
+    and dealing the ranges out evenly then saves more than adding up the sums of shared pairs costs (Qwen3-8B heads,
+    2,048 keys each: from 64 requests on)."""
+    return rows * num_kv_heads > 2 * sm_count()
+
+
+def decode_counters(device: torch.device) -> torch.Tensor:
+    """The counters with which the blocks of the streaming decode kernel that share a long request find out who
+    finishes last. Every launch leaves them zero. One set per device: decode launches on a device must follow one
+    another (one stream, or streams ordered by events), as they do in the engine. They are made outside a graph
+    capture (the engine runs every shape once before it captures it)."""
+    key = torch.device(device).index or 0
+    counters = _decode_counters.get(key)
+    if counters is None:
+        _need(not torch.cuda.is_current_stream_capturing(), "decode counters must exist before a graph is captured")
+        fn = library().llmp_decode_counters
+        fn.argtypes = []
+        fn.restype = _I
+        counters = _decode_counters[key] = torch.zeros(int(fn()), dtype=torch.int32, device=device)
+    return counters
+
+
 def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
                      block_tables: torch.Tensor, ctx_len: torch.Tensor, max_ctx: int, num_heads: int,
                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     scratch: Optional[torch.Tensor] = None, uneven: bool = False) -> torch.Tensor:
     """Attention of one query row per request (row r belongs to request r, at position ctx_len[r] - 1)
     over the request's pages; keys are split into fixed ranges whose partial results go through
-    ``scratch`` (float32, at least ``decode_scratch_floats(...)`` entries; allocated when None)."""
+    ``scratch`` (float32, at least ``decode_scratch_floats(...)`` entries; allocated when None).
+    ``uneven`` (see ``decode_contexts_uneven`` and ``decode_rows_uneven``) picks, where there is a choice, the kernel that deals the key ranges of
+    all requests out evenly over the SMs instead of giving every request blocks of its own; the result is the same
+    beyond rounding. ``LLMP_B200_DECODE_LIST=0`` or ``1`` overrides it."""
+    if _DECODE_LIST in ("0", "1"):
+        uneven = _DECODE_LIST == "1"
     _i32(block_tables, "block_tables")
     _i32(ctx_len, "ctx_len")
     R = ctx_len.numel()
@@ -378,7 +428,7 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: t
     _call("llmp_decode_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), pages.shape[0],
           dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(ctx_len), R, int(max_ctx), num_heads,
           num_kv_heads, head_dim, page_size, int(window), float(scale), _ptr(scratch), scratch.numel(),
-          error_flag().data_ptr(), _stream())
+          _ptr(decode_counters(q.device)), int(bool(uneven)), error_flag().data_ptr(), _stream())
     return out
 
 

@@ -53,3 +53,23 @@ def test_mixed_batches_with_page_reuse(tmp_path, config, seed, page, lengths, dt
     H.assert_close(got, want, H.TOL[dtype], "mixed")
     assert runner.cache.pages_reused > 0
     assert runner.cache.num_live == 0
+
+
+def test_decode_of_uneven_batch_shares_the_long_request(tmp_path):
+    """One request far longer than the others: the decode steps (eager, then as a replayed graph of its own) take
+    the attention kernel that deals key ranges out over all SMs; logits as from the plain implementation."""
+    dtype = torch.bfloat16
+    folder, weights = H.make_case(tmp_path, plain.TINY_D, 5, dtype)
+    requests = _requests(plain.TINY_D, (1700, 20, 60), extra=10)
+    want = H.expected_logits(plain.TINY_D, weights, requests)
+    runner = H.make_runner(folder, dtype, page_size=16, num_pages=160)
+    tail = 10
+    steps = [([(rid, toks[:-tail], list(range(len(toks) - tail)))], []) for rid, toks in requests.items()]
+    for i in range(tail):
+        at = {rid: len(toks) - tail + i for rid, toks in requests.items()}
+        steps.append(([(rid, [toks[at[rid]]], [0]) for rid, toks in requests.items()], list(requests) if i == tail - 1 else []))
+    from llm_pipeline_b200.ops import kernels
+    assert kernels.decode_contexts_uneven([len(t) - tail + 1 for t in requests.values()])
+    H.assert_close(H.replay(runner, steps), want, H.TOL[dtype], "uneven decode")
+    assert runner.graph_replays > 0 and runner.cache.num_live == 0
+    kernels.check_error_flag()

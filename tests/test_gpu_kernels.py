@@ -273,7 +273,7 @@ def attention_reference(q, k, v, window, scale):
     return torch.einsum("nts,snd->tnd", torch.softmax(scores, dim=-1), vv.double()).float()
 
 
-def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None, decode=False):
+def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None, decode=False, uneven=False):
     """requests: list of (context_before, new_tokens). Pages are handed out in a scrambled order."""
     k_ = K()
     gen = torch.Generator().manual_seed(seed)
@@ -319,7 +319,7 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
     if decode:
         assert all(t == 1 for _, t in requests)
         k_.decode_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(ctx), max(ctx), nq, nkv, d, page_size,
-                            window, scale)
+                            window, scale, uneven=uneven)
     else:
         k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
                            dev(tile_tok0), nq, nkv, d, page_size, window, scale, tpt)
@@ -348,23 +348,46 @@ def test_decode_attention_split_keys(dtype, nq, nkv, d, page):
     assert torch.allclose(got_w, want_w, atol=tol(dtype, 2e-5, 2e-2))
 
 
+@pytest.mark.parametrize("uneven", [False, True])
 @pytest.mark.parametrize("nq,nkv,page", [(32, 8, 16), (8, 1, 8), (4, 4, 32), (6, 2, 64), (16, 2, 128)])
-def test_decode_attention_head_size_128_streaming_kernel(nq, nkv, page):
-    """Head size 128 in bfloat16 with up to 8 heads per group takes the persistent TMA kernel: contexts on both
-    sides of the 128-key ranges and of a warp's 32 keys, and enough requests that every block's ring of stages
-    is filled several times over."""
+def test_decode_attention_head_size_128_streaming_kernel(nq, nkv, page, uneven):
+    """Head size 128 in bfloat16 with up to 8 heads per group takes one of the two persistent TMA kernels (blocks of
+    its own for every request, or all key ranges dealt out evenly): contexts on both sides of the 128-key ranges and
+    of a warp's 32 keys, and enough requests that every block's ring of stages is filled several times over."""
     dtype = torch.bfloat16
     contexts = [0, 31, 32, 127, 128, 255, 256, 700, 63, 64, 1030, 5, 129, 511] * 3
     requests = [(c, 1) for c in contexts]
-    got, want = run_paged(dtype, nq, nkv, 128, page, requests, seed=21, decode=True)
+    got, want = run_paged(dtype, nq, nkv, 128, page, requests, seed=21, decode=True, uneven=uneven)
     assert torch.allclose(got, want, atol=2e-2)
-    got_w, want_w = run_paged(dtype, nq, nkv, 128, page, requests, window=300, seed=22, decode=True)
+    got_w, want_w = run_paged(dtype, nq, nkv, 128, page, requests, window=300, seed=22, decode=True, uneven=uneven)
     assert torch.allclose(got_w, want_w, atol=2e-2)
     K().check_error_flag()
     for key_pos in (3, 127, 128, 511, 698):
-        got, want = run_paged(dtype, 8, 2, 128, 16, [(699, 1), (40, 1)], seed=4, boost=(0, key_pos, 5), decode=True)
+        got, want = run_paged(dtype, 8, 2, 128, 16, [(699, 1), (40, 1)], seed=4, boost=(0, key_pos, 5), decode=True,
+                              uneven=uneven)
         assert torch.allclose(got, want, atol=3e-2), key_pos
         assert float(want[0, 5].abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("contexts", [[40000, 10, 300, 129], [9000], [5], [3000, 2999, 3001, 1, 2, 3, 700, 700, 128],
+                                      [20000] * 3 + [17] * 40, [511] * 150])
+@pytest.mark.parametrize("uneven", [True, False])
+def test_decode_attention_streaming_kernel_shares_long_requests(contexts, uneven):
+    """The kernel for uneven batches deals the 128-key ranges of all requests out evenly: a request far longer than
+    the others is shared by many blocks, whose sums the last of them to finish adds up. One decisive key in the long
+    request, in a range of a block in the middle; several times in a row, since the blocks' counters must be zero
+    again. The kernel for even batches takes the same batches, only slower."""
+    dtype = torch.bfloat16
+    requests = [(c, 1) for c in contexts]
+    key_pos = contexts[0] // 2
+    for seed, window in ((31, 0), (32, 0), (33, 2500)):
+        boost = (0, key_pos, 5) if window == 0 else None
+        got, want = run_paged(dtype, 8, 2, 128, 32, requests, window=window, seed=seed, boost=boost, decode=True,
+                              uneven=uneven)
+        assert torch.allclose(got, want, atol=3e-2), (seed, window, float((got - want).abs().max()))
+        if boost is not None:
+            assert float(want[0, 5].abs().max()) > 0.5
+    K().check_error_flag()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
