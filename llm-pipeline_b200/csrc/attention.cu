@@ -194,9 +194,12 @@ int llmp_launch_prefill_mma(const void* q, long q_stride, void* out, long out_st
 // The tcgen05 kernel for bfloat16 pages and head size 128 (attention_prefill_tc.cu).
 bool llmp_prefill_tc_supports(int nq, int nkv, int d, int page_size);
 int llmp_prefill_tc_tokens_per_tile(int nq, int nkv);
+int llmp_prefill_tc_max_segments();
+long llmp_prefill_tc_place_floats();
 int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
                            const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
-                           const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int page_size,
+                           const int* tile_req, const int* tile_tok0, const int* tile_seg, const int* tile_slot,
+                           float* partials, unsigned* counters, int num_tiles, int nq, int nkv, int page_size,
                            int window, float scale, int* error_flag, cudaStream_t stream);
 
 // Number of query tokens one block covers for a given group size, element type, head size and page size (0:
@@ -211,14 +214,29 @@ LLMP_API int llmp_attention_tokens_per_tile(int nq, int nkv, int dtype, int d, i
     return ATT_ROWS / heads;
 }
 
+// How many items may share the keys of one tile of the list (1: the kernel for these sizes takes whole tiles only),
+// and the floats that one place for an item's sums takes per key/value head.
+LLMP_API int llmp_attention_max_segments(int nq, int nkv, int dtype, int d, int page_size) {
+    if (nq <= 0 || nkv <= 0 || nq % nkv) return 1;
+    return dtype == LLMP_BF16 && llmp_prefill_tc_supports(nq, nkv, d, page_size) ? llmp_prefill_tc_max_segments() : 1;
+}
+LLMP_API long llmp_attention_place_floats() { return llmp_prefill_tc_place_floats(); }
+
 // pages: [num_pages, 2, nkv, page_size, d]. error_flag: one int in device-visible memory that a kernel with
 // bounded waits sets to 1 when a wait ran out (the host checks it after synchronising).
+// tile_seg (may be null): the list holds items that share the keys of a tile; item i is number tile_seg[i] & 255 of
+// tile_seg[i] >> 8 items of its tile, which follow one another in the list, and tile_slot[i] is the first of the
+// tile's places (one per item) in partials ([places][nkv][llmp_attention_place_floats()]) and in counters
+// ([places][nkv] unsigned values, zero before the first launch; every launch leaves them zero).
 LLMP_API int llmp_paged_attention(const void* q, long q_stride, void* out, long out_stride, const void* pages,
                                   int num_pages, int dtype, const int* block_tables, int table_stride,
                                   const int* q_start, const int* ctx_len, const int* tile_req, const int* tile_tok0,
+                                  const int* tile_seg, const int* tile_slot, float* partials, unsigned* counters,
                                   int num_tiles, int nq, int nkv, int d, int page_size, int window, float scale,
                                   int tokens_per_tile, int* error_flag, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
+    LLMP_REQUIRE(tile_seg == nullptr || llmp_attention_max_segments(nq, nkv, dtype, d, page_size) > 1,
+                 "attention: the kernel for these sizes takes whole tiles only");
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads cannot share %d key/value heads", nq, nkv);
     LLMP_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "attention: head size %d is not a multiple of 16 in 16..256", d);
     LLMP_REQUIRE(page_size > 0 && num_pages > 0, "attention: bad page size %d or page count %d", page_size, num_pages);
@@ -227,8 +245,8 @@ LLMP_API int llmp_paged_attention(const void* q, long q_stride, void* out, long 
                  llmp_attention_tokens_per_tile(nq, nkv, dtype, d, page_size));
     if (dtype == LLMP_BF16 && llmp_prefill_tc_supports(nq, nkv, d, page_size))
         return llmp_launch_prefill_tc(q, q_stride, out, out_stride, pages, num_pages, block_tables, table_stride, q_start,
-                                      ctx_len, tile_req, tile_tok0, num_tiles, nq, nkv, page_size, window, scale,
-                                      error_flag, stream);
+                                      ctx_len, tile_req, tile_tok0, tile_seg, tile_slot, partials, counters, num_tiles, nq,
+                                      nkv, page_size, window, scale, error_flag, stream);
     if (dtype == LLMP_BF16 && llmp_prefill_mma_supports(d))
         return llmp_launch_prefill_mma(q, q_stride, out, out_stride, pages, block_tables, table_stride, q_start, ctx_len,
                                        tile_req, tile_tok0, num_tiles, nq, nkv, d, page_size, window, scale, stream);

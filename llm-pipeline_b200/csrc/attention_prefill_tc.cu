@@ -21,6 +21,12 @@
 // P V is done), one thread of warp 5 issues the MMAs. Two blocks share an SM (96 KB of shared memory and 256
 // tensor-memory columns each): while one is in its softmax the tensor cores work for the other.
 //
+// Long contexts: a tile of the list may come as up to FA_MAX_SEGMENTS items, each with an equal share of the tile's
+// key tiles (tile_seg: item s of n; tile_slot: where the tile's items keep their sums), so that few query rows over
+// many keys still fill the SMs and items are small against the whole. An item of a shared tile leaves its sums
+// (O, the maximum they are scaled by, the row sum; float32) in global memory and counts itself with an atomic add;
+// the item that counts last adds the sums in item order, normalises, stores and zeroes the counter. Nobody waits.
+//
 // Every wait on an mbarrier is bounded: when one runs out the kernel records 1 in *error_flag and goes on
 // without waiting (its output is then wrong; the host reads the flag), so no thread is left behind at a
 // barrier and the tensor memory is always freed.
@@ -40,6 +46,8 @@
 #define FA_TMEM_COLS 256                         // S (128 columns, P over its first 64) and O (128 columns)
 #define FA_RESCALE_STEP 8.0f
 #define FA_STAGGER_NS 1000
+#define FA_MAX_SEGMENTS 8                        // items that may share the key tiles of one tile
+#define FA_PART (FA_ROWS * FA_D + 2 * FA_ROWS)   // floats of an item's sums: O column by column, the rows' maxima, their sums
 
 struct FaParams {
     const bf16* q;
@@ -49,6 +57,10 @@ struct FaParams {
     const int* ctx_len;
     const int* tile_req;
     const int* tile_tok0;
+    const int* tile_seg;     // null, or per item: its place among the items of its tile | their number << 8
+    const int* tile_slot;    // per item of a shared tile: the first of the tile's places in `partials`
+    float* partials;         // [places][nkv][FA_PART]
+    unsigned* counters;      // [places][nkv], zero between launches
     long q_stride, out_stride;
     int table_stride;
     int nq, nkv, page_size, num_pages, window, tokens_per_cta, num_sms, num_tiles;
@@ -176,6 +188,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
     extern __shared__ unsigned char fa_raw[];
     __shared__ __align__(8) uint64_t k_full, v_full, s_done, o_done, p_ready;
     __shared__ uint32_t tmem_slot;
+    __shared__ unsigned arrived_before;
     // the swizzled tiles want 1024-byte alignment
     const uint32_t raw_addr = tc_smem_u32(fa_raw);
     unsigned char* Qs = fa_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);   // [2 halves][128 rows][128 bytes]
@@ -205,8 +218,19 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
         lo = pos0 + tok0 - p.window + 1;
         if (lo < 0) lo = 0;
     }
-    const int tile_lo = (lo / FA_KEYS) * FA_KEYS;
-    const int num_key_tiles = (hi - tile_lo) / FA_KEYS + 1;
+    const int first_tile_lo = (lo / FA_KEYS) * FA_KEYS;
+    const int all_key_tiles = (hi - first_tile_lo) / FA_KEYS + 1;
+    // this item's share of the tile's key tiles
+    int seg = 0, nseg = 1, slot0 = 0;
+    if (p.tile_seg != nullptr) {
+        const int packed = p.tile_seg[tile];
+        seg = packed & 0xff;
+        nseg = (packed >> 8) & 0xff;
+        slot0 = p.tile_slot[tile];
+    }
+    const int seg_begin = (int)((long)all_key_tiles * seg / nseg);
+    const int tile_lo = first_tile_lo + seg_begin * FA_KEYS;
+    const int num_key_tiles = (int)((long)all_key_tiles * (seg + 1) / nseg) - seg_begin;      // 0: more items than key tiles
     const int pages_per_tile = FA_KEYS / p.page_size;
 
     // warp 4: the boxes of the K and V tile j, one lane per (page, half of the head)
@@ -252,7 +276,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
             asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
         __syncwarp();
-        load_tile(0);
+        if (num_key_tiles > 0) load_tile(0);
     } else if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -405,24 +429,91 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_pages, const
         }
 
         // O is complete when the last P V is done
-        mbar_wait(&o_done, (uint32_t)((num_key_tiles - 1) & 1), p.error_flag);
+        if (num_key_tiles > 0) mbar_wait(&o_done, (uint32_t)((num_key_tiles - 1) & 1), p.error_flag);
         fa_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         bf16* dst = p.out + (size_t)(q_begin + tok0 + (my_pos >= 0 ? my_tl : 0)) * p.out_stride + (size_t)(kvh * G + my_head) * FA_D;
+        if (nseg == 1) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
-        for (int c = 0; c < FA_D; c += 32) {
-            FA_TMEM_LD32(tmem_o + lane_field + c, a, 0);
-            fa_tmem_wait_ld();
-            if (my_pos >= 0) {
+            for (int c = 0; c < FA_D; c += 32) {
+                FA_TMEM_LD32(tmem_o + lane_field + c, a, 0);
+                fa_tmem_wait_ld();
+                if (my_pos >= 0) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 pack;
-                    pack.x = fa_pack(__uint_as_float(a[i]) * inv, __uint_as_float(a[i + 1]) * inv);
-                    pack.y = fa_pack(__uint_as_float(a[i + 2]) * inv, __uint_as_float(a[i + 3]) * inv);
-                    pack.z = fa_pack(__uint_as_float(a[i + 4]) * inv, __uint_as_float(a[i + 5]) * inv);
-                    pack.w = fa_pack(__uint_as_float(a[i + 6]) * inv, __uint_as_float(a[i + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c + i) = pack;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 pack;
+                        pack.x = fa_pack(__uint_as_float(a[i]) * inv, __uint_as_float(a[i + 1]) * inv);
+                        pack.y = fa_pack(__uint_as_float(a[i + 2]) * inv, __uint_as_float(a[i + 3]) * inv);
+                        pack.z = fa_pack(__uint_as_float(a[i + 4]) * inv, __uint_as_float(a[i + 5]) * inv);
+                        pack.w = fa_pack(__uint_as_float(a[i + 6]) * inv, __uint_as_float(a[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + i) = pack;
+                    }
                 }
+            }
+        } else {
+            // ---- an item of a shared tile: its sums to global memory; the item that counts last adds them up ----
+            float* part = p.partials + ((size_t)(slot0 + seg) * p.nkv + kvh) * FA_PART;
+            if (num_key_tiles > 0) {
+#pragma unroll
+                for (int c = 0; c < FA_D; c += 32) {
+                    FA_TMEM_LD32(tmem_o + lane_field + c, a, 0);
+                    fa_tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) part[(size_t)(c + i) * FA_ROWS + tid] = __uint_as_float(a[i]);   // column by column: the lanes of a warp write one line
+                }
+            }
+            part[FA_ROWS * FA_D + tid] = num_key_tiles > 0 ? m_used : -INFINITY;
+            part[FA_ROWS * FA_D + FA_ROWS + tid] = num_key_tiles > 0 ? l_run : 0.f;
+            __threadfence();                                         // the sums are visible before the count is
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (tid == 0) arrived_before = atomicAdd(&p.counters[(size_t)slot0 * p.nkv + kvh], 1u);
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (arrived_before == (unsigned)(nseg - 1)) {
+                __threadfence();
+                const float* first = p.partials + ((size_t)slot0 * p.nkv + kvh) * FA_PART;
+                // weights of the items' sums for this row: 2^(m_s - m) with m the largest maximum
+                float wgt[FA_MAX_SEGMENTS];
+                float m = -INFINITY, l = 0.f;
+#pragma unroll
+                for (int x = 0; x < FA_MAX_SEGMENTS; ++x) {
+                    wgt[x] = x < nseg ? __ldcg(first + (size_t)x * p.nkv * FA_PART + FA_ROWS * FA_D + tid) : -INFINITY;
+                    m = fmaxf(m, wgt[x]);
+                }
+#pragma unroll
+                for (int x = 0; x < FA_MAX_SEGMENTS; ++x) {
+                    wgt[x] = wgt[x] > -INFINITY ? fa_ex2(wgt[x] - m) : 0.f;
+                    if (x < nseg && wgt[x] != 0.f) l = fmaf(__ldcg(first + (size_t)x * p.nkv * FA_PART + FA_ROWS * FA_D + FA_ROWS + tid), wgt[x], l);
+                }
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+                for (int c = 0; c < FA_D; c += 32) {
+                    float acc[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+#pragma unroll
+                    for (int x = 0; x < FA_MAX_SEGMENTS; ++x) {
+                        if (x < nseg && wgt[x] != 0.f) {              // an item without keys for this row left no sums
+                            const float* src = first + (size_t)x * p.nkv * FA_PART + (size_t)c * FA_ROWS + tid;
+                            float v[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __ldcg(src + (size_t)i * FA_ROWS);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[i] = fmaf(v[i], wgt[x], acc[i]);
+                        }
+                    }
+                    if (my_pos >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 pack;
+                            pack.x = fa_pack(acc[i] * inv, acc[i + 1] * inv);
+                            pack.y = fa_pack(acc[i + 2] * inv, acc[i + 3] * inv);
+                            pack.z = fa_pack(acc[i + 4] * inv, acc[i + 5] * inv);
+                            pack.w = fa_pack(acc[i + 6] * inv, acc[i + 7] * inv);
+                            *reinterpret_cast<uint4*>(dst + c + i) = pack;
+                        }
+                    }
+                }
+                if (tid == 0) p.counters[(size_t)slot0 * p.nkv + kvh] = 0u;      // for the next launch
             }
         }
     }
@@ -492,18 +583,26 @@ bool llmp_prefill_tc_supports(int nq, int nkv, int d, int page_size) {
 // Query tokens per block for a group size: 128 rows of (token, head).
 int llmp_prefill_tc_tokens_per_tile(int nq, int nkv) { return FA_ROWS / (nq / nkv); }
 
+// Items that may share a tile's keys, and the floats of one place (one item and key/value head) for their sums.
+int llmp_prefill_tc_max_segments() { return FA_MAX_SEGMENTS; }
+long llmp_prefill_tc_place_floats() { return FA_PART; }
+
 int llmp_launch_prefill_tc(const void* q, long q_stride, void* out, long out_stride, const void* pages, int num_pages,
                            const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
-                           const int* tile_req, const int* tile_tok0, int num_tiles, int nq, int nkv, int page_size,
+                           const int* tile_req, const int* tile_tok0, const int* tile_seg, const int* tile_slot,
+                           float* partials, unsigned* counters, int num_tiles, int nq, int nkv, int page_size,
                            int window, float scale, int* error_flag, cudaStream_t stream) {
     LLMP_REQUIRE(error_flag != nullptr, "attention: an error flag in device memory is required");
+    LLMP_REQUIRE(tile_seg == nullptr || (tile_slot != nullptr && partials != nullptr && counters != nullptr),
+                 "attention: tiles whose keys are shared need places for their sums and counters");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 8) == 0 && ((size_t)q % 16) == 0 && ((size_t)out % 16) == 0 &&
                  ((size_t)pages % 16) == 0, "attention: rows must be 16-byte aligned");
     CUtensorMap map;
     if (llmp_pages_tensor_map(pages, nkv, page_size, num_pages, page_size, 1, &map)) return 1;
     FaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len;
-    p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.q_stride = q_stride; p.out_stride = out_stride;
+    p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.tile_seg = tile_seg; p.tile_slot = tile_slot; p.partials = partials;
+    p.counters = counters; p.q_stride = q_stride; p.out_stride = out_stride;
     p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.tokens_per_cta = llmp_prefill_tc_tokens_per_tile(nq, nkv); p.scale = scale;
     p.error_flag = error_flag;

@@ -164,6 +164,13 @@ class ModelRunner:
         ctx.max_q_len = max(ctx.q_lens)
         ctx.max_ctx_len = max(ctx_len)
         ctx.contexts_uneven = ctx.max_q_len == 1 and kernels.decode_contexts_uneven(ctx_len)
+        lead = 0
+        while lead < len(ctx.q_lens) and ctx.q_lens[lead] == 1:
+            lead += 1
+        ctx.leading_single = lead if lead < len(ctx.q_lens) else 0       # a step of single tokens only is a decode step
+        if ctx.leading_single:
+            ctx.leading_longest = max(ctx_len[:lead])
+            ctx.leading_uneven = kernels.decode_contexts_uneven(ctx_len[:lead])
         ctx.num_logit_rows = len(rows)
         if width is None:
             width = max(1, -(-ctx.max_ctx_len // ps))

@@ -47,7 +47,8 @@ _SIGNATURES = {
     "llmp_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream_swiglu": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_gemm_stream_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
-    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
+                             _P, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _I, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -116,6 +117,41 @@ def tokens_per_attention_tile(num_heads: int, num_kv_heads: int, dtype: torch.dt
     n = fn(num_heads, num_kv_heads, dtype_code(dtype), head_dim, page_size)
     _need(n > 0, f"{num_heads} query heads cannot share {num_kv_heads} key/value heads")
     return n
+
+
+def attention_max_segments(num_heads: int, num_kv_heads: int, dtype: torch.dtype, head_dim: int, page_size: int) -> int:
+    """How many items of the tile list may share the keys of one tile in the general attention kernel that serves
+    these sizes (1: it takes whole tiles only)."""
+    fn = library().llmp_attention_max_segments
+    fn.argtypes = [_I, _I, _I, _I, _I]
+    fn.restype = _I
+    return int(fn(num_heads, num_kv_heads, dtype_code(dtype), head_dim, page_size))
+
+
+ATTENTION_MAX_PLACES = 8192          # places for the sums of items that share a tile, per launch
+_attention_counters: dict = {}
+_place_floats: Optional[int] = None
+
+
+def attention_place_floats() -> int:
+    global _place_floats
+    if _place_floats is None:
+        fn = library().llmp_attention_place_floats
+        fn.argtypes = []
+        fn.restype = _L
+        _place_floats = int(fn())
+    return _place_floats
+
+
+def attention_counters(device: torch.device, count: int) -> torch.Tensor:
+    """Counters with which the items that share a tile find out who finishes last; every launch leaves them zero.
+    One set per device, as for ``decode_counters``."""
+    key = torch.device(device).index or 0
+    counters = _attention_counters.get(key)
+    if counters is None or counters.numel() < count:
+        _need(not torch.cuda.is_current_stream_capturing(), "attention counters must exist before a graph is captured")
+        counters = _attention_counters[key] = torch.zeros(max(count, 65536), dtype=torch.int32, device=device)
+    return counters
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -333,9 +369,14 @@ def gemm_stream_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: torch.Tensor,
                     block_tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
                     tile_req: torch.Tensor, tile_tok0: torch.Tensor, num_heads: int, num_kv_heads: int,
-                    head_dim: int, page_size: int, window: int, scale: float, tokens_per_tile: int) -> torch.Tensor:
+                    head_dim: int, page_size: int, window: int, scale: float, tokens_per_tile: int,
+                    tile_seg: Optional[torch.Tensor] = None, tile_slot: Optional[torch.Tensor] = None,
+                    places: int = 0) -> torch.Tensor:
     """Causal attention of the step's query rows over the paged keys and values (any portion sizes).
-    ``tokens_per_tile`` is the step the tile list was built with (``tokens_per_attention_tile``)."""
+    ``tokens_per_tile`` is the step the tile list was built with (``tokens_per_attention_tile``).
+    With ``tile_seg`` the list holds items that share the keys of a tile (see ``attention_max_segments``): item i is
+    number ``tile_seg[i] & 255`` of ``tile_seg[i] >> 8`` consecutive items of its tile, and ``tile_slot[i]`` is the
+    first of the tile's ``places`` (one per item) for their sums."""
     for name, t in (("block_tables", block_tables), ("q_start", q_start), ("ctx_len", ctx_len),
                     ("tile_req", tile_req), ("tile_tok0", tile_tok0)):
         _i32(t, name)
@@ -343,10 +384,20 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: to
     _need(out.is_contiguous() and out.shape[1] == num_heads * head_dim, "attention output must be [tokens, heads * head_dim]")
     _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (2, num_kv_heads, page_size, head_dim),
           "pages have the wrong layout")
+    seg = slot = partials = counters = None
+    if tile_seg is not None:
+        _i32(tile_seg, "tile_seg")
+        _i32(tile_slot, "tile_slot")
+        _need(tile_seg.numel() == tile_req.numel() == tile_slot.numel() and 0 < places <= ATTENTION_MAX_PLACES,
+              "tile_seg and tile_slot must have an entry per item, and the places a count within bounds")
+        partials = torch.empty(places * num_kv_heads * attention_place_floats(), dtype=torch.float32, device=q.device)
+        counters = attention_counters(q.device, places * num_kv_heads)
+        seg, slot = tile_seg, tile_slot
     _call("llmp_paged_attention", _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(pages), pages.shape[0],
           dtype_code(q.dtype), _ptr(block_tables), block_tables.stride(0), _ptr(q_start), _ptr(ctx_len),
-          _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), num_heads, num_kv_heads, head_dim, page_size,
-          int(window), float(scale), int(tokens_per_tile), error_flag().data_ptr(), _stream())
+          _ptr(tile_req), _ptr(tile_tok0), _ptr(seg), _ptr(slot), _ptr(partials), _ptr(counters), tile_req.numel(),
+          num_heads, num_kv_heads, head_dim, page_size, int(window), float(scale), int(tokens_per_tile),
+          error_flag().data_ptr(), _stream())
     return out
 
 

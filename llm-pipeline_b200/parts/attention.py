@@ -46,6 +46,7 @@ class PagedAttention(Mixer):
         self.rotary_dim = (head_dim if rotary_dim is None else int(rotary_dim)) if position else 0
         self.q_size, self.kv_size = num_heads * head_dim, num_kv_heads * head_dim
         self.tokens_per_tile: Optional[int] = None
+        self.max_key_segments = 1            # items that may share a tile's keys in the kernel for these sizes
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
 
     # -- what it asks of the cache --------------------------------------------------------
@@ -94,6 +95,8 @@ class PagedAttention(Mixer):
         if self.tokens_per_tile is None:
             self.tokens_per_tile = kernels.tokens_per_attention_tile(self.num_heads, self.num_kv_heads, x.dtype,
                                                                      self.head_dim, page_size)
+            self.max_key_segments = kernels.attention_max_segments(self.num_heads, self.num_kv_heads, x.dtype,
+                                                                   self.head_dim, page_size)
         qkv = linear(x, self.w_qkv)
         cos = sin = None
         if self.rotary_dim:

@@ -73,3 +73,47 @@ def test_decode_of_uneven_batch_shares_the_long_request(tmp_path):
     H.assert_close(H.replay(runner, steps), want, H.TOL[dtype], "uneven decode")
     assert runner.graph_replays > 0 and runner.cache.num_live == 0
     kernels.check_error_flag()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("config,seed,page,lengths", CASES)
+def test_mixed_batches_with_decoded_tokens_through_the_decode_kernel(tmp_path, monkeypatch, config, seed, page, lengths, dtype):
+    """In a step that mixes decoded tokens with portions of prompts, the single-token requests at its front go through
+    the decode kernel once one of them has a long context; here always, with the decoding requests put first as the scheduler
+    does."""
+    from llm_pipeline_b200.engine.context import StepContext
+    monkeypatch.setattr(StepContext, "SPLIT_DECODE_MIN_CONTEXT", 0)
+    folder, weights = H.make_case(tmp_path, config, seed, dtype)
+    requests = _requests(config, tuple(lengths) + (29, 12, 44, 7))
+    want = H.expected_logits(config, weights, requests)
+    runner = H.make_runner(folder, dtype, page_size=page, num_pages=4 * (-(-max(len(t) for t in requests.values()) // page)))
+    steps = [(sorted(entries, key=lambda e: len(e[1]) != 1), end)
+             for entries, end in H.cut_mixed(requests, (7, 2, 16, 3, 5), max_live=4, decode_tail=12)]
+    assert any(len(entries[0][1]) == 1 and len(entries[-1][1]) > 1 for entries, _ in steps)
+    H.assert_close(H.replay(runner, steps), want, H.TOL[dtype], "mixed, decode kernel for single tokens")
+    assert runner.cache.num_live == 0
+
+
+def test_prompt_portions_whose_tiles_share_their_keys(tmp_path, monkeypatch):
+    """Long contexts make the work list of the tcgen05 attention kernel cut a tile's keys into items; here from the
+    second key tile on, so that the tiny model's portions take that path: portions of changing size and mixed steps."""
+    from llm_pipeline_b200.engine.context import StepContext
+    from llm_pipeline_b200.ops import kernels
+    monkeypatch.setattr(StepContext, "SPLIT_KEYS_MIN_TILES", 1)
+    shared, launch = [], kernels.paged_attention
+
+    def counting(*args, **kwargs):
+        shared.append(args[18] if len(args) > 18 else kwargs.get("places", 0))
+        return launch(*args, **kwargs)
+
+    monkeypatch.setattr(kernels, "paged_attention", counting)
+    dtype = torch.bfloat16
+    folder, weights = H.make_case(tmp_path, plain.TINY_D, 7, dtype)
+    requests = _requests(plain.TINY_D, (533, 9, 262, 700))
+    want = H.expected_logits(plain.TINY_D, weights, requests)
+    runner = H.make_runner(folder, dtype, page_size=16, num_pages=128)
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, H.TOL[dtype], "whole")
+    H.assert_close(H.replay(runner, H.cut_portions(requests, (70, 2, 160, 33, 5))), want, H.TOL[dtype], "portions")
+    H.assert_close(H.replay(runner, H.cut_mixed(requests, (70, 2, 160, 33, 5), max_live=4)), want, H.TOL[dtype], "mixed")
+    assert runner.cache.num_live == 0 and max(shared) > 0
+    kernels.check_error_flag()

@@ -273,7 +273,8 @@ def attention_reference(q, k, v, window, scale):
     return torch.einsum("nts,snd->tnd", torch.softmax(scores, dim=-1), vv.double()).float()
 
 
-def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None, decode=False, uneven=False):
+def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=None, decode=False, uneven=False,
+              segments=1):
     """requests: list of (context_before, new_tokens). Pages are handed out in a scrambled order."""
     k_ = K()
     gen = torch.Generator().manual_seed(seed)
@@ -308,11 +309,15 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
         q_start.append(q_start[-1] + T)
         ctx.append(S)
     tpt = k_.tokens_per_attention_tile(nq, nkv, dtype, d, page_size)
-    tile_req, tile_tok0 = [], []
+    tile_req, tile_tok0, tile_seg, tile_slot = [], [], [], []
     for r, (_, T) in enumerate(requests):
         for t0 in range(0, T, tpt):
-            tile_req.append(r)
-            tile_tok0.append(t0)
+            # with segments: every tile as that many consecutive items that share its keys
+            for k in range(segments):
+                tile_req.append(r)
+                tile_tok0.append(t0)
+                tile_seg.append(k | segments << 8)
+                tile_slot.append(len(tile_req) - 1 - k)
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)   # noqa: E731
     out = torch.zeros(N, nq * d, dtype=dtype, device=DEV)
     scale = d ** -0.5
@@ -321,8 +326,9 @@ def run_paged(dtype, nq, nkv, d, page_size, requests, window=0, seed=0, boost=No
         k_.decode_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(ctx), max(ctx), nq, nkv, d, page_size,
                             window, scale, uneven=uneven)
     else:
+        shared = dict(tile_seg=dev(tile_seg), tile_slot=dev(tile_slot), places=len(tile_req)) if segments > 1 else {}
         k_.paged_attention(q, q.stride(0), out, pages, tables.to(DEV), dev(q_start), dev(ctx), dev(tile_req),
-                           dev(tile_tok0), nq, nkv, d, page_size, window, scale, tpt)
+                           dev(tile_tok0), nq, nkv, d, page_size, window, scale, tpt, **shared)
     want = torch.cat([attention_reference(q[q_start[r]:q_start[r + 1]].float().view(-1, nq, d).cpu(), ks[r].float().cpu(),
                                           vs[r].float().cpu(), window, scale) for r in range(R)])
     return out.float().cpu().view(N, nq, d), want
@@ -367,6 +373,24 @@ def test_decode_attention_head_size_128_streaming_kernel(nq, nkv, page, uneven):
                               uneven=uneven)
         assert torch.allclose(got, want, atol=3e-2), key_pos
         assert float(want[0, 5].abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("segments", [2, 3, 8])
+def test_prefill_attention_head_size_128_items_share_a_tile(segments):
+    """The tcgen05 kernel with every tile as several items that share its keys: each leaves its sums in global memory
+    and the last to finish adds them up. Contexts with fewer key tiles than items (items without keys), a window
+    that leaves some items nothing, one decisive key in an item in the middle; several launches in a row, since
+    the counters must be zero again."""
+    dtype = torch.bfloat16
+    assert K().attention_max_segments(8, 2, dtype, 128, 16) >= 8
+    requests = [(0, 37), (1130, 70), (63, 2), (300, 200), (5, 1), (700, 33)]
+    for seed, window in ((41, 0), (42, 0), (43, 200)):
+        boost = (1, 600, 5) if window == 0 else None
+        got, want = run_paged(dtype, 8, 2, 128, 16, requests, window=window, seed=seed, boost=boost, segments=segments)
+        assert torch.allclose(got, want, atol=3e-2), (seed, window, float((got - want).abs().max()))
+    K().check_error_flag()
+    with pytest.raises(Exception, match="whole tiles only"):
+        run_paged(dtype, 4, 2, 64, 16, [(100, 40)], segments=2)
 
 
 @pytest.mark.parametrize("contexts", [[40000, 10, 300, 129], [9000], [5], [3000, 2999, 3001, 1, 2, 3, 700, 700, 128],
