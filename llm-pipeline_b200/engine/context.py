@@ -44,10 +44,10 @@ class StepContext:
         self.num_logit_rows = 0
         self.table_width = 0
         self.decode_ctx_bound = 0            # when set: the context length the decode kernels size their grid for
-        self.contexts_uneven = False         # decode steps: one request is much longer than the average
+        self.decode_keys = (0, 0)            # decode steps: the most keys a request sees, and the keys of all
         self.leading_single = 0              # requests at the front of the step that bring one token each
         self.leading_longest = 0             # the most keys one of them sees
-        self.leading_uneven = False          # one of them sees far more keys than their average
+        self.leading_keys = 0                # the keys they see together
         # device side (int32)
         self.token_ids: torch.Tensor = None  # [N]
         self.positions: torch.Tensor = None  # [N]
@@ -116,7 +116,7 @@ class StepContext:
             kernels.decode_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group],
                                      self.ctx_len, self.decode_ctx_bound or self.max_ctx_len, mixer.num_heads,
                                      mixer.num_kv_heads, mixer.head_dim, page_size, mixer.window or 0, mixer.scale,
-                                     uneven=self.contexts_uneven or kernels.decode_rows_uneven(self.num_requests, mixer.num_kv_heads))
+                                     uneven=kernels.decode_prefers_list(*self.decode_keys, self.num_requests, mixer.num_kv_heads))
             return
         lead = 0
         if self.leading_single and self.leading_longest >= self.SPLIT_DECODE_MIN_CONTEXT:
@@ -128,7 +128,7 @@ class StepContext:
             kernels.decode_attention(qkv, qkv.stride(0), out[:lead], cache.pages, tables[:lead], self.ctx_len[:lead],
                                      self.leading_longest, mixer.num_heads, mixer.num_kv_heads, mixer.head_dim, page_size,
                                      mixer.window or 0, mixer.scale,
-                                     uneven=self.leading_uneven or kernels.decode_rows_uneven(lead, mixer.num_kv_heads))
+                                     uneven=kernels.decode_prefers_list(self.leading_longest, self.leading_keys, lead, mixer.num_kv_heads))
         tile_req, tile_tok0, tile_seg, tile_slot, places = self.attention_tiles(mixer.tokens_per_tile, lead, getattr(mixer, "max_key_segments", 1),
                                                                                 mixer.num_kv_heads)
         kernels.paged_attention(qkv, qkv.stride(0), out, cache.pages, self.block_tables[cache.group], self.q_start,

@@ -163,14 +163,13 @@ class ModelRunner:
         ctx.num_tokens, ctx.num_requests = q_start[-1], len(entries)
         ctx.max_q_len = max(ctx.q_lens)
         ctx.max_ctx_len = max(ctx_len)
-        ctx.contexts_uneven = ctx.max_q_len == 1 and kernels.decode_contexts_uneven(ctx_len)
+        ctx.decode_keys = (ctx.max_ctx_len, sum(ctx_len))
         lead = 0
         while lead < len(ctx.q_lens) and ctx.q_lens[lead] == 1:
             lead += 1
         ctx.leading_single = lead if lead < len(ctx.q_lens) else 0       # a step of single tokens only is a decode step
         if ctx.leading_single:
-            ctx.leading_longest = max(ctx_len[:lead])
-            ctx.leading_uneven = kernels.decode_contexts_uneven(ctx_len[:lead])
+            ctx.leading_longest, ctx.leading_keys = max(ctx_len[:lead]), sum(ctx_len[:lead])
         ctx.num_logit_rows = len(rows)
         if width is None:
             width = max(1, -(-ctx.max_ctx_len // ps))
@@ -239,7 +238,10 @@ class ModelRunner:
         step_w = self.GRAPH_WIDTH_STEP
         width = -(-max(1, -(-longest // ps)) // step_w) * step_w
         # a graph holds the decode kernel that was chosen when it was captured: even and uneven batches have their own
-        key = (len(entries), tuple(len(e.want) for e in entries), width, kernels.decode_contexts_uneven(lengths))
+        total = sum(lengths)
+        which = tuple(kernels.decode_prefers_list(longest, total, len(entries), getattr(group.spec, "num_kv_heads", 1))
+                      for group in cache.groups)
+        key = (len(entries), tuple(len(e.want) for e in entries), width, which)
         slot = self._graphs.get(key)
         if slot is None:
             if len(self._graphs) >= self.MAX_GRAPHS:

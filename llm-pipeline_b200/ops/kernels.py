@@ -422,18 +422,23 @@ def sm_count() -> int:
     return _sm_count
 
 
-def decode_contexts_uneven(ctx_lens: Sequence[int]) -> bool:
-    """Whether one request of a decode step is much longer than the average: its blocks would still be reading
-    when the others are done, unless the key ranges of all requests are dealt out evenly."""
-    longest, total, rows = max(ctx_lens), sum(ctx_lens), len(ctx_lens)
-    return longest * rows > 2 * total + 512 * rows
-
-
-def decode_rows_uneven(rows: int, num_kv_heads: int) -> bool:
-    """Many more (request, key/value head) pairs than SMs: whole pairs per block leave SMs idle in the last round,
-    and dealing the ranges out evenly then saves more than adding up the sums of shared pairs costs (Qwen3-8B heads,
-    2,048 keys each: from 64 requests on)."""
-    return rows * num_kv_heads > 2 * sm_count()
+def decode_prefers_list(longest: int, total: int, rows: int, num_kv_heads: int) -> bool:
+    """Whether a decode step over ``rows`` requests that see ``total`` keys together, the longest ``longest``, is
+    better served by the kernel that deals the key ranges of all requests out evenly over the SMs than by the one
+    that gives every (request, key/value head) pair blocks of its own. The latter walks as many keys per block as
+    the longest request needs with the up to 8 blocks a pair can get; the former the average, plus the adding up of
+    shared sums through global memory (worth about a thousand keys of reading). Also with many more pairs than SMs:
+    whole pairs per block then leave SMs idle in the last round (Qwen3-8B heads, 2,048 keys each: from 64 requests on)."""
+    sms = sm_count()
+    pairs = rows * num_kv_heads
+    if pairs > 2 * sms:
+        return True
+    blocks = 1
+    while blocks < 8 and pairs * blocks * 2 <= sms:
+        blocks *= 2
+    own = longest * -(-pairs // sms) / blocks
+    even = total * num_kv_heads / sms
+    return own > 1.25 * even + 1024
 
 
 def decode_counters(device: torch.device) -> torch.Tensor:
@@ -459,7 +464,7 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, pages: t
     """Attention of one query row per request (row r belongs to request r, at position ctx_len[r] - 1)
     over the request's pages; keys are split into fixed ranges whose partial results go through
     ``scratch`` (float32, at least ``decode_scratch_floats(...)`` entries; allocated when None).
-    ``uneven`` (see ``decode_contexts_uneven`` and ``decode_rows_uneven``) picks, where there is a choice, the kernel that deals the key ranges of
+    ``uneven`` (see ``decode_prefers_list``) picks, where there is a choice, the kernel that deals the key ranges of
     all requests out evenly over the SMs instead of giving every request blocks of its own; the result is the same
     beyond rounding. ``LLMP_B200_DECODE_LIST=0`` or ``1`` overrides it."""
     if _DECODE_LIST in ("0", "1"):

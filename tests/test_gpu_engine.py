@@ -55,9 +55,12 @@ def test_mixed_batches_with_page_reuse(tmp_path, config, seed, page, lengths, dt
     assert runner.cache.num_live == 0
 
 
-def test_decode_of_uneven_batch_shares_the_long_request(tmp_path):
-    """One request far longer than the others: the decode steps (eager, then as a replayed graph of its own) take
-    the attention kernel that deals key ranges out over all SMs; logits as from the plain implementation."""
+def test_decode_of_uneven_batch_shares_the_long_request(tmp_path, monkeypatch):
+    """One request far longer than the others: the decode steps (eager, then as a replayed graph) take the attention
+    kernel that deals key ranges out over all SMs (forced here: at this tiny size the other one would be chosen);
+    logits as from the plain implementation."""
+    from llm_pipeline_b200.ops import kernels
+    monkeypatch.setattr(kernels, "_DECODE_LIST", "1")
     dtype = torch.bfloat16
     folder, weights = H.make_case(tmp_path, plain.TINY_D, 5, dtype)
     requests = _requests(plain.TINY_D, (1700, 20, 60), extra=10)
@@ -68,8 +71,6 @@ def test_decode_of_uneven_batch_shares_the_long_request(tmp_path):
     for i in range(tail):
         at = {rid: len(toks) - tail + i for rid, toks in requests.items()}
         steps.append(([(rid, [toks[at[rid]]], [0]) for rid, toks in requests.items()], list(requests) if i == tail - 1 else []))
-    from llm_pipeline_b200.ops import kernels
-    assert kernels.decode_contexts_uneven([len(t) - tail + 1 for t in requests.values()])
     H.assert_close(H.replay(runner, steps), want, H.TOL[dtype], "uneven decode")
     assert runner.graph_replays > 0 and runner.cache.num_live == 0
     kernels.check_error_flag()
@@ -117,3 +118,15 @@ def test_prompt_portions_whose_tiles_share_their_keys(tmp_path, monkeypatch):
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (70, 2, 160, 33, 5), max_live=4)), want, H.TOL[dtype], "mixed")
     assert runner.cache.num_live == 0 and max(shared) > 0
     kernels.check_error_flag()
+
+
+def test_which_decode_kernel_a_step_takes():
+    """Blocks of its own for every request while contexts are even; key ranges dealt out evenly when one request would
+    keep its blocks reading long after the others, or when requests are many (Qwen3-8B heads on the GPU's SMs)."""
+    from llm_pipeline_b200.ops import kernels
+
+    def takes_list(contexts, kv_heads=8):
+        return kernels.decode_prefers_list(max(contexts), sum(contexts), len(contexts), kv_heads)
+
+    assert not takes_list([2048]) and not takes_list([2048] * 8) and not takes_list([16384] * 8) and not takes_list([2048] * 32)
+    assert takes_list([131072]) and takes_list([32768, 600]) and takes_list([16384] + [512] * 7) and takes_list([2048] * 64)
