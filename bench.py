@@ -131,7 +131,7 @@ def prefill_flops(cfg, layers, T):
     return layers * (per_token * T + attention) + 2 * V * H
 
 
-def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256):
+def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256, pages=None):
     import torch
 
     from llm_pipeline_b200.config import resolve_config
@@ -144,7 +144,8 @@ def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256):
     config = resolve_config({**cfg, "num_hidden_layers": layers})
     model = build_model(config)
     model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
-    pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
+    if pages is None:
+        pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
     engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=pages, max_num_seqs=batch_cap,
                               max_num_batched_tokens=PREFILL_TOKENS, max_model_len=tokens_per_request)
     return engine
@@ -157,9 +158,10 @@ def random_prompts(vocab, count, length, seed):
     return torch.randint(0, vocab, (count, length), generator=gen).tolist()
 
 
-def time_decode(engine, batch, steps, warmup, seed, e2e=True):
+def time_decode(engine, batch, steps, warmup, seed, e2e=True, contexts=None):
     """Device-timed decode steps through the step function, and wall-clock steps through
-    ``GenerationEngine.step`` (host lists in and out). Returns a dict of figures."""
+    ``GenerationEngine.step`` (host lists in and out). Returns a dict of figures. ``contexts``: the
+    requests' context lengths when they are not all CONTEXT (device-timed part only)."""
     import torch
 
     from llm_pipeline_b200.engine import StepEntry
@@ -167,12 +169,16 @@ def time_decode(engine, batch, steps, warmup, seed, e2e=True):
     from llm_pipeline_b200.sampling import SamplingConfig
 
     vocab = engine.model.spec.vocab_size
-    prompts = random_prompts(vocab, batch, CONTEXT - 1, seed)
+    if contexts is None:
+        prompts = random_prompts(vocab, batch, CONTEXT - 1, seed)
+    else:
+        prompts = [random_prompts(vocab, 1, n - 1, seed + i)[0] for i, n in enumerate(contexts)]
     runner = engine.runner
     ids = [f"bench{seed}_{i}" for i in range(batch)]
-    # fill the cache: every request gets CONTEXT - 1 tokens, in portions of up to 2,048 tokens
+    # fill the cache: every request gets its context less one token, in portions of up to 2,048 tokens
     for rid, prompt in zip(ids, prompts):
-        runner.step([StepEntry(rid, prompt, [])])
+        for at in range(0, len(prompt), PREFILL_TOKENS):
+            runner.step([StepEntry(rid, prompt[at:at + PREFILL_TOKENS], [])])
     last = [p[-1] for p in prompts]
     out = torch.empty(batch, dtype=torch.int32, device=engine.device)
 
@@ -292,7 +298,17 @@ def run_ours(args):
     dtype = torch.bfloat16
     # room per request: the context, the set-up, warm-up and timed decode steps, in whole pages
     room = -(-(CONTEXT + 64 + args.warmup + args.steps) // 256) * 256
-    engine = build_ours(cfg, layers, max(64, args.batch), dtype, tokens_per_request=max(CONTEXT + 256, room))
+    contexts = [int(n) for n in args.contexts.split(",")] if args.contexts else None
+    if contexts:
+        if args.only != "decode":
+            print("--contexts goes with --only decode")
+            return 2
+        args.batch = len(contexts)
+        longest = -(-(max(contexts) + 64 + args.warmup + args.steps) // 256) * 256
+        pages = sum(-(-(n + 64 + args.warmup + args.steps) // PAGE_SIZE) for n in contexts)
+        engine = build_ours(cfg, layers, args.batch, dtype, tokens_per_request=longest, pages=pages)
+    else:
+        engine = build_ours(cfg, layers, max(64, args.batch), dtype, tokens_per_request=max(CONTEXT + 256, room))
     clocks = ClockSampler()
     clocks.start()
     if args.only == "prefill":
@@ -300,10 +316,13 @@ def run_ours(args):
         prefill_ms = time_prefill(engine, PREFILL_TOKENS, repeats=2, warmup=3)
         print(json.dumps({"only": "prefill", "layers": layers, "prefill_ms": round(prefill_ms, 3)}))
         return 0
-    main = time_decode(engine, args.batch, args.steps, args.warmup, seed=1, e2e=args.only == "all")
+    main = time_decode(engine, args.batch, args.steps, args.warmup, seed=1, e2e=args.only == "all", contexts=contexts)
     clock_info = clocks.stop()
     if args.only == "decode":
-        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(main["ms"], 4)}))
+        line = {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(main["ms"], 4)}
+        if contexts:
+            line["contexts"] = args.contexts
+        print(json.dumps(line))
         return 0
     points = {}
     for b in (1, 64):
@@ -415,6 +434,8 @@ def main() -> int:
     parser.add_argument("--shape", default="8b", choices=tuple(SHAPES), help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--workload", default="decode", choices=("decode", "mix"),
                         help="mix: the continuous-batching mix of 64 requests through the Python entry point")
+    parser.add_argument("--contexts", default="", help="with --only decode: the requests' context lengths, comma-separated "
+                        "(a batch of uneven lengths), instead of --batch requests of 2,048 tokens")
     parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
                         help="run one part only (for profiler captures on a small case); the line then lacks the other parts")
     args = parser.parse_args()
