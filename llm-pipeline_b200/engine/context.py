@@ -72,33 +72,8 @@ class StepContext:
         key = (tokens_per_tile, first_request, max_segments, num_kv_heads)
         tiles = self._tiles.get(key)
         if tiles is None:
-            found = []
-            for r in range(first_request, len(self.q_lens)):
-                n = self.q_lens[r]
-                before = self.starts[r]
-                for t in range(0, n, tokens_per_tile):
-                    found.append((before + min(t + tokens_per_tile, n), r, t))
-            segments = [1] * len(found)
-            blocks = len(found) * num_kv_heads
-            target = self.SPLIT_KEYS_FILL * kernels.sm_count()
-            if max_segments > 1 and blocks <= self.SPLIT_KEYS_BELOW * kernels.sm_count():
-                key_tiles = [-(-f[0] // self.KEY_TILE) for f in found]
-                want = target // blocks                      # never more than SPLIT_KEYS_FILL full rounds of blocks
-                segments = [max(1, min(max_segments, want, k // self.SPLIT_KEYS_MIN_TILES)) for k in key_tiles]
-                if sum(n for n in segments if n > 1) * num_kv_heads > kernels.ATTENTION_MAX_PLACES:
-                    segments = [1] * len(found)
-            # in the order of the keys an item sees: the kernels start the last item first, the longest blocks lead
-            order = sorted(range(len(found)), key=lambda i: (found[i][0] / segments[i], found[i][1], found[i][2]))
-            req, tok0, seg, slot = [], [], [], []
-            places = 0
-            for i in order:
-                for k in range(segments[i]):
-                    req.append(found[i][1])
-                    tok0.append(found[i][2])
-                    seg.append(k | segments[i] << 8)
-                    slot.append(places if segments[i] > 1 else 0)
-                if segments[i] > 1:
-                    places += segments[i]
+            req, tok0, seg, slot, places = self.plan_attention_items(self.starts, self.q_lens, tokens_per_tile, first_request,
+                                                                     max_segments, num_kv_heads, kernels.sm_count())
             rows = [req, tok0] + ([seg, slot] if places else [])
             host = torch.tensor(rows, dtype=torch.int32).pin_memory()
             dev = host.to(self.device, non_blocking=True)
@@ -106,6 +81,39 @@ class StepContext:
                      dev[3].contiguous() if places else None, places)
             self._tiles[key] = tiles
         return tiles
+
+    @classmethod
+    def plan_attention_items(cls, starts: List[int], q_lens: List[int], tokens_per_tile: int, first_request: int,
+                             max_segments: int, num_kv_heads: int, sms: int):
+        """The work list of ``attention_tiles`` as host lists (request, first token, item of its tile | items << 8,
+        first place of the tile) and the number of places, for a GPU of ``sms`` SMs."""
+        found = []
+        for r in range(first_request, len(q_lens)):
+            n = q_lens[r]
+            before = starts[r]
+            for t in range(0, n, tokens_per_tile):
+                found.append((before + min(t + tokens_per_tile, n), r, t))
+        segments = [1] * len(found)
+        blocks = len(found) * num_kv_heads
+        if max_segments > 1 and blocks <= cls.SPLIT_KEYS_BELOW * sms:
+            key_tiles = [-(-f[0] // cls.KEY_TILE) for f in found]
+            want = cls.SPLIT_KEYS_FILL * sms // blocks       # never more than SPLIT_KEYS_FILL full rounds of blocks
+            segments = [max(1, min(max_segments, want, k // cls.SPLIT_KEYS_MIN_TILES)) for k in key_tiles]
+            if sum(n for n in segments if n > 1) * num_kv_heads > kernels.ATTENTION_MAX_PLACES:
+                segments = [1] * len(found)
+        # in the order of the keys an item sees: the kernels start the last item first, the longest blocks lead
+        order = sorted(range(len(found)), key=lambda i: (found[i][0] / segments[i], found[i][1], found[i][2]))
+        req, tok0, seg, slot = [], [], [], []
+        places = 0
+        for i in order:
+            for k in range(segments[i]):
+                req.append(found[i][1])
+                tok0.append(found[i][2])
+                seg.append(k | segments[i] << 8)
+                slot.append(places if segments[i] > 1 else 0)
+            if segments[i] > 1:
+                places += segments[i]
+        return req, tok0, seg, slot, places
 
     def attention(self, mixer, qkv: torch.Tensor, out: torch.Tensor, cache) -> None:
         """Causal attention of the step's query rows (the first ``num_heads * head_dim`` columns of

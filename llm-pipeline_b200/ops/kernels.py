@@ -422,14 +422,14 @@ def sm_count() -> int:
     return _sm_count
 
 
-def decode_prefers_list(longest: int, total: int, rows: int, num_kv_heads: int) -> bool:
+def decode_prefers_list(longest: int, total: int, rows: int, num_kv_heads: int, sms: Optional[int] = None) -> bool:
     """Whether a decode step over ``rows`` requests that see ``total`` keys together, the longest ``longest``, is
     better served by the kernel that deals the key ranges of all requests out evenly over the SMs than by the one
     that gives every (request, key/value head) pair blocks of its own. The latter walks as many keys per block as
     the longest request needs with the up to 8 blocks a pair can get; the former the average, plus the adding up of
     shared sums through global memory (worth about a thousand keys of reading). Also with many more pairs than SMs:
     whole pairs per block then leave SMs idle in the last round (Qwen3-8B heads, 2,048 keys each: from 64 requests on)."""
-    sms = sm_count()
+    sms = sms or sm_count()
     pairs = rows * num_kv_heads
     if pairs > 2 * sms:
         return True
