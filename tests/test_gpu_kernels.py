@@ -394,13 +394,13 @@ def test_prefill_attention_head_size_128_items_share_a_tile(segments):
 
 
 @pytest.mark.parametrize("contexts", [[40000, 10, 300, 129], [9000], [5], [3000, 2999, 3001, 1, 2, 3, 700, 700, 128],
-                                      [20000] * 3 + [17] * 40, [511] * 150])
+                                      [20000] * 3 + [17] * 40, [511] * 150, [9000] + [40] * 530])
 @pytest.mark.parametrize("uneven", [True, False])
 def test_decode_attention_streaming_kernel_shares_long_requests(contexts, uneven):
     """The kernel for uneven batches deals the 128-key ranges of all requests out evenly: a request far longer than
     the others is shared by many blocks, whose sums the last of them to finish adds up. One decisive key in the long
     request, in a range of a block in the middle; several times in a row, since the blocks' counters must be zero
-    again. The kernel for even batches takes the same batches, only slower."""
+    again. The kernel for even batches takes the same batches, only slower, and those of more than 512 requests."""
     dtype = torch.bfloat16
     requests = [(c, 1) for c in contexts]
     key_pos = contexts[0] // 2
