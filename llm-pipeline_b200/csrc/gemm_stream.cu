@@ -48,6 +48,21 @@ struct StreamParams {
     int stages;
     int out_f32;
     int glu_rows;         // 0, or I: W is [gate rows; up rows] of I rows each and Y[m, i] = silu(gate_i . x_m) * (up_i . x_m)
+    // Rows of X that still lack a factor (M <= 8): row m of the product is multiplied by
+    // rsqrt(sum over in_parts of in_sumsq[part][m] * in_inv_width + in_eps) before anything else is done with it.
+    const float* in_sumsq;
+    int in_parts;
+    float in_inv_width, in_eps;
+    // The product as an addend of a float32 residual that a norm follows (M <= 8): r = residual + product is stored back,
+    // r * norm_w goes to xw in bfloat16, and this block's sums of r^2 over its columns go to out_sumsq[block][m], from
+    // which the next product takes the rows' factors. Y is not written.
+    float* residual;
+    long ldr;
+    const void* norm_w;
+    int norm_w_f32;
+    bf16* xw;
+    long ldxw;
+    float* out_sumsq;
     int* error_flag;
 };
 
@@ -86,6 +101,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const StreamParams p) {
     extern __shared__ unsigned char gs_raw[];
     __shared__ __align__(8) uint64_t full_bar[GS_MAX_STAGES], empty_bar[GS_MAX_STAGES];
+    __shared__ float row_factor[8];                              // in_sumsq: the rows' factors
     const uint32_t raw_addr = tc_smem_u32(gs_raw);
     unsigned char* ring = gs_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);      // 1024-byte aligned stages
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,6 +186,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int i = 0; i < MT; ++i)
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+        // 16 threads per row of X: thread `part16` of row `row16`
+        const int row16 = tid >> 4, part16 = tid & 15;
+        float block_squares = 0.f;                               // residual: this block's sum of r^2 of row row16 (in part16 == 0)
+        if (p.in_sumsq != nullptr) {
+            // The rows' factors, while the boxes of X are on their way: the sums of squares that the blocks of the
+            // product before left, added in a fixed order (16 threads a row, each its parts in turn, then a tree).
+            pdl_wait();
+            float sum = 0.f;
+            if (row16 < p.M)
+                for (int b = part16; b < p.in_parts; b += 16) sum += p.in_sumsq[(size_t)b * 8 + row16];
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (part16 == 0 && row16 < p.M) row_factor[row16] = rsqrtf(sum * p.in_inv_width + p.in_eps);
+        }
         const int steps16 = 4 * p.KB;                            // 16-element K steps per stage
         const int mine = (p.stages - warp + GS_CWARPS - 1) / GS_CWARPS;      // ring slots of this warp: warp, warp + 4, ...
         int j = 0;                                               // stages this warp has taken
@@ -224,11 +254,36 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int n0 = row_begin + sub * p.RB;               // first column of Y of this chunk
             int rows = row_end - n0;
             if (rows > p.RB) rows = p.RB;
+            if (p.residual != nullptr) {
+                // Thread part16 of row row16 takes the columns part16, part16 + 16, ... of its row: r = residual + product,
+                // r * norm weight for the next product, and r^2 added in a fixed order (its columns in turn, then a tree).
+                float sum = 0.f;
+                if (row16 < p.M) {
+                    for (int c = part16; c < rows; c += 16) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * p.part_rows + c) * pstride + row16];
+                        if (p.in_sumsq != nullptr) v *= row_factor[row16];
+                        const int n = n0 + c;
+                        const float r = p.residual[(size_t)row16 * p.ldr + n] + v;
+                        p.residual[(size_t)row16 * p.ldr + n] = r;
+                        const float wn = p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n]
+                                                      : __bfloat162float(reinterpret_cast<const bf16*>(p.norm_w)[n]);
+                        p.xw[(size_t)row16 * p.ldxw + n] = __float2bfloat16_rn(r * wn);
+                        sum = fmaf(r, r, sum);
+                    }
+                }
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                block_squares += sum;
+                continue;
+            }
             for (int e = tid; e < rows * p.M; e += GS_CWARPS * 32) {
                 const int m = e / rows, row = e - m * rows;     // consecutive threads store consecutive columns of Y
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * p.part_rows + row) * pstride + m];
+                if (p.in_sumsq != nullptr) v *= row_factor[m];
                 if (p.glu_rows) {
                     float* kept = gate + (size_t)(sub * p.RB + row) * (8 * NT) + m;
                     if (chunk < half_chunks) {                   // a gate chunk: kept for the up chunk of the same rows
@@ -242,6 +297,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 else reinterpret_cast<bf16*>(p.Y)[(size_t)m * p.ldy + n0 + row] = __float2bfloat16_rn(v);
             }
         }
+        if (p.residual != nullptr && part16 == 0) p.out_sumsq[(size_t)blockIdx.x * 8 + row16] = row16 < p.M ? block_squares : 0.f;
     }
 }
 
@@ -351,12 +407,24 @@ LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) 
 }
 
 // X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; shapes as llmp_gemm_stream_supports says.
+struct StreamExtras {                                           // see StreamParams
+    const float* in_sumsq = nullptr;
+    int in_parts = 0;
+    float in_inv_width = 0.f, in_eps = 0.f;
+    float* residual = nullptr;
+    long ldr = 0;
+    const void* norm_w = nullptr;
+    int norm_w_f32 = 0;
+    void* xw = nullptr;
+    long ldxw = 0;
+    float* out_sumsq = nullptr;
+};
 static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
-                              long ldy, int glu_rows, int* error_flag, cudaStream_t stream);
+                              long ldy, int glu_rows, const StreamExtras& extras, int* error_flag, cudaStream_t stream);
 
 LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
                               long ldy, int* error_flag, cudaStream_t stream) {
-    return gemm_stream_launch(X, W, Y, out_dtype, M, N, K, ldx, ldw, ldy, 0, error_flag, stream);
+    return gemm_stream_launch(X, W, Y, out_dtype, M, N, K, ldx, ldw, ldy, 0, StreamExtras(), error_flag, stream);
 }
 
 // W holds the I gate rows and then the I up rows of a SwiGLU feed-forward (N = 2 I rows of K):
@@ -368,11 +436,44 @@ LLMP_API int llmp_gemm_stream_swiglu_supports(int M, int I, int K, long ldx, lon
 
 LLMP_API int llmp_gemm_stream_swiglu(const void* X, const void* W, void* Y, int out_dtype, int M, int I, int K, long ldx,
                                      long ldw, long ldy, int* error_flag, cudaStream_t stream) {
-    return gemm_stream_launch(X, W, Y, out_dtype, M, 2 * I, K, ldx, ldw, ldy, I, error_flag, stream);
+    return gemm_stream_launch(X, W, Y, out_dtype, M, 2 * I, K, ldx, ldw, ldy, I, StreamExtras(), error_flag, stream);
+}
+
+// Blocks that a product of these sizes is dealt out to (each leaves one row of out_sumsq); 0: the sizes are not taken.
+LLMP_API int llmp_gemm_stream_blocks(int M, int N, int K, long ldx, long ldw) {
+    StreamPlan q;
+    return stream_plan(M, N, K, ldx, ldw, 0, &q) ? q.grid : 0;
+}
+
+// The streaming product between a norm and the residual sum, for at most 8 rows of X. Either part may be left out.
+//  - in_sumsq != null: the rows of X lack the factor rsqrt(sum of in_sumsq[0 .. in_parts)[m] * in_inv_width + in_eps); the
+//    product is multiplied by it (before SwiGLU when glu_rows = N / 2 > 0: W is then [gate rows; up rows], Y is [M, N / 2]).
+//  - residual != null (glu_rows = 0, N the width of the residual): residual[m, n] += product, xw[m, n] =
+//    bfloat16(residual[m, n] * norm_w[n]) and out_sumsq[block][m] = this block's sum of residual[m, n]^2 (8 floats a block,
+//    llmp_gemm_stream_blocks(...) blocks); Y is not written. xw and out_sumsq are what the next product takes as X and in_sumsq.
+LLMP_API int llmp_gemm_stream_fused(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
+                                    long ldy, int glu_rows, const float* in_sumsq, int in_parts, float in_inv_width,
+                                    float in_eps, float* residual, long ldr, const void* norm_w, int norm_w_dtype, void* xw,
+                                    long ldxw, float* out_sumsq, int* error_flag, cudaStream_t stream) {
+    LLMP_REQUIRE(M <= 8, "gemm_stream: the fused forms take at most 8 rows, not %d", M);
+    LLMP_REQUIRE(glu_rows == 0 || glu_rows * 2 == N, "gemm_stream: %d gate rows do not make %d rows of W", glu_rows, N);
+    StreamExtras e;
+    if (in_sumsq != nullptr) {
+        LLMP_REQUIRE(in_parts > 0, "gemm_stream: sums of squares need their number");
+        e.in_sumsq = in_sumsq; e.in_parts = in_parts; e.in_inv_width = in_inv_width; e.in_eps = in_eps;
+    }
+    if (residual != nullptr) {
+        LLMP_REQUIRE(glu_rows == 0 && norm_w != nullptr && xw != nullptr && out_sumsq != nullptr,
+                     "gemm_stream: the residual form needs a norm weight and places for its results, and no SwiGLU");
+        LLMP_REQUIRE(norm_w_dtype == LLMP_F32 || norm_w_dtype == LLMP_BF16, "gemm_stream: norm weights are float32 or bfloat16");
+        e.residual = residual; e.ldr = ldr; e.norm_w = norm_w; e.norm_w_f32 = norm_w_dtype == LLMP_F32; e.xw = xw; e.ldxw = ldxw;
+        e.out_sumsq = out_sumsq;
+    }
+    return gemm_stream_launch(X, W, Y, out_dtype, M, N, K, ldx, ldw, ldy, glu_rows, e, error_flag, stream);
 }
 
 static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dtype, int M, int N, int K, long ldx, long ldw,
-                              long ldy, int glu_rows, int* error_flag, cudaStream_t stream) {
+                              long ldy, int glu_rows, const StreamExtras& extras, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     StreamPlan q;
     LLMP_REQUIRE(stream_plan(M, N, K, ldx, ldw, glu_rows, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
@@ -381,6 +482,9 @@ static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dty
     StreamParams p;
     p.Y = Y; p.ldy = ldy; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == LLMP_F32; p.error_flag = error_flag;
     p.glu_rows = glu_rows;
+    p.in_sumsq = extras.in_sumsq; p.in_parts = extras.in_parts; p.in_inv_width = extras.in_inv_width; p.in_eps = extras.in_eps;
+    p.residual = extras.residual; p.ldr = extras.ldr; p.norm_w = extras.norm_w; p.norm_w_f32 = extras.norm_w_f32;
+    p.xw = (bf16*)extras.xw; p.ldxw = extras.ldxw; p.out_sumsq = extras.out_sumsq;
     p.per = q.per; p.RB = q.rb; p.MB = 8 * q.nt; p.KB = q.kb; p.part_rows = q.mt * 16; p.stages = q.stages;
     const int grid = q.grid, rb = q.rb, kb = q.kb, nt = q.nt, mt = q.mt;
     const size_t smem = q.smem;

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "llmp_gemm_stream_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P, _P],
     "llmp_paged_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                              _P, _P],
+    "llmp_gemm_stream_fused": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _L, _P, _P, _P],
     "llmp_decode_attention": [_P, _L, _P, _L, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _L, _P, _I, _P, _P],
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
@@ -343,6 +344,53 @@ def gemm_stream_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch
     _call("llmp_gemm_stream_tc", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0), w.stride(0),
           out.stride(0), error_flag().data_ptr(), _stream())
     return out
+
+
+def gemm_stream_blocks(M: int, N: int, K: int, ldx: int, ldw: int) -> int:
+    """Blocks that ``gemm_stream`` deals a product of these sizes out to (0: sizes it does not take)."""
+    fn = library().llmp_gemm_stream_blocks
+    fn.argtypes = [_I, _I, _I, _L, _L]
+    fn.restype = _I
+    return int(fn(M, N, K, ldx, ldw))
+
+
+def gemm_stream_fused(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], *, glu: bool = False,
+                      in_sumsq: Optional[torch.Tensor] = None, in_parts: int = 0, in_width: int = 0, in_eps: float = 0.0,
+                      residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                      xw: Optional[torch.Tensor] = None, out_sumsq: Optional[torch.Tensor] = None) -> None:
+    """The streaming product (at most 8 rows of x) with the work of the RMSNorm around it folded in.
+
+    ``in_sumsq`` [parts, 8] float32: the rows of ``x`` still lack the factor rsqrt(sum(in_sumsq[:in_parts, m]) / in_width +
+    in_eps); the product is multiplied by it (with ``glu`` before the SwiGLU of ``w`` = [gate rows; up rows]).
+    ``residual`` [M, N] float32: the product is added into it; ``xw`` [M, N] bfloat16 receives residual * norm_weight and
+    ``out_sumsq`` [gemm_stream_blocks(...), 8] each block's sums of residual^2, which are what the next product takes as
+    ``x`` and ``in_sumsq``; ``out`` is then not written and may be None."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= 8, "gemm_stream_fused takes up to 8 bfloat16 rows")
+    _need(w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1, "gemm operands must be row-major and match")
+    if out is not None:
+        _need(out.shape == (M, N // 2 if glu else N) and out.stride(1) == 1, "gemm output has the wrong shape")
+    if in_sumsq is not None:
+        _need(in_sumsq.dtype == torch.float32 and in_sumsq.is_contiguous() and in_sumsq.shape[1] == 8 and
+              0 < in_parts <= in_sumsq.shape[0] and in_width > 0, "sums of squares must be [parts, 8] float32")
+    if residual is not None:
+        _need(not glu and out_sumsq is not None and xw is not None and norm_weight is not None,
+              "the residual form needs a norm weight, xw and out_sumsq, and no SwiGLU")
+        _need(residual.dtype == torch.float32 and residual.shape == (M, N) and residual.stride(1) == 1, "residual must be [M, N] float32")
+        _need(xw.dtype == torch.bfloat16 and xw.shape == (M, N) and xw.stride(1) == 1, "xw must be [M, N] bfloat16")
+        _need(norm_weight.numel() == N and norm_weight.is_contiguous() and norm_weight.dtype in (torch.float32, torch.bfloat16),
+              "the norm weight must have N entries")
+        _need(out_sumsq.dtype == torch.float32 and out_sumsq.is_contiguous() and out_sumsq.shape[1] == 8 and
+              out_sumsq.shape[0] >= gemm_stream_blocks(M, N, K, x.stride(0), w.stride(0)) > 0, "out_sumsq must be [blocks, 8] float32")
+    else:
+        _need(out is not None, "a product that is no residual addend needs an output")
+    _call("llmp_gemm_stream_fused", _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype) if out is not None else BF16, M, N, K,
+          x.stride(0), w.stride(0), out.stride(0) if out is not None else 0, N // 2 if glu else 0,
+          _ptr(in_sumsq), int(in_parts), 1.0 / in_width if in_width else 0.0, float(in_eps),
+          _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
+          dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), xw.stride(0) if xw is not None else 0,
+          _ptr(out_sumsq), error_flag().data_ptr(), _stream())
 
 
 def gemm_stream_swiglu_supports(M: int, I: int, K: int, ldx: int, ldw: int) -> bool:

@@ -25,6 +25,86 @@ def register_bf16_kernel(fn: Callable) -> None:
     _BF16_KERNELS.append(fn)
 
 
+# ---- a norm between two streaming products, folded into them ------------------------------------------------
+# A decode step of a few rows spends as long between kernels as in them, and the residual add with its RMSNorm is a
+# kernel of its own between the product before it and the product after it. RMSNorm is a factor per row: x_norm[m] =
+# (r[m] * w) * rsqrt(mean(r[m]^2) + eps). So the product before it can add its result into the residual r, leave r * w
+# (rounded once to bfloat16, as the norm's output is) and its share of the rows' sums of squares, and the product
+# after it multiplies its result by the rows' factors: no kernel in between. FUSE_NORM=0 (LLMP_B200_FUSE_NORM) keeps
+# the norm kernel.
+FUSE_NORM = os.environ.get("LLMP_B200_FUSE_NORM", "1") == "1"
+
+
+class PendingProduct:
+    """``x @ weight^T`` that has not been taken yet. A norm that can fold the product into its own work asks for
+    ``x`` and ``weight``; everybody else calls ``value()``."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor):
+        self.x, self.weight = x, weight
+
+    def value(self) -> torch.Tensor:
+        return linear(self.x, self.weight)
+
+
+class ScaledRows:
+    """Rows that still lack a factor each: ``values`` [M, width] bfloat16 and, per row m, the factor
+    rsqrt(sum(sumsq[:parts, m]) / width + eps). A product that can apply the factors to its result takes the fields;
+    everybody else calls ``value()``, which has ``materialise`` (given by whoever made the rows) build the finished rows."""
+
+    def __init__(self, values: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float, materialise: Callable[[], torch.Tensor]):
+        self.values, self.sumsq, self.parts, self.eps = values, sumsq, int(parts), float(eps)
+        self._materialise = materialise
+        self._value: Optional[torch.Tensor] = None
+
+    shape = property(lambda self: self.values.shape)
+    dtype = property(lambda self: self.values.dtype)
+    device = property(lambda self: self.values.device)
+
+    def value(self) -> torch.Tensor:
+        if self._value is None:
+            self._value = self._materialise()
+        return self._value
+
+
+def pending_product(x: torch.Tensor, weight: torch.Tensor):
+    """``x @ weight^T`` as a PendingProduct where a following norm could fold it in (the sizes of the streaming
+    product for at most 8 bfloat16 rows), else the product itself."""
+    M, K = x.shape
+    if (FUSE_NORM and STREAM_GEMM and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and 0 < M <= 8 and
+            x.stride(1) == 1 and weight.stride(1) == 1 and not x.data_ptr() % 16 and not weight.data_ptr() % 16 and
+            kernels.gemm_stream_blocks(M, weight.shape[0], K, x.stride(0), weight.stride(0)) > 0):
+        return PendingProduct(x, weight)
+    return linear(x, weight)
+
+
+def residual_product(product: PendingProduct, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                     materialise: Callable[[], torch.Tensor]) -> ScaledRows:
+    """residual += product; returns residual * norm_weight with the rows' factors still to be applied."""
+    x, weight = product.x, product.weight
+    M, N = x.shape[0], weight.shape[0]
+    blocks = kernels.gemm_stream_blocks(M, N, x.shape[1], x.stride(0), weight.stride(0))
+    xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    sumsq = torch.empty((blocks, 8), dtype=torch.float32, device=x.device)
+    kernels.gemm_stream_fused(x, weight, None, residual=residual, norm_weight=norm_weight, xw=xw, out_sumsq=sumsq)
+    return ScaledRows(xw, sumsq, blocks, eps, materialise)
+
+
+def _scaled_stream(x: ScaledRows, weight: torch.Tensor, glu: bool) -> Optional[torch.Tensor]:
+    values = x.values
+    M, K = values.shape
+    N = weight.shape[0]
+    if not STREAM_GEMM or weight.stride(1) != 1 or weight.data_ptr() % 16 or (glu and N % 2):
+        return None
+    if glu:
+        if not kernels.gemm_stream_swiglu_supports(M, N // 2, K, values.stride(0), weight.stride(0)):
+            return None
+    elif not kernels.gemm_stream_supports(M, N, K, values.stride(0), weight.stride(0)):
+        return None
+    out = torch.empty((M, N // 2 if glu else N), dtype=values.dtype, device=values.device)
+    kernels.gemm_stream_fused(values, weight, out, glu=glu, in_sumsq=x.sumsq, in_parts=x.parts, in_width=K, in_eps=x.eps)
+    return out
+
+
 def _stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """The weight-streaming kernel for the few rows of a decode step: one persistent block per SM, the rows
     of the weight matrix dealt out evenly, a ring of TMA boxes fed by a load warp."""
@@ -61,7 +141,10 @@ def _stream_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) ->
 def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
     """silu(x gate^T) * (x up^T) for ``w_gate_up`` = [gate rows; up rows] in one streaming kernel, where that kernel
     serves the gate/up product anyway (bfloat16, at most 8 rows); None otherwise: the caller then takes the product
-    and the activation kernel."""
+    and the activation kernel. ``x`` may be ScaledRows."""
+    if isinstance(x, ScaledRows):
+        # None leaves the rows as they are: the caller's linear() takes them
+        return _scaled_stream(x, w_gate_up, glu=True) if x.shape[1] >= FUSED_SWIGLU_MIN_K else None
     M, K = x.shape
     if not STREAM_GEMM or x.dtype != torch.bfloat16 or not 0 < M <= 8 or x.stride(1) != 1 or w_gate_up.stride(1) != 1:
         return None
@@ -153,7 +236,13 @@ register_bf16_kernel(_tensor_memory_prefill)
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type)."""
+    """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type). ``x`` may be ScaledRows."""
+    if isinstance(x, ScaledRows):
+        if bias is None and out_dtype in (None, x.dtype):
+            out = _scaled_stream(x, weight, glu=False)
+            if out is not None:
+                return out
+        x = x.value()
     if not x.is_cuda:
         raise kernels.KernelError("linear() was given a CPU tensor; this engine has no CPU path")
     out_dtype = out_dtype or x.dtype

@@ -21,7 +21,7 @@ import torch
 
 from ..cache.spec import KVPagesSpec
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import PendingProduct, linear, pending_product
 from ..weights.source import ParamSpec
 from .base import LayerCache, Mixer, TensorGetter
 from .registry import register_mixer
@@ -88,7 +88,13 @@ class PagedAttention(Mixer):
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
     # -- one step --------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx, cache: LayerCache):
+    takes_scaled_rows = True             # x goes straight into linear()
+
+    def forward(self, x, ctx, cache: LayerCache):
+        out, bias = self.forward_deferred(x, ctx, cache)
+        return (out.value() if isinstance(out, PendingProduct) else out), bias
+
+    def forward_deferred(self, x, ctx, cache: LayerCache):
         if cache.pages is None or cache.group is None:
             raise RuntimeError("the attention mixer needs the pages of its cache")
         page_size = cache.pages.shape[3]
@@ -109,4 +115,4 @@ class PagedAttention(Mixer):
                          pages=cache.pages if writes else None, page_size=page_size)
         out = torch.empty((ctx.num_tokens, self.q_size), dtype=x.dtype, device=x.device)
         ctx.attention(self, qkv, out, cache)
-        return linear(out, self.w_o), self.b_o
+        return pending_product(out, self.w_o), self.b_o

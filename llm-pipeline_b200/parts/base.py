@@ -13,6 +13,12 @@ works on the tensors of one step. No part knows which model it is in.
   ``state_spec()`` tell the cache manager what it needs.
 * ``FeedForward.forward(x, ctx) -> (out, bias)``: works on each token alone.
 * ``Block.forward(stream, ctx, cache)``: the arrangement of the above around the residual stream.
+
+Optional, for the few rows of a decode step (``ops/linear.py``: a norm between two streaming products folded into
+them): a mixer or feed-forward with ``forward_deferred(...)`` may return its last product as a ``PendingProduct``; a
+norm with ``add_norm_deferred(stream, ctx)`` may take such a product from the stream and return ``ScaledRows``; a part
+that sets ``takes_scaled_rows`` accepts those as its ``x`` (``linear()`` does). A block uses these only where both
+sides offer them; parts without them see tensors only.
 """
 
 from __future__ import annotations
@@ -23,6 +29,7 @@ from typing import Callable, Dict, Optional, Tuple
 import torch
 
 from ..cache.spec import KVPagesSpec, StateSpec
+from ..ops.linear import PendingProduct
 from ..weights.source import ParamSpec
 
 TensorGetter = Callable[[str, str], torch.Tensor]   # (full tensor name, role) -> tensor on the device
@@ -46,13 +53,34 @@ class ResidualStream:
 
     def __init__(self, residual: torch.Tensor):
         self.residual = residual
-        self.pending: Optional[torch.Tensor] = None
+        self._pending = None
         self.pending_bias: Optional[torch.Tensor] = None
 
-    def add(self, delta: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
-        if self.pending is not None:
+    def add(self, delta, bias: Optional[torch.Tensor] = None) -> None:
+        """``delta``: a tensor, or a product not yet taken (``ops.linear.PendingProduct``) that the next norm may
+        fold into its own work."""
+        if self._pending is not None:
             raise RuntimeError("the residual stream already holds a pending addend")
-        self.pending, self.pending_bias = delta, bias
+        self._pending, self.pending_bias = delta, bias
+
+    @property
+    def pending(self) -> Optional[torch.Tensor]:
+        """The pending addend as a tensor (a product not yet taken is taken now)."""
+        if isinstance(self._pending, PendingProduct):
+            self._pending = self._pending.value()
+        return self._pending
+
+    @pending.setter
+    def pending(self, delta) -> None:
+        self._pending = delta
+
+    def take_pending_product(self) -> Optional[PendingProduct]:
+        """The pending addend if it is a product not yet taken and without bias, which is then the caller's to add;
+        else None, and nothing changes."""
+        if isinstance(self._pending, PendingProduct) and self.pending_bias is None:
+            product, self._pending = self._pending, None
+            return product
+        return None
 
 
 class Part:

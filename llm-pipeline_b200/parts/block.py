@@ -14,9 +14,18 @@ from .registry import register_block
 @register_block("pre_norm_residual")
 class PreNormResidualBlock(Block):
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
-        h = self.mixer_norm.add_norm(stream, ctx)
-        out, bias = self.mixer.forward(h, ctx, cache)
+        h = self._norm(self.mixer_norm, self.mixer, stream, ctx)
+        out, bias = getattr(self.mixer, "forward_deferred", self.mixer.forward)(h, ctx, cache)
         stream.add(out, bias)
-        h = self.feed_forward_norm.add_norm(stream, ctx)
-        out, bias = self.feed_forward.forward(h, ctx)
+        h = self._norm(self.feed_forward_norm, self.feed_forward, stream, ctx)
+        out, bias = getattr(self.feed_forward, "forward_deferred", self.feed_forward.forward)(h, ctx)
         stream.add(out, bias)
+
+    @staticmethod
+    def _norm(norm, consumer, stream: ResidualStream, ctx):
+        """The norm's rows for ``consumer``: with their factors still to be applied where the norm can leave them so
+        and the consumer takes them so."""
+        deferred = getattr(norm, "add_norm_deferred", None)
+        if deferred is not None and getattr(consumer, "takes_scaled_rows", False):
+            return deferred(stream, ctx)
+        return norm.add_norm(stream, ctx)

@@ -9,7 +9,7 @@ from typing import Dict
 import torch
 
 from ..ops import kernels
-from ..ops.linear import gate_up_swiglu, linear
+from ..ops.linear import PendingProduct, gate_up_swiglu, linear, pending_product
 from ..weights.source import ParamSpec
 from .base import FeedForward, TensorGetter
 from .registry import register_feed_forward
@@ -34,10 +34,16 @@ class SwiGLU(FeedForward):
                                    dim=0).contiguous()
         self.w_down = get(f"{p}.down_proj.weight", "matrix").contiguous()
 
-    def forward(self, x: torch.Tensor, ctx):
+    takes_scaled_rows = True             # x goes straight into gate_up_swiglu() or linear()
+
+    def forward(self, x, ctx):
+        out, bias = self.forward_deferred(x, ctx)
+        return (out.value() if isinstance(out, PendingProduct) else out), bias
+
+    def forward_deferred(self, x, ctx):
         act = gate_up_swiglu(x, self.w_gate_up)          # the few rows of a decode step: product and activation in one kernel
         if act is None:
             gate_up = linear(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
             kernels.swiglu(gate_up, act)
-        return linear(act, self.w_down), None
+        return pending_product(act, self.w_down), None

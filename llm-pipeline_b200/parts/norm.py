@@ -12,6 +12,7 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import kernels
+from ..ops.linear import residual_product
 from ..weights.source import ParamSpec
 from .base import Norm, ResidualStream, TensorGetter
 from .registry import register_norm
@@ -39,3 +40,18 @@ class RMSNorm(Norm):
         if rows is None:
             stream.pending, stream.pending_bias = None, None
         return out
+
+    def add_norm_deferred(self, stream: ResidualStream, ctx):
+        """As ``add_norm`` for all rows, but a pending product of a decode step's few rows is added into the residual by
+        its own kernel, which leaves the rows normalised but for their factors (``ScaledRows``) to the product after."""
+        product = stream.take_pending_product()
+        if product is None:
+            return self.add_norm(stream, ctx)
+        residual = stream.residual
+
+        def finished() -> torch.Tensor:
+            # for a consumer that cannot apply the factors: the norm of the residual as it now is
+            out = torch.empty((residual.shape[0], self.size), dtype=ctx.dtype, device=residual.device)
+            return kernels.add_rmsnorm(residual, None, self.weight, self.eps, out)
+
+        return residual_product(product, residual, self.weight, self.eps, finished)

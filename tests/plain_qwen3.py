@@ -328,3 +328,13 @@ TINY_D = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "attention_bias": False,
     "max_position_embeddings": 2048, "hidden_act": "silu",
 }
+
+# widths in multiples of 64, which the streaming products of a decode step take: the norm between two of them is then
+# folded into them
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 128, "num_attention_heads": 2, "num_key_value_heads": 1,
+    "head_dim": 64, "intermediate_size": 192, "vocab_size": 211, "rope_theta": 500000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "attention_bias": False,
+    "max_position_embeddings": 1024, "hidden_act": "silu",
+}

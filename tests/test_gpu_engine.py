@@ -14,6 +14,7 @@ CASES = [
     pytest.param(plain.TINY_B, 1, 8, (1, 9, 24, 40), id="tiny_b"),
     pytest.param(plain.TINY_C, 2, 16, (3, 50, 21), id="tiny_c"),
     pytest.param(plain.TINY_D, 3, 16, (133, 9, 262), id="tiny_d"),       # crosses the 128-key tiles of attention
+    pytest.param(plain.TINY_E, 4, 8, (7, 30, 61), id="tiny_e"),          # decode steps fold the norms into the products
 ]
 DTYPES = [pytest.param(torch.float32, id="f32"), pytest.param(torch.bfloat16, id="bf16")]
 

@@ -514,3 +514,53 @@ def test_kernels_refuse_what_they_cannot_do():
         run_paged(torch.float32, 2, 1, 24, 8, [(0, 2)])
     with pytest.raises(k_.KernelError, match="float32 and bfloat16"):
         k_.swiglu(torch.zeros(2, 4, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV))
+
+
+@pytest.mark.parametrize("M,N,Kd,H", [(8, 4096, 4096, 4096), (1, 1024, 3072, 1024), (5, 5120, 256, 5120), (3, 192, 320, 192)])
+def test_gemm_stream_between_norms(M, N, Kd, H):
+    """The streaming product with the residual add and the RMSNorm around it folded in: as producer it adds into the
+    float32 residual and leaves residual * norm weight and its blocks' sums of squares; as consumer it multiplies its
+    result by the rows' factors. Together they give what the norm kernel between two plain products gives."""
+    k_ = K()
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=70), rnd(N, Kd, dtype=torch.bfloat16, seed=71, scale=0.05)
+    residual = rnd(M, N, seed=72, scale=3.0)
+    for norm_dtype in (torch.float32, torch.bfloat16):
+        norm_w = (1 + 0.2 * rnd(N, seed=73)).to(norm_dtype)
+        blocks = k_.gemm_stream_blocks(M, N, Kd, Kd, Kd)
+        assert blocks > 0
+        res = residual.clone()
+        xw = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        sumsq = torch.full((blocks + 2, 8), 7.0, device=DEV)
+        k_.gemm_stream_fused(x, w, None, residual=res, norm_weight=norm_w, xw=xw, out_sumsq=sumsq)
+        want_res = residual.double() + x.double() @ w.double().t()
+        assert torch.allclose(res.double(), want_res, atol=2e-3, rtol=1e-5)
+        assert torch.equal(xw, (res * norm_w.float()).to(torch.bfloat16))
+        assert torch.allclose(sumsq[:blocks, :M].sum(0).double(), (res.double() ** 2).sum(1), rtol=1e-5)
+        assert float(sumsq[:blocks, M:].abs().max()) == 0.0 if M < 8 else True
+        assert float(sumsq[blocks:].min()) == 7.0                    # rows beyond the blocks are not touched
+        # the same launch again gives the same bits (sums in a fixed order)
+        res2, xw2, sumsq2 = residual.clone(), torch.zeros_like(xw), torch.zeros_like(sumsq)
+        k_.gemm_stream_fused(x, w, None, residual=res2, norm_weight=norm_w, xw=xw2, out_sumsq=sumsq2)
+        assert torch.equal(res2, res) and torch.equal(sumsq2[:blocks], sumsq[:blocks])
+    # consumer: a product of the rows that lack their factors, against the norm kernel and a plain product
+    eps = 1e-6
+    norm_w = (1 + 0.2 * rnd(N, seed=73))
+    res = residual.clone()
+    xw = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    blocks = k_.gemm_stream_blocks(M, N, Kd, Kd, Kd)
+    sumsq = torch.empty(blocks, 8, device=DEV)
+    k_.gemm_stream_fused(x, w, None, residual=res, norm_weight=norm_w, xw=xw, out_sumsq=sumsq)
+    w2 = rnd(2 * 96, H, dtype=torch.bfloat16, seed=74, scale=0.05)
+    assert N == H
+    normed = plain.rms_norm(want_res.float(), norm_w, eps)
+    want = normed.double() @ w2.double().t()
+    out = torch.empty(M, w2.shape[0], dtype=torch.bfloat16, device=DEV)
+    k_.gemm_stream_fused(xw, w2, out, in_sumsq=sumsq, in_parts=blocks, in_width=H, in_eps=eps)
+    scale = float(want.abs().max())
+    assert float((out.double() - want).abs().max()) <= 2e-2 * max(1.0, scale)
+    # and with SwiGLU
+    act = torch.empty(M, 96, dtype=torch.bfloat16, device=DEV)
+    k_.gemm_stream_fused(xw, w2, act, glu=True, in_sumsq=sumsq, in_parts=blocks, in_width=H, in_eps=eps)
+    want_act = torch.nn.functional.silu(want[:, :96]) * want[:, 96:]
+    assert float((act.double() - want_act).abs().max()) <= 3e-2 * max(1.0, float(want_act.abs().max()))
+    k_.check_error_flag()
