@@ -203,7 +203,26 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int steps16 = 4 * p.KB;                            // 16-element K steps per stage
         const int mine = (p.stages - warp + GS_CWARPS - 1) / GS_CWARPS;      // ring slots of this warp: warp, warp + 4, ...
         int j = 0;                                               // stages this warp has taken
+        if (p.residual != nullptr && p.in_sumsq == nullptr) pdl_wait();      // the residual is read below
         for (int chunk = 0; chunk < chunks; ++chunk) {
+            // residual: this thread's entries of the residual and of the norm weight for the chunk's columns, asked for
+            // now so that they are there when the sums are (thread part16 of row row16: columns part16, part16 + 16, ...)
+            float r_before[GS_MAX_RB / 16], w_norm[GS_MAX_RB / 16];
+            if (p.residual != nullptr) {
+                const int n0 = row_begin + chunk * p.RB;
+                int rows = row_end - n0;
+                if (rows > p.RB) rows = p.RB;
+#pragma unroll
+                for (int i = 0; i < GS_MAX_RB / 16; ++i) {
+                    const int c = part16 + 16 * i;
+                    r_before[i] = w_norm[i] = 0.f;
+                    if (row16 < p.M && c < rows) {
+                        r_before[i] = p.residual[(size_t)row16 * p.ldr + n0 + c];
+                        w_norm[i] = p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n0 + c]
+                                                 : __bfloat162float(reinterpret_cast<const bf16*>(p.norm_w)[n0 + c]);
+                    }
+                }
+            }
             // warp w takes the chunk's stages w, w + 4, ... whole: a wait and a hand-back per stage and warp
             for (int ks = warp; ks < ksteps; ks += GS_CWARPS, ++j) {
                 const int slot = GS_CWARPS * (j % mine) + warp;  // this warp's j-th stage: see the load warp
@@ -258,18 +277,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 // Thread part16 of row row16 takes the columns part16, part16 + 16, ... of its row: r = residual + product,
                 // r * norm weight for the next product, and r^2 added in a fixed order (its columns in turn, then a tree).
                 float sum = 0.f;
-                if (row16 < p.M) {
-                    for (int c = part16; c < rows; c += 16) {
+#pragma unroll
+                for (int i = 0; i < GS_MAX_RB / 16; ++i) {
+                    const int c = part16 + 16 * i;
+                    if (row16 < p.M && c < rows) {
                         float v = 0.f;
 #pragma unroll
                         for (int w = 0; w < GS_CWARPS; ++w) v += part[((size_t)w * p.part_rows + c) * pstride + row16];
                         if (p.in_sumsq != nullptr) v *= row_factor[row16];
-                        const int n = n0 + c;
-                        const float r = p.residual[(size_t)row16 * p.ldr + n] + v;
-                        p.residual[(size_t)row16 * p.ldr + n] = r;
-                        const float wn = p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n]
-                                                      : __bfloat162float(reinterpret_cast<const bf16*>(p.norm_w)[n]);
-                        p.xw[(size_t)row16 * p.ldxw + n] = __float2bfloat16_rn(r * wn);
+                        const float r = r_before[i] + v;
+                        p.residual[(size_t)row16 * p.ldr + n0 + c] = r;
+                        p.xw[(size_t)row16 * p.ldxw + n0 + c] = __float2bfloat16_rn(r * w_norm[i]);
                         sum = fmaf(r, r, sum);
                     }
                 }
