@@ -89,6 +89,7 @@ class CacheGroup:
 class _Request:
     slot: int
     length: int = 0
+    admission: int = 0       # counts admissions of the manager: tells a request from an earlier one of the same name
 
 
 class CacheManager:
@@ -135,6 +136,7 @@ class CacheManager:
                                                     device=device)
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
+        self._admissions = 0
         self.pages_reused = 0
         self._ever_used = [set() for _ in self.groups]
 
@@ -157,7 +159,8 @@ class CacheManager:
         if not self._free_slots:
             raise CacheError(f"all {self.max_requests} request slots are in use")
         slot = self._free_slots.pop()
-        self._requests[req_id] = _Request(slot)
+        self._admissions += 1
+        self._requests[req_id] = _Request(slot, admission=self._admissions)
         for group in self.groups:
             group.tables[req_id] = []
         for tensor in self.states.values():
@@ -166,6 +169,11 @@ class CacheManager:
 
     def slot_of(self, req_id: Hashable) -> int:
         return self._requests[req_id].slot
+
+    def admission(self, req_id: Hashable) -> int:
+        """A number that no other admission of this manager has: a request that ended (or was preempted) and came
+        back under the same name has another one, and block tables remembered for the old one are void."""
+        return self._requests[req_id].admission
 
     def length(self, req_id: Hashable) -> int:
         """Tokens of the request whose keys/values (or state) the cache holds."""

@@ -60,7 +60,7 @@ class _DecodeGraph:
         self.copied = None
         self.launches = 0
         self.host_np = None          # the pinned buffer as a numpy array (same memory)
-        self.req_ids = None          # the requests of the last step, in row order
+        self.req_ids = None          # the requests of the last step in row order, each with its admission number
         self.table_lens = None       # per cache group and row: pages of the block table already in the buffer
 
 
@@ -276,7 +276,7 @@ class ModelRunner:
             slot.graph = graph
         else:
             slot.copied.synchronize()            # the previous copy out of the pinned buffer is done
-            if slot.req_ids == [e.req_id for e in entries]:
+            if slot.req_ids == [(e.req_id, cache.admission(e.req_id)) for e in entries]:
                 self._refill(slot, entries, width)
             else:
                 flat = self._fill(slot.ctx, entries, width)
@@ -291,7 +291,7 @@ class ModelRunner:
         return self._finish(slot.ctx, entries, slot.logits)
 
     def _remember(self, slot: _DecodeGraph, entries: Sequence[StepEntry]) -> None:
-        slot.req_ids = [e.req_id for e in entries]
+        slot.req_ids = [(e.req_id, self.cache.admission(e.req_id)) for e in entries]
         slot.table_lens = [[len(self.cache.block_table(e.req_id, g)) for e in entries] for g in range(len(self.cache.groups))]
 
     def _refill(self, slot: _DecodeGraph, entries: Sequence[StepEntry], width: int) -> None:

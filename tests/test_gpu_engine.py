@@ -131,3 +131,27 @@ def test_which_decode_kernel_a_step_takes():
 
     assert not takes_list([2048]) and not takes_list([2048] * 8) and not takes_list([16384] * 8) and not takes_list([2048] * 32)
     assert takes_list([131072]) and takes_list([32768, 600]) and takes_list([16384] + [512] * 7) and takes_list([2048] * 64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_request_name_that_comes_back_gets_its_own_block_table(tmp_path, dtype):
+    """A request ends and a new one arrives under the same name, on other pages: replayed decode graphs keep the
+    rows of their last step's requests and rewrite only what moved, so they must tell the two apart."""
+    config = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, config, 11, dtype)
+    first = {"a": H.random_tokens(config["vocab_size"], 40, 1)}
+    second = {"a": H.random_tokens(config["vocab_size"], 40, 2), "b": H.random_tokens(config["vocab_size"], 30, 3)}
+    runner = H.make_runner(folder, dtype, page_size=8, num_pages=32)
+    H.assert_close(H.replay(runner, H.cut_portions(first, (1,))), H.expected_logits(config, weights, first), H.TOL[dtype], "first")
+    steps = [([("b", second["b"][:29], [28])], [])]                   # b takes the pages that a had
+    # a again: most of it as one portion, so that its first single-token step finds the graph of the first a's last
+    # steps, with a block table as long as the one remembered there
+    steps.append(([("a", second["a"][:33], [32])], []))
+    for i in range(33, 40):
+        steps.append(([("a", [second["a"][i]], [0])], ["a"] if i == 39 else []))
+    steps.append(([("b", second["b"][29:], [0])], ["b"]))
+    want = H.expected_logits(config, weights, second)
+    got = H.replay(runner, steps)
+    assert torch.allclose(got["a"], want["a"][32:], atol=H.TOL[dtype]), float((got["a"] - want["a"][32:]).abs().max())
+    assert torch.allclose(got["b"], want["b"][28:], atol=H.TOL[dtype])
+    assert runner.graph_replays > 0 and runner.cache.num_live == 0

@@ -52,3 +52,37 @@ def test_random_configuration_mixed_trace(tmp_path, seed, dtype):
     got = H.replay(runner, H.cut_mixed(requests, sizes, max_live=4))
     H.assert_close(got, want, H.TOL[dtype], f"random configuration {seed} ({config})")
     assert runner.cache.num_live == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configuration_with_widths_in_multiples_of_64(tmp_path, seed):
+    """Widths that the streaming products of a decode step take, so that steps of up to 8 tokens fold their norms into
+    the products around them (and steps of more tokens do not): token by token, in small portions and mixed."""
+    dtype = torch.bfloat16
+    rng = random.Random(500 + seed)
+    config = dict(random_config(seed), hidden_size=rng.choice([64, 128, 192, 320]), intermediate_size=rng.choice([64, 192, 448]),
+                  head_dim=rng.choice([64, 128]))
+    page = rng.choice([8, 16, 32])
+    folder, weights = H.make_case(tmp_path, config, seed, dtype)
+    lengths = [rng.choice([1, 2, 9, 17, 40, 130]) for _ in range(5)] + [rng.randrange(120, 260)]
+    requests = {f"r{i}": H.random_tokens(config["vocab_size"], n + 7, 3000 + 10 * seed + i) for i, n in enumerate(lengths)}
+    want = H.expected_logits(config, weights, requests)
+    longest = max(len(t) for t in requests.values())
+    runner = H.make_runner(folder, dtype, page_size=page, num_pages=4 * (-(-longest // page)))
+    from llm_pipeline_b200.ops import kernels
+    folded, launch = [], kernels.gemm_stream_fused
+
+    def counting(*args, **kwargs):
+        folded.append(1)
+        return launch(*args, **kwargs)
+
+    kernels.gemm_stream_fused = counting
+    try:
+        H.assert_close(H.replay(runner, H.cut_portions(requests, (1,))), want, H.TOL[dtype], f"token by token ({config})")
+        H.assert_close(H.replay(runner, H.cut_portions(requests, (3, 8, 2, 9))), want, H.TOL[dtype], f"portions ({config})")
+        H.assert_close(H.replay(runner, H.cut_mixed(requests, (2, 3, 5, 16), max_live=4)), want, H.TOL[dtype], f"mixed ({config})")
+    finally:
+        kernels.gemm_stream_fused = launch
+    # a product with a bias is not handed to the norm, and the last layer's goes to the final norm as a tensor
+    assert folded or (config["attention_bias"] and config["num_hidden_layers"] == 1)
+    assert runner.cache.num_live == 0
