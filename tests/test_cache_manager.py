@@ -138,3 +138,18 @@ def test_random_orders_keep_the_books(seed):
     m.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.groups)
     assert m.free_slots == 5
+
+
+def test_admissions_are_numbered():
+    """A request that ends and comes back under the same name is another admission: who remembers block tables by
+    name can tell the two apart."""
+    m = manager()
+    m.admit("a")
+    m.admit("b")
+    first_a, first_b = m.admission("a"), m.admission("b")
+    assert first_a != first_b
+    m.free("a")
+    m.admit("a")
+    assert m.admission("a") not in (first_a, first_b) and m.admission("b") == first_b
+    with pytest.raises(KeyError):
+        m.admission("c")
