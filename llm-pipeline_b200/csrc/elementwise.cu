@@ -94,8 +94,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
-// The same operation for rows of at most 4096 entries whose width is a multiple of 4: one 4-entry
-// piece per thread, held in registers from the first load to the store, so the row makes one trip.
+// The same operation for rows of at most 16384 entries whose width is a multiple of 4: one, two or four 4-entry
+// pieces per thread, held in registers from the first load to the store, so the row makes one trip.
 template <typename T> struct Vec4;
 template <> struct Vec4<float> {
     static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
@@ -122,7 +122,8 @@ template <> struct Vec4<bf16> {
     }
 };
 
-template <typename T>
+// PIECES 4-entry pieces per thread (piece p of thread t at column 4 (t + p * blockDim)): rows of at most 4096 PIECES entries.
+template <typename T, int PIECES>
 __global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                         const void* __restrict__ delta_bias, int bias_bf16,
                                         const void* __restrict__ weight, int weight_bf16, float eps,
@@ -130,37 +131,61 @@ __global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* _
     __shared__ float scratch[32];
     const int m = blockIdx.x;
     const int r = rows ? rows[m] : m;
-    const int c = threadIdx.x * 4;
-    const bool active = c < H;
-    float x[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
-    if (active) {
+    float x[PIECES][4], w[PIECES][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = load_as_float(weight, weight_bf16, c + i);
+    for (int p = 0; p < PIECES; ++p) {
+        const int c = (threadIdx.x + p * blockDim.x) * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[p][i] = 0.f;
+            w[p][i] = c < H ? load_as_float(weight, weight_bf16, c + i) : 0.f;
+        }
     }
     pdl_wait();                                    // the addend (and the residual of the kernel before) is complete
     pdl_trigger();
-    if (active) {
-        Vec4<float>::load(residual + (size_t)r * H + c, x);
-        if (delta) {
-            float dl[4];
-            Vec4<T>::load(delta + (size_t)r * H + c, dl);
+    float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] += dl[i];
-        }
-        if (delta_bias) {
+    for (int p = 0; p < PIECES; ++p) {
+        const int c = (threadIdx.x + p * blockDim.x) * 4;
+        if (c < H) {
+            Vec4<float>::load(residual + (size_t)r * H + c, x[p]);
+            if (delta) {
+                float dl[4];
+                Vec4<T>::load(delta + (size_t)r * H + c, dl);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] += load_as_float(delta_bias, bias_bf16, c + i);
+                for (int i = 0; i < 4; ++i) x[p][i] += dl[i];
+            }
+            if (delta_bias) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) x[p][i] += load_as_float(delta_bias, bias_bf16, c + i);
+            }
         }
+        ss += x[p][0] * x[p][0] + x[p][1] * x[p][1] + x[p][2] * x[p][2] + x[p][3] * x[p][3];
     }
-    const float ss = block_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3], scratch);
+    ss = block_sum(ss, scratch);
     const float rstd = rsqrtf(ss / (float)H + eps);
-    if (active) {
-        if (rows == nullptr && (delta != nullptr || delta_bias != nullptr)) Vec4<float>::store(residual + (size_t)r * H + c, x);
-        float y[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) y[i] = w[i] * (x[i] * rstd);
-        Vec4<T>::store(out + (size_t)m * H + c, y);
+    for (int p = 0; p < PIECES; ++p) {
+        const int c = (threadIdx.x + p * blockDim.x) * 4;
+        if (c < H) {
+            if (rows == nullptr && (delta != nullptr || delta_bias != nullptr)) Vec4<float>::store(residual + (size_t)r * H + c, x[p]);
+            float y[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[i] = w[p][i] * (x[p][i] * rstd);
+            Vec4<T>::store(out + (size_t)m * H + c, y);
+        }
     }
+}
+
+template <typename T, int PIECES>
+static cudaError_t launch_add_rmsnorm_row4(float* residual, const void* delta, const void* delta_bias, int bias_dtype,
+                                           const void* weight, int weight_dtype, float eps, void* out, const int* rows, int M,
+                                           int H, cudaStream_t stream) {
+    const int per_thread = 4 * PIECES;
+    const int threads = (((H + per_thread - 1) / per_thread + 31) / 32) * 32;
+    return llmp_launch_dependent(add_rmsnorm_row4_kernel<T, PIECES>, dim3(M), dim3(threads), 0, stream, residual, (const T*)delta,
+                                 delta_bias, (int)(bias_dtype == LLMP_BF16), weight, (int)(weight_dtype == LLMP_BF16), eps, (T*)out,
+                                 rows, H);
 }
 
 LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* delta_bias, int bias_dtype,
@@ -168,17 +193,15 @@ LLMP_API int llmp_add_rmsnorm(float* residual, const void* delta, const void* de
                               const int* rows, int M, int H, cudaStream_t stream) {
     if (M <= 0) return 0;
     LLMP_REQUIRE(H > 0, "add_rmsnorm: bad width %d", H);
-    if (H % 4 == 0 && H <= 4096) {
-        const int threads = ((H / 4 + 31) / 32) * 32;
+    if (H % 4 == 0 && H <= 16384) {
+        // the register-resident kernel: one, two or four 4-entry pieces per thread
         cudaError_t launched;
-        if (dtype == LLMP_F32)
-            launched = llmp_launch_dependent(add_rmsnorm_row4_kernel<float>, dim3(M), dim3(threads), 0, stream, residual, (const float*)delta, delta_bias,
-                                                                      bias_dtype == LLMP_BF16, weight,
-                                                                      weight_dtype == LLMP_BF16, eps, (float*)out, rows, H);
-        else
-            launched = llmp_launch_dependent(add_rmsnorm_row4_kernel<bf16>, dim3(M), dim3(threads), 0, stream, residual, (const bf16*)delta, delta_bias,
-                                                                     bias_dtype == LLMP_BF16, weight,
-                                                                     weight_dtype == LLMP_BF16, eps, (bf16*)out, rows, H);
+#define NORM_LAUNCH(T)                                                                                                          \
+    (H <= 4096 ? launch_add_rmsnorm_row4<T, 1>(residual, delta, delta_bias, bias_dtype, weight, weight_dtype, eps, out, rows, M, H, stream) \
+     : H <= 8192 ? launch_add_rmsnorm_row4<T, 2>(residual, delta, delta_bias, bias_dtype, weight, weight_dtype, eps, out, rows, M, H, stream) \
+                 : launch_add_rmsnorm_row4<T, 4>(residual, delta, delta_bias, bias_dtype, weight, weight_dtype, eps, out, rows, M, H, stream))
+        launched = dtype == LLMP_F32 ? NORM_LAUNCH(float) : NORM_LAUNCH(bf16);
+#undef NORM_LAUNCH
         if (launched != cudaSuccess) {
             llmp_set_error("add_rmsnorm: launch failed: %s", cudaGetErrorString(launched));
             return 2;

@@ -51,7 +51,7 @@ def test_rope_tables_match_the_reference_formula():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H", [1000, 4096 + 16])
+@pytest.mark.parametrize("H", [1000, 4096 + 16, 5120, 8200, 1002, 16400])
 def test_add_rmsnorm(dtype, H):
     residual = rnd(7, H, seed=1)
     delta = rnd(7, H, dtype=dtype, seed=2)
