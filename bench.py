@@ -45,7 +45,7 @@ QWEN3_32B = {**QWEN3_8B, "num_hidden_layers": 64, "hidden_size": 5120, "num_atte
 SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 32
+PAGE_SIZE = 16           # tokens per page of the key/value cache (--page-size)
 
 
 def peaks():
@@ -438,7 +438,9 @@ def main() -> int:
                         "(a batch of uneven lengths), instead of --batch requests of 2,048 tokens")
     parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
                         help="run one part only (for profiler captures on a small case); the line then lacks the other parts")
+    parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
     args = parser.parse_args()
+    globals()["PAGE_SIZE"] = args.page_size
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print("bench.py measures a single-GPU engine: run it with --gpus 1 (no multi-GPU path is built)")

@@ -9,8 +9,8 @@ write; they grow with the request; and the manager never evicts: ``reserve`` rep
 the scheduler decides.
 
 Layers with the same need form a *group* with pages of its own: one page id addresses the same
-page in every cache of the group (tensor ``[num_pages, 2, kv_heads, page_size, head_dim]`` per
-cache). A group whose layers see only a window of keys gives pages back as soon as every token
+page in every cache of the group (a tensor ``[num_pages, *spec.page_shape(page_size)]`` per cache:
+``[num_pages, 2, kv_heads, page_size, head_dim]`` for keys and values). A group whose layers see only a window of keys gives pages back as soon as every token
 in them has left the window; its block table then holds -1 there. Beside the pages, every live
 request owns a *slot*: an index into per-cache state tensors of fixed size per request, zeroed
 when the slot is handed out.
@@ -23,7 +23,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .spec import KVPagesSpec, StateSpec
+from .spec import PagesSpec, StateSpec
 
 
 class CacheError(RuntimeError):
@@ -78,7 +78,7 @@ class PagePool:
 
 @dataclass
 class CacheGroup:
-    spec: KVPagesSpec
+    spec: PagesSpec
     cache_ids: List[int]
     pool: PagePool
     tables: Dict[Hashable, List[int]] = field(default_factory=dict)
@@ -93,12 +93,12 @@ class _Request:
 
 
 class CacheManager:
-    """``cache_specs[i]`` is what cache id ``i`` needs: ``(KVPagesSpec | None, StateSpec | None)``.
+    """``cache_specs[i]`` is what cache id ``i`` needs: ``(PagesSpec | None, StateSpec | None)``.
     ``num_pages`` is the page count of every group, or a list with one count per group (groups
     are numbered in order of first appearance). With ``device=None`` no tensor is allocated and
     the manager only keeps books (used by the scheduler's tests)."""
 
-    def __init__(self, cache_specs: Sequence[Tuple[Optional[KVPagesSpec], Optional[StateSpec]]], page_size: int,
+    def __init__(self, cache_specs: Sequence[Tuple[Optional[PagesSpec], Optional[StateSpec]]], page_size: int,
                  num_pages: Union[int, Sequence[int]], max_requests: int, max_request_tokens: int,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16):
         if page_size <= 0:
@@ -127,10 +127,9 @@ class CacheManager:
         self.states: Dict[int, torch.Tensor] = {}
         if device is not None:
             for group in self.groups:
-                s = group.spec
+                shape = (group.pool.num_pages,) + tuple(group.spec.page_shape(self.page_size))
                 for cache_id in group.cache_ids:
-                    group.tensors[cache_id] = torch.zeros(
-                        (group.pool.num_pages, 2, s.num_kv_heads, self.page_size, s.head_dim), dtype=dtype, device=device)
+                    group.tensors[cache_id] = torch.zeros(shape, dtype=group.spec.dtype or dtype, device=device)
             for cache_id, spec in self.state_specs.items():
                 self.states[cache_id] = torch.zeros((self.max_requests,) + tuple(spec.shape), dtype=spec.dtype,
                                                     device=device)
@@ -273,6 +272,22 @@ class CacheManager:
         """Physical token slot (page * page_size + offset) of a position, or -1 without a page."""
         page = self.groups[group].tables[req_id][position // self.page_size]
         return -1 if page < 0 else page * self.page_size + position % self.page_size
+
+    @staticmethod
+    def bytes_per_page(cache_specs, page_size: int, dtype: torch.dtype) -> List[int]:
+        """Per group (in the order the manager numbers them), the bytes one page id costs over all caches of the
+        group: what a memory budget divides by."""
+        keys: Dict[tuple, int] = {}
+        out: List[int] = []
+        for pages, _state in cache_specs:
+            if pages is None:
+                continue
+            key = pages.group_key()
+            if key not in keys:
+                keys[key] = len(out)
+                out.append(0)
+            out[keys[key]] += pages.bytes_per_token(dtype) * page_size
+        return out
 
     # -- bookkeeping -----------------------------------------------------------------------
     def stats(self) -> Dict[str, object]:

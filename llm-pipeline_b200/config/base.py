@@ -25,13 +25,30 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: an arrangement (``block``) of a mixer, a feed-forward and their norms.
-    Different layers of one model may name different kinds."""
+    Different layers of one model may name different kinds. A block finds its norms by name:
+    ``mixer_norm`` and ``feed_forward_norm`` are the two of a pre-norm block (names "mixer" and
+    "feed_forward"); ``norms`` holds any further ones a block kind asks for (post-norms, a norm
+    of a parallel branch, ...), so a block with four norms or with none is a matter of
+    configuration."""
 
     block: str
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
+    norms: Dict[str, PartSpec] = field(default_factory=dict)
+
+    def named_norms(self) -> Dict[str, PartSpec]:
+        out: Dict[str, PartSpec] = {}
+        if self.mixer_norm is not None:
+            out["mixer"] = self.mixer_norm
+        if self.feed_forward_norm is not None:
+            out["feed_forward"] = self.feed_forward_norm
+        for name, spec in self.norms.items():
+            if name in out:
+                raise ValueError(f"the layer names its norm {name!r} twice")
+            out[name] = spec
+        return out
 
 
 @dataclass(frozen=True)

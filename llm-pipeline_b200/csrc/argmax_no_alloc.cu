@@ -41,14 +41,15 @@ __global__ void __launch_bounds__(256) na_partial_kernel(const float* __restrict
                                                          float* __restrict__ scratch) {
     __shared__ NaBest per_warp[8];
     const int m = blockIdx.y, slice = blockIdx.x;
-    const int per = (V + NA_SLICES - 1) / NA_SLICES;
-    const int begin = slice * per;
-    const int end = begin + per < V ? begin + per : V;
+    // in long: near V = 2^31 the last slices' bounds and the loop's increment would wrap an int
+    const long per = ((long)V + NA_SLICES - 1) / NA_SLICES;
+    const long begin = slice * per;
+    const long end = begin + per < V ? begin + per : V;
     const float* row = logits + (size_t)m * stride;
     NaBest best = {-INFINITY, -1};
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    for (long i = begin + threadIdx.x; i < end; i += blockDim.x) {
         const float v = row[i];
-        if (!(v != v)) best = na_better(best, NaBest{v, i});
+        if (!(v != v)) best = na_better(best, NaBest{v, (int)i});
     }
     best = na_warp_best(best);
     if ((threadIdx.x & 31) == 0) per_warp[threadIdx.x >> 5] = best;

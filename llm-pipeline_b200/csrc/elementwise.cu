@@ -123,8 +123,9 @@ template <> struct Vec4<bf16> {
 };
 
 // PIECES 4-entry pieces per thread (piece p of thread t at column 4 (t + p * blockDim)): rows of at most 4096 PIECES entries.
+// The launcher starts up to 1024 threads (the widest rows of each PIECES); the bound keeps the registers within that.
 template <typename T, int PIECES>
-__global__ void add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_row4_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                         const void* __restrict__ delta_bias, int bias_bf16,
                                         const void* __restrict__ weight, int weight_bf16, float eps,
                                         T* __restrict__ out, const int* __restrict__ rows, int H) {

@@ -17,10 +17,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// Bounded wait: false (and *error_flag = 1) when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_flag) {
+// Bounded wait: false (and *error_flag = 1) when the phase did not complete within ``limit`` tries. The kernels wait
+// with TC_WAIT_LIMIT (mbar_wait below); the self-check of bounded_wait_check.cu passes a small limit to the same code.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, int* error_flag, uint32_t limit) {
     const uint32_t addr = tc_smem_u32(bar);
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -33,6 +34,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     }
     *reinterpret_cast<volatile int*>(error_flag) = 1;
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_flag) {
+    return mbar_wait_limited(bar, parity, error_flag, TC_WAIT_LIMIT);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {

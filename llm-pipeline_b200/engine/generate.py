@@ -66,8 +66,7 @@ class GenerationEngine:
     def _pages_that_fit(self, specs, page_size: int, fraction: float, max_num_seqs: int, max_model_len: int) -> int:
         """Pages per group from the device memory that is free after the weights: ``fraction`` of it,
         capped at what ``max_num_seqs`` requests of ``max_model_len`` tokens can use."""
-        element = 4 if self.dtype == torch.float32 else 2
-        per_page = sum(2 * kv.num_kv_heads * kv.head_dim * page_size * element for kv, _ in specs if kv is not None)
+        per_page = sum(CacheManager.bytes_per_page(specs, page_size, self.dtype))      # one page id in every group
         if per_page == 0:
             return 1
         free, _total = torch.cuda.mem_get_info(self.device)

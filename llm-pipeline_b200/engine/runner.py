@@ -20,7 +20,7 @@ from ..cache import CacheManager
 from ..models.model import Model
 from ..ops import kernels
 from ..parts import LayerCache
-from .context import StepContext
+from .context import StepContext, StepShape
 
 
 class OutOfPages(RuntimeError):
@@ -73,6 +73,7 @@ class ModelRunner:
     live in the graph's static buffer and are valid until the next step of the same shape."""
 
     GRAPH_WIDTH_STEP = 32
+    CONTEXT_BOUND_STEP = 128
     MAX_GRAPHS = 64
 
     def __init__(self, model: Model, cache: CacheManager, use_graphs: bool = True):
@@ -91,6 +92,7 @@ class ModelRunner:
         self.use_graphs = bool(use_graphs and parts is not None and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
+        self._context_limit = model.captured_context_limit() if hasattr(model, "captured_context_limit") else None
 
     # -- pages for the step's tokens -----------------------------------------------------------
     def _reserve(self, entries: Sequence[StepEntry]) -> None:
@@ -163,7 +165,7 @@ class ModelRunner:
         ctx.num_tokens, ctx.num_requests = q_start[-1], len(entries)
         ctx.max_q_len = max(ctx.q_lens)
         ctx.max_ctx_len = max(ctx_len)
-        ctx.decode_keys = (ctx.max_ctx_len, sum(ctx_len))
+        ctx.total_ctx = sum(ctx_len)
         lead = 0
         while lead < len(ctx.q_lens) and ctx.q_lens[lead] == 1:
             lead += 1
@@ -213,9 +215,26 @@ class ModelRunner:
             ctx.slot_mapping.append(take(N))
             ctx.block_tables.append(take(R * width).view(R, width))
 
+    @classmethod
+    def decode_graph_shape(cls, longest: int, page_size: int, max_request_tokens: int, limit: Optional[int] = None):
+        """(block-table width, context bound) of the graph that serves a decode step whose longest request sees
+        ``longest`` keys. The width is the request's pages rounded up to ``GRAPH_WIDTH_STEP``; the bound, for which the
+        captured kernels size their grids and scratch, is what that width can hold but never more than a request
+        may grow to (rounded up to ``CONTEXT_BOUND_STEP``). None as bound: it is beyond ``limit``, the longest context
+        the model's mixers take in a captured step (``Mixer.captured_context_limit``), so the step must run eagerly
+        with its real length."""
+        step_w = cls.GRAPH_WIDTH_STEP
+        width = -(-max(1, -(-longest // page_size)) // step_w) * step_w
+        split = cls.CONTEXT_BOUND_STEP
+        bound = min(width * page_size, -(-max(max_request_tokens, longest) // split) * split)
+        return width, (bound if limit is None or bound <= limit else None)
+
     def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Reserve pages and build the step context with its arrays on the device (one copy)."""
         self._reserve(entries)
+        return self._prepare_reserved(entries)
+
+    def _prepare_reserved(self, entries: Sequence[StepEntry]) -> StepContext:
         ctx = StepContext(self.device, self.dtype)
         flat = self._fill(ctx, entries)
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
@@ -235,12 +254,14 @@ class ModelRunner:
         ps = cache.page_size
         lengths = [cache.length(e.req_id) + 1 for e in entries]
         longest = max(lengths)
-        step_w = self.GRAPH_WIDTH_STEP
-        width = -(-max(1, -(-longest // ps)) // step_w) * step_w
-        # a graph holds the decode kernel that was chosen when it was captured: even and uneven batches have their own
-        total = sum(lengths)
-        which = tuple(kernels.decode_prefers_list(longest, total, len(entries), getattr(group.spec, "num_kv_heads", 1))
-                      for group in cache.groups)
+        width, bound = self.decode_graph_shape(longest, ps, cache.max_request_tokens, self._context_limit)
+        if bound is None:
+            # the width bucket reaches past what the decode kernels take although the request does not: no graph
+            ctx = self._prepare_reserved(entries)
+            return self._finish(ctx, entries, self._run(ctx))
+        # a graph holds the kernels that were chosen when it was captured; where a mixer's choice follows the step's
+        # shape (even and uneven contexts in attention), the mixers say so and such steps get graphs of their own
+        which = self.model.graph_key(StepShape(len(entries), longest, sum(lengths)))
         key = (len(entries), tuple(len(e.want) for e in entries), width, which)
         slot = self._graphs.get(key)
         if slot is None:
@@ -264,7 +285,7 @@ class ModelRunner:
             self._remember(slot, entries)
             slot.dev = slot.host.to(self.device)
             self._bind(slot.ctx, slot.dev)
-            slot.ctx.decode_ctx_bound = width * ps
+            slot.ctx.decode_ctx_bound = bound
             slot.copied = torch.cuda.Event()
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()

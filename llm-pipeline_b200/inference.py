@@ -137,12 +137,12 @@ class Qwen3InferenceEngine:
         ids = [self.engine.add_request(p, max_tokens, replace(base, seed=base.seed + i), eos_token_ids=eos,
                                        ignore_eos=bool(kwargs.get("ignore_eos", False)))
                for i, p in enumerate(prompts)]
-        done = {}
-        while len(done) < len(ids):
-            for request in self.engine.step():
-                done[request.req_id] = request
-        for i in ids:
-            r = done[i]
+        mine = [self.engine._requests[i] for i in ids]
+        # until every request of THIS call is finished: requests of other callers (an open stream, add_request) may
+        # finish meanwhile and are none of this call's business
+        while any(r.status != "finished" for r in mine):
+            self.engine.step()
+        for i, r in zip(ids, mine):
             self.engine._requests.pop(i, None)
             results.append(GenerationResult(i, r.prompt, r.output, r.finish_reason, r.preemptions))
         return results
@@ -171,19 +171,28 @@ class Qwen3InferenceEngine:
         request = self.engine._requests[req_id]
         sent = 0
         text_so_far = ""
-        while request.status != "finished":
-            self.engine.step()
-            if len(request.output) > sent:
-                if as_text:
-                    text = self.tokenizer.decode(request.output, skip_special_tokens=True)
-                    piece, text_so_far = text[len(text_so_far):], text
-                    if piece:
-                        yield piece
-                else:
-                    for token in request.output[sent:]:
-                        yield token
-                sent = len(request.output)
-        self.engine._requests.pop(req_id, None)
+        try:
+            while True:
+                # what the request has produced since the last look: in this call's own steps, or in the steps of
+                # another caller of the engine while this generator was not being read
+                if len(request.output) > sent:
+                    if as_text:
+                        text = self.tokenizer.decode(request.output, skip_special_tokens=True)
+                        piece, text_so_far = text[len(text_so_far):], text
+                        if piece:
+                            yield piece
+                    else:
+                        for token in request.output[sent:]:
+                            yield token
+                    sent = len(request.output)
+                if request.status == "finished":
+                    break
+                self.engine.step()
+        finally:
+            # a caller that stops iterating (or closes the generator) must not leave the request running with its pages
+            if request.status != "finished":
+                self.engine.scheduler.abort(req_id)
+            self.engine._requests.pop(req_id, None)
 
     def get_stats(self):
         return self.engine.stats()

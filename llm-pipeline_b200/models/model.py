@@ -10,7 +10,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..cache.spec import KVPagesSpec, StateSpec
+from ..cache.spec import PagesSpec, StateSpec
 from ..config.base import ModelSpec, PartSpec
 from ..parts import LayerCache, ResidualStream, lookup
 from ..weights.source import (ParamSpec, WeightSource, check_names_and_shapes, stored_dtype_policy)
@@ -30,7 +30,7 @@ class Model:
         for layer in spec.layers:
             block_cls = lookup("block", layer.block)
             self.blocks.append(block_cls(_make("mixer", layer.mixer), _make("feed_forward", layer.feed_forward),
-                                         _make("norm", layer.mixer_norm), _make("norm", layer.feed_forward_norm)))
+                                         norms={name: _make("norm", norm) for name, norm in layer.named_norms().items()}))
         self.final_norm = _make("norm", spec.final_norm)
         self.head = _make("head", spec.head)
         self.schedule = list(spec.schedule)
@@ -38,6 +38,9 @@ class Model:
         self._owner: Dict[int, int] = {}
         for i, entry in enumerate(self.schedule):
             self._owner.setdefault(entry.cache, i)
+        # one mixer of every group whose members answer ``graph_key`` alike (36 equal attention layers: one question)
+        self._key_mixers = list({block.mixer.graph_key_group(): block.mixer
+                                 for block in (self.blocks[e.layer] for e in self.schedule)}.values())
         self.device: Optional[torch.device] = None
         self.dtype: Optional[torch.dtype] = None
 
@@ -59,10 +62,21 @@ class Model:
                 out.setdefault(name, spec)
         return out
 
-    def cache_specs(self) -> List[Tuple[Optional[KVPagesSpec], Optional[StateSpec]]]:
+    def graph_key(self, shape) -> tuple:
+        """What the launches of a step of single tokens depend on beyond the number of requests, as the mixers say
+        (``Mixer.graph_key``): part of the key of a captured decode step."""
+        return tuple(mixer.graph_key(shape) for mixer in self._key_mixers)
+
+    def captured_context_limit(self) -> Optional[int]:
+        """The longest context every mixer takes in a captured step (None: any)."""
+        limits = [m.captured_context_limit() for m in self._key_mixers]
+        limits = [n for n in limits if n is not None]
+        return min(limits) if limits else None
+
+    def cache_specs(self) -> List[Tuple[Optional[PagesSpec], Optional[StateSpec]]]:
         """Per cache id, what the layer that owns it asks of the cache manager."""
         count = max((e.cache for e in self.schedule), default=-1) + 1
-        specs: List[Tuple[Optional[KVPagesSpec], Optional[StateSpec]]] = [(None, None)] * count
+        specs: List[Tuple[Optional[PagesSpec], Optional[StateSpec]]] = [(None, None)] * count
         for cache_id, index in self._owner.items():
             mixer = self.blocks[self.schedule[index].layer].mixer
             specs[cache_id] = (mixer.cache_spec(), mixer.state_spec())

@@ -54,6 +54,7 @@ _SIGNATURES = {
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "llmp_bounded_wait_check": [_P, _I, _P, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -290,6 +291,15 @@ def check_error_flag() -> None:
         raise KernelError("a kernel gave up waiting on one of its barriers (bounded wait ran out); its output is not valid")
 
 
+def bounded_wait_check(limit: int = 1024) -> bool:
+    """Self-check of the bounded waits: launches one thread that waits, with the kernels' own wait and a limit of
+    ``limit`` tries, on a barrier that nothing completes. True when the wait gave up; ``check_error_flag()`` then raises
+    after the next synchronisation, as it does when a wait of a real kernel runs out."""
+    gave_up = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _call("llmp_bounded_wait_check", error_flag().data_ptr(), int(limit), _ptr(gave_up), _stream())
+    return bool(int(gave_up.item()))
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA loads, accumulator in tensor
     memory); bfloat16 operands, bfloat16 or float32 output."""
@@ -457,6 +467,8 @@ def decode_scratch_floats(rows: int, num_heads: int, head_dim: int, max_ctx: int
 
 
 _decode_counters: dict = {}
+DECODE_RANGE = 128                   # keys per fixed range of the decode attention kernels
+DECODE_MAX_KEYS = 1024 * DECODE_RANGE   # the longest context the decode attention kernels take
 _DECODE_LIST = os.environ.get("LLMP_B200_DECODE_LIST", "")
 
 

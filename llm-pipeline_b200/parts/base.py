@@ -24,11 +24,11 @@ sides offer them; parts without them see tensors only.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Hashable, Optional, Tuple
 
 import torch
 
-from ..cache.spec import KVPagesSpec, StateSpec
+from ..cache.spec import KVPagesSpec, PagesSpec, StateSpec
 from ..ops.linear import PendingProduct
 from ..weights.source import ParamSpec
 
@@ -108,11 +108,27 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_spec(self) -> Optional[KVPagesSpec]:
+    def cache_spec(self) -> Optional[PagesSpec]:
         return None
 
     def state_spec(self) -> Optional[StateSpec]:
         return None
+
+    def graph_key(self, shape) -> Hashable:
+        """For a mixer whose launches for a step of single tokens depend on more than the number of requests: what they
+        depend on, as a hashable value (``shape``: ``engine.StepShape``). It becomes part of the key under which the step
+        function captures and replays such steps. None: nothing."""
+        return None
+
+    def captured_context_limit(self) -> Optional[int]:
+        """The longest context (keys a request sees) for which the mixer's kernels can be sized in a captured step of
+        single tokens; None: any. Mixers of one ``graph_key_group`` answer alike."""
+        return None
+
+    def graph_key_group(self) -> Hashable:
+        """Mixers that return equal values here give equal ``graph_key`` for every step; the model then asks one of
+        them. The default keeps every mixer apart."""
+        return id(self)
 
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         raise NotImplementedError
@@ -136,12 +152,35 @@ class Head(Part):
 
 
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    """An arrangement of a mixer, a feed-forward and named norms around the residual stream. ``norms`` maps the
+    names of ``LayerSpec.named_norms()`` to the built norms; the two of a pre-norm block may also come as the third
+    and fourth argument. ``NORMS`` lists the names a block kind needs; building a layer without one of them fails."""
+
+    NORMS: Tuple[str, ...] = ()
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Optional[Norm] = None,
+                 feed_forward_norm: Optional[Norm] = None, norms: Optional[Dict[str, Norm]] = None):
         self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.norms: Dict[str, Norm] = {}
+        if mixer_norm is not None:
+            self.norms["mixer"] = mixer_norm
+        if feed_forward_norm is not None:
+            self.norms["feed_forward"] = feed_forward_norm
+        self.norms.update(norms or {})
+        missing = [name for name in self.NORMS if name not in self.norms]
+        if missing:
+            raise ValueError(f"a {type(self).__name__} needs the norms {list(self.NORMS)}; the layer lacks {missing}")
+
+    @property
+    def mixer_norm(self) -> Optional[Norm]:
+        return self.norms.get("mixer")
+
+    @property
+    def feed_forward_norm(self) -> Optional[Norm]:
+        return self.norms.get("feed_forward")
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return tuple(self.norms.values()) + (self.mixer, self.feed_forward)
 
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         raise NotImplementedError

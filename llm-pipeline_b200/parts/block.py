@@ -13,6 +13,8 @@ from .registry import register_block
 
 @register_block("pre_norm_residual")
 class PreNormResidualBlock(Block):
+    NORMS = ("mixer", "feed_forward")
+
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         h = self._norm(self.mixer_norm, self.mixer, stream, ctx)
         out, bias = getattr(self.mixer, "forward_deferred", self.mixer.forward)(h, ctx, cache)

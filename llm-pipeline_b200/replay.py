@@ -11,7 +11,10 @@ Input, one JSON object per line on standard input::
 all entries of a step run as one batch. ``end``: requests that are finished after this step; their
 pages and slot are given back. For a step in which something is wanted, ``<out>/<step>.f32``
 receives the logits ``[wanted, vocab]`` as little-endian float32 in the order of the entries and
-of ``want``. After every step the line ``done <step>`` is printed and flushed.
+of ``want``. Every step that brings entries also writes ``<out>/<step>.pages.json``: for each of its requests the
+page ids of its block table in every cache group after the step (-1: a page a window has passed), so that a reader
+can see from the files alone that a page went from a finished request to a later one. After every step the line
+``done <step>`` is printed and flushed.
 """
 
 from __future__ import annotations
@@ -73,6 +76,10 @@ def main(argv: Optional[Sequence[str]] = None, stdin=None, stdout=None) -> int:
                 os.path.join(args.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize(model.device)
+        if entries:
+            tables = {str(e.req_id): [list(cache.block_table(e.req_id, g)) for g in range(len(cache.groups))] for e in entries}
+            with open(os.path.join(args.out, f"{step}.pages.json"), "w") as f:
+                json.dump({"step": step, "page_size": PAGE_SIZE, "pages": tables}, f)
         kernels.check_error_flag()                      # a kernel whose bounded wait ran out leaves no valid logits
         for req_id in record.get("end", []):
             runner.release(req_id)

@@ -1,14 +1,17 @@
-"""Importable name of the package whose sources live in the folder ``llm-pipeline_b200/``.
+"""Importable name, in a checkout, of the package whose sources live in the folder ``llm-pipeline_b200/``.
 
-A hyphen cannot appear in a Python module name, so this module points its ``__path__`` at that
-folder and runs the folder's ``__init__.py`` in its own namespace; ``import llm_pipeline_b200.engine``
-then resolves to ``llm-pipeline_b200/engine``.
+A hyphen cannot appear in a Python module name. An installed copy maps the folder to this name (``pyproject.toml``,
+``package-dir``); in a checkout this module loads the folder's ``__init__.py`` as the package ``llm_pipeline_b200``
+through importlib's own loader and puts it in its place, so that ``import llm_pipeline_b200.engine`` resolves to
+``llm-pipeline_b200/engine``.
 """
 
+import importlib.util as _util
 import os as _os
+import sys as _sys
 
 _real = _os.path.normpath(_os.path.join(_os.path.dirname(_os.path.abspath(__file__)), _os.pardir, "llm-pipeline_b200"))
-__path__ = [_real]
-with open(_os.path.join(_real, "__init__.py")) as _f:
-    exec(compile(_f.read(), _os.path.join(_real, "__init__.py"), "exec"))
-del _f
+_spec = _util.spec_from_file_location(__name__, _os.path.join(_real, "__init__.py"), submodule_search_locations=[_real])
+_module = _util.module_from_spec(_spec)
+_sys.modules[__name__] = _module
+_spec.loader.exec_module(_module)

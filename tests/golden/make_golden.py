@@ -10,9 +10,10 @@ of ``tests/plain_qwen3.py``, loads the same seeded random weights by name, and r
 * the reference's own incremental path (a prefix, then single tokens with ``past_key_values``).
 
 It prints the largest differences from ``plain_qwen3.forward_logits`` and writes
-``tests/golden/<name>.json``: the token ids and, for a few positions, the reference's logits
-(first 8 vocabulary entries), its argmax and the largest absolute logit, so that
-``tests/test_plain_reference.py`` can check the plain implementation without the reference.
+``tests/golden/<name>.json``: the token ids and, for a few positions, the reference's logits over
+the whole vocabulary, its argmax and the largest absolute logit, so that
+``tests/test_plain_reference.py`` can check the plain implementation without the reference. All five
+tiny configurations are recorded, head sizes 16, 32, 48, 64 and 128 among them.
 """
 
 from __future__ import annotations
@@ -47,7 +48,8 @@ def main() -> int:
     torch.manual_seed(0)
     summary = {}
     for name, config, seed, length in (("tiny_a", plain.TINY_A, 0, 33), ("tiny_b", plain.TINY_B, 1, 40),
-                                       ("tiny_c", plain.TINY_C, 2, 29)):
+                                       ("tiny_c", plain.TINY_C, 2, 29), ("tiny_d", plain.TINY_D, 3, 37),
+                                       ("tiny_e", plain.TINY_E, 4, 45)):
         weights = plain.random_weights(config, seed)
         model = ref.Qwen3ForCausalLM(ref.Qwen3Config(**config)).eval()
         state = dict(weights)
@@ -78,14 +80,14 @@ def main() -> int:
         positions = [0, 1, length // 2, length - 1]
         summary = {
             "config": config, "seed": seed, "token_ids": ids, "positions": positions,
-            "logits_head": [[round(float(v), 7) for v in whole[p, :8]] for p in positions],
+            "logits": [[round(float(v), 7) for v in whole[p]] for p in positions],
             "argmax": [int(whole[p].argmax()) for p in positions],
             "max_abs_logit": scale,
             "plain_minus_reference_whole": diff_whole,
             "plain_minus_reference_incremental": diff_incremental,
         }
         with open(os.path.join(HERE, f"{name}.json"), "w") as f:
-            json.dump(summary, f, indent=1)
+            f.write("{\n" + ",\n".join(f" {json.dumps(k)}: {json.dumps(v)}" for k, v in summary.items()) + "\n}\n")
         assert diff_whole < 2e-5 and diff_incremental < 5e-5
     return 0
 

@@ -11,7 +11,8 @@ import torch
 
 import plain_qwen3 as plain
 
-TOL = {torch.float32: 1e-4, torch.bfloat16: 4e-2}
+# absolute, on logits of the tiny models (largest about 1); the engine in bfloat16 is about 5e-3 from the oracle there
+TOL = {torch.float32: 1e-4, torch.bfloat16: 1.5e-2}
 
 
 def write_model_dir(path: str, config: dict, weights: Dict[str, torch.Tensor], dtype: torch.dtype) -> str:

@@ -128,8 +128,10 @@ def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], index: int, confi
 
 
 def forward_logits(config: dict, weights: Dict[str, torch.Tensor], token_ids: Sequence[int],
-                   dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """models/qwen3/custom_builder.py:311-375,393-421 — logits [T, V] of one whole sequence."""
+                   dtype: torch.dtype = torch.float32, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """models/qwen3/custom_builder.py:311-375,393-421 — logits [T, V] of one whole sequence. ``rows`` keeps only
+    those positions for the output head (a large vocabulary times a long sequence is a lot of logits nobody reads);
+    the layers always run on the whole sequence."""
     w = {k: v.to(dtype) for k, v in weights.items()}
     device = next(iter(w.values())).device
     ids = torch.as_tensor(list(token_ids), dtype=torch.long, device=device)
@@ -144,6 +146,8 @@ def forward_logits(config: dict, weights: Dict[str, torch.Tensor], token_ids: Se
         head = w["model.embed_tokens.weight"]
     else:
         head = w["lm_head.weight"]
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=device)]
     return x @ head.t()                                                         # :415
 
 

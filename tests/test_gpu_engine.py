@@ -83,8 +83,8 @@ def test_mixed_batches_with_decoded_tokens_through_the_decode_kernel(tmp_path, m
     """In a step that mixes decoded tokens with portions of prompts, the single-token requests at its front go through
     the decode kernel once one of them has a long context; here always, with the decoding requests put first as the scheduler
     does."""
-    from llm_pipeline_b200.engine.context import StepContext
-    monkeypatch.setattr(StepContext, "SPLIT_DECODE_MIN_CONTEXT", 0)
+    from llm_pipeline_b200.parts.attention import AttentionPolicy
+    monkeypatch.setattr(AttentionPolicy, "SPLIT_DECODE_MIN_CONTEXT", 0)
     folder, weights = H.make_case(tmp_path, config, seed, dtype)
     requests = _requests(config, tuple(lengths) + (29, 12, 44, 7))
     want = H.expected_logits(config, weights, requests)
@@ -99,9 +99,9 @@ def test_mixed_batches_with_decoded_tokens_through_the_decode_kernel(tmp_path, m
 def test_prompt_portions_whose_tiles_share_their_keys(tmp_path, monkeypatch):
     """Long contexts make the work list of the tcgen05 attention kernel cut a tile's keys into items; here from the
     second key tile on, so that the tiny model's portions take that path: portions of changing size and mixed steps."""
-    from llm_pipeline_b200.engine.context import StepContext
     from llm_pipeline_b200.ops import kernels
-    monkeypatch.setattr(StepContext, "SPLIT_KEYS_MIN_TILES", 1)
+    from llm_pipeline_b200.parts.attention import AttentionPolicy
+    monkeypatch.setattr(AttentionPolicy, "SPLIT_KEYS_MIN_TILES", 1)
     shared, launch = [], kernels.paged_attention
 
     def counting(*args, **kwargs):

@@ -217,6 +217,90 @@ def test_trace_run_program(tmp_path, dtype_name):
             assert float((data[row:row + len(w)] - ref).abs().max()) <= H.TOL[dtype], (i, rid)
             row += len(w)
             cursor[rid] += len(toks)
+    # the page ids the program wrote per step: a page that a finished request held is later held by another one
+    held_by_finished = {}
+    handed_on = 0
+    for i, (entries, end) in enumerate(steps):
+        if not entries:
+            assert not (out_dir / f"{i}.pages.json").exists()
+            continue
+        pages = json.loads((out_dir / f"{i}.pages.json").read_text())["pages"]
+        assert set(pages) == {rid for rid, _, _ in entries}
+        for rid, tables in pages.items():
+            assert len(tables[0]) == -(-cursor_after(steps, i, rid) // 16)
+            for page in tables[0]:
+                if page in held_by_finished and held_by_finished[page] != rid:
+                    handed_on += 1
+        for rid in end:
+            for page in pages[rid][0]:
+                held_by_finished[page] = rid
+    assert handed_on > 0
+
+
+def cursor_after(steps, upto, rid):
+    return sum(len(toks) for entries, _ in steps[:upto + 1] for r, toks, _ in entries if r == rid)
+
+
+def write_tokenizer(folder, vocab_size):
+    """A word-level tokenizer.json with ``vocab_size`` entries and a tokenizer_config.json with a one-line chat template."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    words = ["<unk>", "<eos>"] + [f"w{i}" for i in range(vocab_size - 2)]
+    tokenizer = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tokenizer.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tokenizer.save(os.path.join(folder, "tokenizer.json"))
+    with open(os.path.join(folder, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<eos>", "unk_token": "<unk>",
+                   "chat_template": "{% for m in messages %}w7 {{ m['content'] }} w8{% endfor %}"}, f)
+
+
+def test_string_prompts_through_a_tokenizer(tmp_path):
+    """The reference's public shape (src/llm_pipeline/inference/qwen3_engine.py:311-350, src/llm_pipeline/cli.py:24-41):
+    a string in, a string out; a list of strings in, a list out; pieces of text from the stream; ``--prompt`` and
+    ``--chat`` on the command line. The folder gets a tiny word-level tokenizer whose ids are the model's vocabulary."""
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    write_tokenizer(folder, tiny["vocab_size"])
+    engine = engine_for(folder, torch.float32)
+    assert engine.tokenizer is not None and engine.config.eos_token_id == 1
+    ids = [5, 17, 3, 200, 9]
+    text = " ".join(f"w{i - 2}" for i in ids)
+    assert engine.tokenizer(text)["input_ids"] == ids
+    want_ids = plain.greedy_generate(tiny, weights, ids, 6, eos_token_id=1)
+    want = engine.tokenizer.decode(want_ids, skip_special_tokens=True)
+    assert engine.generate(text, max_tokens=6, temperature=0.0) == want
+    assert engine.generate([text, text], max_tokens=6, temperature=0.0) == [want, want]
+    assert "".join(engine.stream_generate(text, max_tokens=6, temperature=0.0)) == want
+    assert engine.engine.cache.num_live == 0
+    base = [sys.executable, "-m", "llm_pipeline_b200.cli", "infer", "--model", folder, "--dtype", "fp32",
+            "--max-new-tokens", "6", "--temperature", "0"]
+    proc = subprocess.run(base + ["--prompt", text], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.strip() == want
+    proc = subprocess.run(base + ["--prompt", text, "--chat"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    chat_ids = [9] + ids + [10]                                      # the template wraps the prompt in w7 ... w8
+    assert proc.stdout.strip() == engine.tokenizer.decode(plain.greedy_generate(tiny, weights, chat_ids, 6, eos_token_id=1),
+                                                          skip_special_tokens=True)
+
+
+def test_a_stream_that_nobody_reads_to_the_end(tmp_path):
+    """A caller that stops reading a stream leaves no request behind, and a generate call made while a stream is
+    open waits for its own requests only."""
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    engine = engine_for(folder, torch.float32)
+    prompt = H.random_tokens(256, 9, 77)
+    stream = engine.stream_generate(prompt, max_tokens=5, temperature=0.0)
+    first = next(stream)
+    assert engine.engine.cache.num_live == 1
+    other = H.random_tokens(256, 12, 78)
+    got = engine.generate(other, max_tokens=12, temperature=0.0)      # the stream's request finishes during this call
+    assert got == plain.greedy_generate(tiny, weights, other, 12)
+    assert [first] + list(stream) == plain.greedy_generate(tiny, weights, prompt, 5)
+    stream = engine.stream_generate(prompt, max_tokens=50, temperature=0.0)
+    next(stream)
+    stream.close()
+    assert engine.engine.cache.num_live == 0 and not engine.engine.has_unfinished()
 
 
 def test_cli_infer_with_token_ids(tmp_path):

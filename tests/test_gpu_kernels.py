@@ -51,7 +51,7 @@ def test_rope_tables_match_the_reference_formula():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H", [1000, 4096 + 16, 5120, 8200, 1002, 16400])
+@pytest.mark.parametrize("H", [1000, 4096, 4096 + 16, 5120, 8192, 8200, 1002, 16384, 16400])       # 4096, 8192, 16384: blocks of 1024 threads
 def test_add_rmsnorm(dtype, H):
     residual = rnd(7, H, seed=1)
     delta = rnd(7, H, dtype=dtype, seed=2)
@@ -564,3 +564,26 @@ def test_gemm_stream_between_norms(M, N, Kd, H):
     want_act = torch.nn.functional.silu(want[:, :96]) * want[:, 96:]
     assert float((act.double() - want_act).abs().max()) <= 3e-2 * max(1.0, float(want_act.abs().max()))
     k_.check_error_flag()
+
+
+def test_a_wait_that_runs_out_reaches_the_host_and_the_next_launch_works():
+    """Every wait on a barrier in the TMA and tcgen05 kernels is bounded; a wait that runs out sets a word in mapped
+    host memory and the kernel returns. Here the kernels' own wait gets a barrier that nothing completes and a small
+    limit: it gives up, the host check raises, and the device goes on working (nothing faulted or hung)."""
+    from llm_pipeline_b200.ops.kernels import KernelError
+    k = K()
+    torch.cuda.synchronize()
+    k.check_error_flag()                                     # clean before
+    assert k.bounded_wait_check(limit=1024)                  # the wait returned without completion
+    torch.cuda.synchronize()
+    with pytest.raises(KernelError, match="gave up waiting"):
+        k.check_error_flag()
+    k.check_error_flag()                                     # raising cleared the word
+    x, w = rnd(8, 256, dtype=torch.bfloat16, seed=1), rnd(512, 256, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(8, 512, dtype=torch.float32, device=DEV)
+    k.gemm_tc(x, w, out)                                     # a kernel with bounded waits of its own, right after
+    torch.cuda.synchronize()
+    k.check_error_flag()
+    assert torch.allclose(out, x.float() @ w.float().t(), atol=1e-3, rtol=1e-3)
+    with pytest.raises(KernelError):
+        k.bounded_wait_check(limit=0)

@@ -1,7 +1,7 @@
 """The host-side decisions about attention work (no GPU): which decode kernel a step takes and how the work list of
 the general kernel shares a tile's keys among items, for a GPU of 148 SMs."""
 
-from llm_pipeline_b200.engine.context import StepContext
+from llm_pipeline_b200.parts.attention import AttentionPolicy
 from llm_pipeline_b200.ops import kernels
 
 SMS = 148
@@ -23,7 +23,7 @@ def test_uneven_or_many_requests_take_the_list_kernel():
 
 
 def plan(starts, q_lens, max_segments=8, kv_heads=8, tokens_per_tile=32, first=0):
-    return StepContext.plan_attention_items(starts, q_lens, tokens_per_tile, first, max_segments, kv_heads, SMS)
+    return AttentionPolicy.plan_items(starts, q_lens, tokens_per_tile, first, max_segments, kv_heads, SMS)
 
 
 def items_of(plan_):
@@ -76,3 +76,23 @@ def test_requests_before_the_first_are_left_out_and_mixed_lengths_split_by_their
     assert by_request[(1, 0)] == 1 and by_request[(1, 32)] == 1        # 140 keys: whole
     assert by_request[(2, 0)] == 8 and by_request[(2, 32)] == 8        # 20,033 keys: shared
     assert places == 16
+
+
+def test_decode_graph_shape_at_the_kernels_limit():
+    """The block-table width of a decode graph is rounded up to 32 pages; the context bound its kernels are sized for
+    never passes what a request may hold, and a bound beyond the decode kernels' limit means: no graph."""
+    from llm_pipeline_b200.engine.runner import ModelRunner
+    from llm_pipeline_b200.ops import kernels
+    limit = kernels.DECODE_MAX_KEYS
+
+    def shape(longest, page, most):
+        return ModelRunner.decode_graph_shape(longest, page, most, limit)
+
+    assert shape(2049, 16, 4096) == (160, 2560)                       # 129 pages -> 160; 160 * 16 keys
+    assert shape(4000, 16, 4096) == (256, 4096)
+    assert shape(4090, 16, 4090) == (256, 4096)                       # the limit of the request, rounded up to a range
+    # a request of legal length whose width bucket alone reaches past the limit: clamped, the graph stays
+    assert shape(limit - 5, 48, limit) == (2752, limit)
+    # a cache made for longer requests than the decode kernels take: eager steps, which refuse only what really is too long
+    assert shape(limit - 5, 48, 2 * limit) == (2752, None)
+    assert shape(1000, 16, 2 * limit) == (64, 1024)

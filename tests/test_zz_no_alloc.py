@@ -53,3 +53,15 @@ def test_no_alloc_argmax_refuses_more_rows_than_its_scratch_holds():
     assert fn(logits.data_ptr(), 16, 4, 16, out.data_ptr(), stream) == 0   # still usable after a refusal
     torch.cuda.synchronize()
     assert out[:4].tolist() == [0, 0, 0, 0]
+
+
+def test_no_alloc_source_names_no_allocating_call():
+    """The check on torch's allocator above cannot see a raw runtime allocation inside the library, so the source
+    is read: the file names none of the runtime's allocating or freeing calls."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "llm-pipeline_b200", "csrc", "argmax_no_alloc.cu")) as f:
+        code = re.sub(r"//[^\n]*", "", f.read())
+    for name in ("cudaMalloc", "cudaFree", "cudaMallocAsync", "cudaHostAlloc", "cuMemAlloc", "new ", "malloc("):
+        assert name not in code, name
