@@ -10,8 +10,16 @@ for every request of the batch, from the embedding to the sampled token id. It p
 through the Python entry point (``GenerationEngine.step``: host token lists in, host token ids out,
 the index arrays copied from pinned memory every step); ``prefill`` is one 2,048-token prompt in one
 step; ``roofline`` is the decode step against the bytes it must read; ``points`` are decode at batch
-1 and 64. All weights and token ids are synthetic (seeded); the inputs are far larger than L2, so
-no flush is needed between iterations.
+1 and 64 and at batch 8 with pages of 32 tokens. ``breakdown`` gives, for one decode step of the batch
+and for the prefill step, the device time of every kernel class (CUDA events around every launch of
+an eager step that is queued behind a sleeping kernel, so that launches do not wait for the host) with
+the achieved GB/s of the weight-streaming products and the decode attention and the TFLOP/s of the
+prefill products and attention, each over the measured peak (burst figure: kernels alone).
+``baselines.plain_pytorch`` is this repository's plain PyTorch implementation (``tests/plain_qwen3.py``:
+whole sequences, no cache) on the same GPU in bfloat16 at batch 1. ``selfcheck`` compares, outside any
+timed region, the greedy tokens of steps of 8 and 64 requests on a two-layer model of the same widths
+with the plain implementation. All weights and token ids are synthetic (seeded); the inputs are far
+larger than L2, so no flush is needed between iterations.
 
 ``--impl reference`` runs DavidAkinpelu/llm-pipeline's own ``Qwen3ForCausalLM`` from
 ``baseline/_ref`` (installed offline with pip --no-deps --target) with its ``past_key_values``
@@ -56,10 +64,10 @@ def peaks():
                 data = json.load(f)
             return {"hbm_gbs": float(data["hbm_gbs"]),
                     "bf16_tflops": float(data.get("bf16_tflops_sustained") or data["bf16_tflops"]),
-                    "source": "measured"}
+                    "bf16_tflops_burst": float(data["bf16_tflops"]), "source": "measured"}
         except Exception:
             pass
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_burst": 1590.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -119,8 +127,9 @@ def weight_bytes(cfg, layers, element=2):
     return (layers * per_layer + V * H + H) * element          # the layers, the output head and the final norm
 
 
-def kv_bytes_per_token(cfg, layers, element=2):
-    return 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * layers * element
+def kv_bytes_per_token(engine):
+    """Bytes the caches of all layers hold per token, from what the mixers ask of the cache manager."""
+    return sum(pages.bytes_per_token(engine.dtype) for pages, _state in engine.model.cache_specs() if pages is not None)
 
 
 def prefill_flops(cfg, layers, T):
@@ -131,7 +140,7 @@ def prefill_flops(cfg, layers, T):
     return layers * (per_token * T + attention) + 2 * V * H
 
 
-def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256, pages=None):
+def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256, pages=None, page_size=None, model=None):
     import torch
 
     from llm_pipeline_b200.config import resolve_config
@@ -141,12 +150,14 @@ def build_ours(cfg, layers, batch_cap, dtype, tokens_per_request=CONTEXT + 256, 
     from llm_pipeline_b200.weights import random_tensors
 
     build_library()
+    page_size = page_size or PAGE_SIZE
     config = resolve_config({**cfg, "num_hidden_layers": layers})
-    model = build_model(config)
-    model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
+    if model is None:
+        model = build_model(config)
+        model.load(random_tensors(config, seed=0, dtype=dtype, device="cuda:0"), torch.device("cuda:0"), dtype)
     if pages is None:
-        pages = batch_cap * (-(-tokens_per_request // PAGE_SIZE))
-    engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=pages, max_num_seqs=batch_cap,
+        pages = batch_cap * (-(-tokens_per_request // page_size))
+    engine = GenerationEngine(model, config, page_size=page_size, num_pages=pages, max_num_seqs=batch_cap,
                               max_num_batched_tokens=PREFILL_TOKENS, max_model_len=tokens_per_request)
     return engine
 
@@ -252,6 +263,237 @@ def time_prefill(engine, tokens, repeats, warmup):
     return times[len(times) // 2]
 
 
+class KernelTimes:
+    """CUDA events around every kernel launch of an eager step: this library's entry points (all go through
+    ``kernels._call``) and the library matrix product (``torch.mm``). The step is queued behind a sleeping kernel, so
+    the launches wait on the device, not for the host, and an interval is the kernel's own time (plus the events')."""
+
+    GEMMS = ("llmp_gemm_stream", "llmp_gemm_stream_fused", "llmp_gemm_stream_swiglu", "llmp_gemm_stream_tc", "llmp_gemm_tc",
+             "llmp_gemm_skinny")
+
+    def __init__(self, cfg):
+        self.cfg = cfg
+        self.items = []
+
+    def product_class(self, N, K):
+        cfg = self.cfg
+        H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+        q = cfg["num_attention_heads"] * cfg["head_dim"]
+        qkv = q + 2 * cfg["num_key_value_heads"] * cfg["head_dim"]
+        if N == V:
+            return "product_head"
+        if N == 2 * I:
+            return "product_gate_up"
+        if N == qkv and K == H:
+            return "product_qkv"
+        if N == H and K == I:
+            return "product_down"
+        if N == H and K == q:
+            return "product_o"
+        return "product_other"
+
+    def __enter__(self):
+        import torch
+
+        from llm_pipeline_b200.ops import kernels
+        self._call, self._mm = kernels._call, torch.mm
+        outer = self
+
+        def timed(label, work, fn, *args, **kwargs):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = fn(*args, **kwargs)
+            stop.record()
+            outer.items.append((label, work, start, stop))
+            return out
+
+        def call(name, *args):
+            label, work = name[5:], None
+            if name in self.GEMMS:
+                M, N, K = args[4], args[5], args[6]
+                if name == "llmp_gemm_stream_swiglu":
+                    N *= 2
+                label, work = outer.product_class(N, K) + ("+swiglu" if name == "llmp_gemm_stream_swiglu" or
+                                                           (name == "llmp_gemm_stream_fused" and args[10]) else ""), (M, N, K)
+            return timed(label, work, outer._call, name, *args)
+
+        def mm(a, b, **kwargs):
+            M, K, N = a.shape[0], a.shape[1], b.shape[1]
+            return timed(outer.product_class(N, K) + " (library)", (M, N, K), outer._mm, a, b, **kwargs)
+
+        kernels._call, torch.mm = call, mm
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+
+        from llm_pipeline_b200.ops import kernels
+        kernels._call, torch.mm = self._call, self._mm
+
+    def summary(self, peak, attention_bytes=0.0, attention_flops=0.0):
+        """Per class: launches, microseconds, and for the products and the attention kernels what they achieved over the
+        measured peak (GB/s of the bytes they must read when the rows are few, TFLOP/s otherwise)."""
+        classes = {}
+        for label, work, start, stop in self.items:
+            entry = classes.setdefault(label, {"launches": 0, "us": 0.0, "bytes": 0.0, "flops": 0.0, "rows": 0})
+            entry["launches"] += 1
+            entry["us"] += start.elapsed_time(stop) * 1e3
+            if work is not None:
+                M, N, K = work
+                entry["bytes"] += 2.0 * N * K + 2.0 * M * K + 2.0 * M * N
+                entry["flops"] += 2.0 * M * N * K
+                entry["rows"] = M
+        out = {}
+        total = sum(e["us"] for e in classes.values())
+        for label, e in sorted(classes.items(), key=lambda kv: -kv[1]["us"]):
+            row = {"launches": e["launches"], "us": round(e["us"], 1), "share": round(e["us"] / total, 3)}
+            seconds = e["us"] * 1e-6
+            if label == "decode_attention" and attention_bytes:
+                e["bytes"], e["rows"] = attention_bytes, 1
+            if label == "paged_attention" and attention_flops:
+                e["flops"], e["rows"] = attention_flops, 1 << 20
+            if e["bytes"] and e["rows"] <= 64:
+                row["gbs"] = round(e["bytes"] / seconds / 1e9, 1)
+                row["frac_hbm"] = round(e["bytes"] / seconds / 1e9 / peak["hbm_gbs"], 3)
+            elif e["flops"]:
+                row["tflops"] = round(e["flops"] / seconds / 1e12, 1)
+                row["frac_bf16_burst"] = round(e["flops"] / seconds / 1e12 / peak["bf16_tflops_burst"], 3)
+            out[label] = row
+        return {"kernel_us": round(total, 1), "classes": out}
+
+
+def breakdown_of_a_step(engine, cfg, peak, entries_of, attention_bytes=0.0, attention_flops=0.0, release=()):
+    """One eager step (no graph) with events around every launch, queued behind a sleeping kernel."""
+    import torch
+
+    runner = engine.runner
+    graphs, runner.use_graphs = runner.use_graphs, False
+    try:
+        runner.step(entries_of(0))                      # untimed: first-call set-up of every kernel of the shape
+        torch.cuda.synchronize()
+        times = KernelTimes(cfg)
+        torch.cuda._sleep(int(1.5e8))                   # some 80 ms at the SM clock: the whole step queues up behind it
+        with times:
+            runner.step(entries_of(1))
+        torch.cuda.synchronize()
+    finally:
+        runner.use_graphs = graphs
+        for rid in release:
+            runner.release(rid)
+    return times.summary(peak, attention_bytes, attention_flops)
+
+
+def decode_breakdown(engine, cfg, peak, batch):
+    import torch
+
+    from llm_pipeline_b200.engine import StepEntry
+
+    vocab = engine.model.spec.vocab_size
+    prompts = random_prompts(vocab, batch, CONTEXT - 2, 77)
+    ids = [f"breakdown{i}" for i in range(batch)]
+    for rid, prompt in zip(ids, prompts):
+        engine.runner.step([StepEntry(rid, prompt, [])])
+    layers = len(engine.model.schedule)
+    kv_bytes = batch * CONTEXT * kv_bytes_per_token(engine)
+    out = breakdown_of_a_step(engine, cfg, peak, lambda k: [StepEntry(rid, [p[k]], [0]) for rid, p in zip(ids, prompts)],
+                              attention_bytes=kv_bytes, release=ids)
+    out["launches_per_step"] = sum(c["launches"] for c in out["classes"].values())
+    out["layers"] = layers
+    return out
+
+
+def prefill_breakdown(engine, cfg, peak, tokens):
+    from llm_pipeline_b200.engine import StepEntry
+
+    vocab = engine.model.spec.vocab_size
+    prompts = random_prompts(vocab, 2, tokens, 88)
+    layers = len(engine.model.schedule)
+    flops = layers * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
+    runner = engine.runner
+
+    def entries(k):
+        if k:
+            runner.release("prefill_breakdown")
+        return [StepEntry("prefill_breakdown", prompts[k], [tokens - 1])]
+
+    return breakdown_of_a_step(engine, cfg, peak, entries, attention_flops=flops, release=["prefill_breakdown"])
+
+
+def plain_baseline(cfg, layers, tokens):
+    """This repository's plain PyTorch implementation (tests/plain_qwen3.py: whole sequences, no cache, library
+    products) in bfloat16 on the GPU with the same seeded weights: the time of one forward over ``tokens`` tokens, which
+    is its prefill and, having no cache, also what one more decoded token costs it at that context."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_qwen3 as plain
+
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.weights import random_tensors
+
+    config_json = {**cfg, "num_hidden_layers": layers}
+    source = random_tensors(resolve_config(config_json), seed=0, dtype=torch.bfloat16, device="cuda:0")
+    weights = {name: source.get(name) for name in source.names()}
+    ids = random_prompts(cfg["vocab_size"], 1, tokens, 99)[0]
+    times = []
+    with torch.no_grad():
+        for i in range(5):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            logits = plain.forward_logits(config_json, weights, ids, dtype=torch.bfloat16, rows=[tokens - 1])
+            token = int(logits[0].argmax())
+            stop.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(start.elapsed_time(stop))
+    del weights, logits
+    torch.cuda.empty_cache()
+    ms = sorted(times)[len(times) // 2]
+    return {"what": "tests/plain_qwen3.py, bfloat16, whole sequence per token (no cache)", "context": tokens, "layers": layers,
+            "ms_per_forward": round(ms, 3), "decode_b1": round(1e3 / ms, 2), "prefill": round(tokens * 1e3 / ms, 1), "last_token": token}
+
+
+def selfcheck(cfg, batches=(8, 64), prompt_tokens=48, new_tokens=4):
+    """Outside every timed region: a two-layer model of the benchmark's widths generates greedily through the Python
+    entry point in steps of 8 and of 64 requests (the fused streaming products, the library products and both decode
+    attention streams), and every generated token must be the plain implementation's greedy choice at its place, or
+    lose to it by less than the bfloat16 rounding noise of these logits (0.25 on logits that reach 7)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_qwen3 as plain
+
+    from llm_pipeline_b200.weights import random_tensors
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    engine = build_ours(cfg, 2, max(batches), torch.bfloat16, tokens_per_request=256)
+    config_json = {**cfg, "num_hidden_layers": 2}
+    source = random_tensors(engine.config, seed=0, dtype=torch.bfloat16, device="cuda:0")
+    weights = {name: source.get(name).float() for name in source.names()}
+    report = {}
+    for batch in batches:
+        prompts = random_prompts(cfg["vocab_size"], batch, prompt_tokens, 4000 + batch)
+        results = engine.generate(prompts, max_tokens=new_tokens, temperature=0.0, ignore_eos=True)
+        equal = close = wrong = 0
+        for prompt, result in zip(prompts, results):
+            ids = list(prompt) + list(result.token_ids)
+            rows = list(range(len(prompt) - 1, len(ids) - 1))
+            logits = plain.forward_logits(config_json, weights, ids, rows=rows)
+            for row, token in zip(logits, result.token_ids):
+                best = int(row.argmax())
+                if best == token:
+                    equal += 1
+                elif float(row[best] - row[token]) < 0.25:
+                    close += 1
+                else:
+                    wrong += 1
+        report[f"batch_{batch}"] = {"tokens": batch * new_tokens, "equal": equal, "within_rounding": close, "wrong": wrong}
+    del engine, weights
+    torch.cuda.empty_cache()
+    report["ok"] = all(r["wrong"] == 0 and r["equal"] >= 0.9 * r["tokens"] for r in report.values() if isinstance(r, dict))
+    return report
+
+
 def run_mix(args):
     """A continuous-batching mix through the Python entry point: 64 requests with prompt lengths uniform in
     [16, 2048] and 128 decoded tokens each (seeded), context up to 4,096; reports total tokens per second."""
@@ -330,7 +572,23 @@ def run_ours(args):
         points[f"decode_b{b}"] = round(r["tok_s"], 1)
     prefill_ms = time_prefill(engine, PREFILL_TOKENS, repeats=5, warmup=3)
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
-    step_bytes = weight_bytes(cfg, layers) + args.batch * (CONTEXT + args.warmup + args.steps // 2) * kv_bytes_per_token(cfg, layers)
+    kv_per_token = kv_bytes_per_token(engine)
+    breakdown = baselines = check = None
+    if not args.lean:
+        breakdown = {f"decode_b{args.batch}": decode_breakdown(engine, cfg, peak, args.batch),
+                     f"prefill_{PREFILL_TOKENS}": prefill_breakdown(engine, cfg, peak, PREFILL_TOKENS)}
+        # the same batch with pages of 32 tokens (half as many TMA boxes in the decode attention stream)
+        other_page = 32 if PAGE_SIZE != 32 else 16
+        wide = build_ours(cfg, layers, args.batch, dtype, tokens_per_request=max(CONTEXT + 256, room), page_size=other_page,
+                          model=engine.model)
+        r = time_decode(wide, args.batch, max(5, args.steps // 2), args.warmup, seed=30, e2e=False)
+        points[f"decode_b{args.batch}_page{other_page}"] = round(r["tok_s"], 1)
+        del wide
+        del engine
+        torch.cuda.empty_cache()
+        baselines = {"plain_pytorch": plain_baseline(cfg, layers, CONTEXT)}
+        check = selfcheck(cfg)
+    step_bytes = weight_bytes(cfg, layers) + args.batch * (CONTEXT + args.warmup + args.steps // 2) * kv_per_token
     achieved = step_bytes / (main["ms"] * 1e-3) / 1e9
     line = {
         "metric": f"decode tok/s at batch {args.batch}, 2,048-token context ({name.split()[0]} bf16)",
@@ -348,14 +606,19 @@ def run_ours(args):
         "gpu_launches": main["launches"],
         "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4),
+                    "frac_burst": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops_burst"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
         "clocks": clock_info,
     }
+    if breakdown is not None:
+        line["breakdown"] = breakdown
+        line["baselines"] = baselines
+        line["selfcheck"] = check
     print(json.dumps(line))
-    return 0
+    return 0 if check is None or check["ok"] else 1
 
 
 def run_reference(args):
@@ -428,7 +691,8 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=4)
-    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference", "plain"),
+                        help="plain: this repository's plain PyTorch implementation (tests/plain_qwen3.py) alone")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--shape", default="8b", choices=tuple(SHAPES), help="layer sizes (default: Qwen3-8B)")
@@ -438,6 +702,8 @@ def main() -> int:
                         "(a batch of uneven lengths), instead of --batch requests of 2,048 tokens")
     parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
                         help="run one part only (for profiler captures on a small case); the line then lacks the other parts")
+    parser.add_argument("--lean", action="store_true", help="leave out the per-kernel breakdown, the page-size point, the plain "
+                        "PyTorch baseline and the self-check")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
     args = parser.parse_args()
     globals()["PAGE_SIZE"] = args.page_size
@@ -446,6 +712,12 @@ def main() -> int:
             print("bench.py measures a single-GPU engine: run it with --gpus 1 (no multi-GPU path is built)")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.impl == "plain":
+        name, cfg = SHAPES[args.shape]
+        out = plain_baseline(cfg, args.layers or cfg["num_hidden_layers"], CONTEXT)
+        print(json.dumps({"impl": "plain", "metric": f"decode tok/s at batch 1, 2,048-token context ({name.split()[0]} bf16)",
+                          "value": out["decode_b1"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", **out}))
+        return 0
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
 

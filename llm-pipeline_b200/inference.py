@@ -175,16 +175,18 @@ class Qwen3InferenceEngine:
             while True:
                 # what the request has produced since the last look: in this call's own steps, or in the steps of
                 # another caller of the engine while this generator was not being read
-                if len(request.output) > sent:
-                    if as_text:
-                        text = self.tokenizer.decode(request.output, skip_special_tokens=True)
-                        piece, text_so_far = text[len(text_so_far):], text
-                        if piece:
-                            yield piece
-                    else:
-                        for token in request.output[sent:]:
-                            yield token
+                # (the count is taken before every yield: the caller may run the engine before it comes back)
+                if as_text and len(request.output) > sent:
                     sent = len(request.output)
+                    text = self.tokenizer.decode(request.output[:sent], skip_special_tokens=True)
+                    piece, text_so_far = text[len(text_so_far):], text
+                    if piece:
+                        yield piece
+                    continue
+                if not as_text and len(request.output) > sent:
+                    sent += 1
+                    yield request.output[sent - 1]
+                    continue
                 if request.status == "finished":
                     break
                 self.engine.step()

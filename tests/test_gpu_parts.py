@@ -452,3 +452,165 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
     H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=6)), want, 2e-4, "routed tail")
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 2e-4, "routed mixed")
     assert not runner.use_graphs and runner.graph_replays == 0   # the routed feed-forward does not declare graph_safe
+
+
+# ------------------------------------------------------------------------------------------
+# A toy mixer whose cache holds one latent vector per token (a width that is neither the hidden size nor a head
+# size), and a toy block with four norms (one before and one after each of mixer and feed-forward). Both are
+# registered from this file. The mixer attends over its own latents:
+#   c_t = x_t Wc ;  p_tj = softmax_j<=t((x_t Wq) . c_j / sqrt(L)) ;  out_t = (sum_j p_tj c_j) Wo
+# ------------------------------------------------------------------------------------------
+
+def _register_toy_latent_and_sandwich():
+    from llm_pipeline_b200.cache import TokenPagesSpec
+    from llm_pipeline_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
+                                          register_architecture)
+    from llm_pipeline_b200.parts import Block, Mixer, ResidualStream, register_block, register_mixer
+    from llm_pipeline_b200.weights import ParamSpec
+
+    @register_mixer("toy_latent_lookback")
+    class LatentLookback(Mixer):
+        def __init__(self, prefix, hidden_size, latent_size):
+            self.prefix, self.H, self.L = prefix, hidden_size, latent_size
+
+        def cache_spec(self):
+            return TokenPagesSpec((self.L,), dtype=torch.float32)       # one vector per token, float32 whatever the model computes in
+
+        def param_specs(self):
+            p = self.prefix
+            return {f"{p}.wc": ParamSpec((self.L, self.H)), f"{p}.wq": ParamSpec((self.L, self.H)), f"{p}.wo": ParamSpec((self.H, self.L))}
+
+        def load(self, get):
+            self.wc, self.wq, self.wo = (get(f"{self.prefix}.{n}", "matrix").float() for n in ("wc", "wq", "wo"))
+
+        def forward(self, x, ctx, cache):
+            page_size = cache.pages.shape[1]
+            latents = cache.pages.view(-1, self.L)                        # [pages * page_size, L]
+            c = x.float() @ self.wc.t()
+            latents[ctx.slot_mapping[cache.group].long()] = c             # this step's tokens into their page slots
+            q = x.float() @ self.wq.t()
+            out = torch.empty((x.shape[0], self.H), dtype=x.dtype, device=x.device)
+            row = 0
+            for r, (start, n) in enumerate(zip(ctx.starts, ctx.q_lens)):
+                pages = ctx.block_tables[cache.group][r, :-(-(start + n) // page_size)].long()
+                mine = cache.pages[pages].reshape(-1, self.L)[:start + n]      # every latent of the request, through its block table
+                scores = (q[row:row + n] @ mine.t()) * self.L ** -0.5
+                keys = torch.arange(start + n, device=x.device)
+                scores = scores.masked_fill(keys[None, :] > (start + torch.arange(n, device=x.device))[:, None], float("-inf"))
+                out[row:row + n] = ((torch.softmax(scores, -1) @ mine) @ self.wo.t()).to(x.dtype)
+                row += n
+            return out, None
+
+    @register_block("toy_sandwich")
+    class Sandwich(Block):
+        NORMS = ("mixer", "post_mixer", "feed_forward", "post_feed_forward")
+
+        def forward(self, stream, ctx, cache):
+            out, _ = self.mixer.forward(self.norms["mixer"].add_norm(stream, ctx), ctx, cache)
+            stream.add(self._normed(self.norms["post_mixer"], out, ctx))
+            out, _ = self.feed_forward.forward(self.norms["feed_forward"].add_norm(stream, ctx), ctx)
+            stream.add(self._normed(self.norms["post_feed_forward"], out, ctx))
+
+        @staticmethod
+        def _normed(norm, out, ctx):
+            return norm.add_norm(ResidualStream(out.float().contiguous()), ctx)      # the norm of a tensor that is no residual
+
+    class ToyLatentConfig(ModelConfig):
+        architecture = "ToyLatentForCausalLM"
+
+        def __init__(self, data):
+            self.data = data
+
+        @classmethod
+        def from_json(cls, data):
+            return cls(dict(data))
+
+        def to_json(self):
+            return dict(self.data)
+
+        def model_spec(self):
+            d = self.data
+            H, V = d["hidden_size"], d["vocab_size"]
+            norm = lambda name: PartSpec("rms_norm", {"size": H, "eps": d["eps"]}, name)  # noqa: E731
+            ff = lambda i: PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["intermediate_size"]}, f"layers.{i}.ff")  # noqa: E731
+            attn = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"],
+                                          "head_dim": d["head_dim"], "scale": d["head_dim"] ** -0.5, "qk_norm": False,
+                                          "position": "rope"}, "layers.1.attn")
+            layers = (
+                LayerSpec("toy_sandwich", PartSpec("toy_latent_lookback", {"hidden_size": H, "latent_size": d["latent_size"]}, "layers.0.mix"),
+                          ff(0), norm("layers.0.pre_mix"), norm("layers.0.pre_ff"),
+                          norms={"post_mixer": norm("layers.0.post_mix"), "post_feed_forward": norm("layers.0.post_ff")}),
+                LayerSpec("pre_norm_residual", attn, ff(1), norm("layers.1.n1"), norm("layers.1.n2")),
+            )
+            return ModelSpec("ToyLatentForCausalLM", V, H, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "embed"),
+                             {"rope": PartSpec("rotary", {"rotary_dim": d["head_dim"], "theta": 10000.0})}, layers,
+                             (ScheduleEntry(0, 0), ScheduleEntry(1, 1)), norm("final"),
+                             PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tied_to": "embed"}, "head"), 512)
+
+    register_architecture("ToyLatentForCausalLM", ToyLatentConfig)
+
+
+TOY_LATENT = {"architectures": ["ToyLatentForCausalLM"], "hidden_size": 40, "vocab_size": 89, "intermediate_size": 56, "heads": 2,
+              "kv_heads": 1, "head_dim": 16, "eps": 1e-5, "latent_size": 24}
+
+
+def toy_latent_reference(w, ids):
+    d = TOY_LATENT
+    T, L = len(ids), d["latent_size"]
+    x = w["embed.weight"][torch.tensor(ids)]
+    pos = torch.arange(T)
+    causal = pos[None, :] > pos[:, None]
+    norm = lambda t, name: plain.rms_norm(t, w[f"{name}.weight"], d["eps"])  # noqa: E731
+
+    def ff(h, i):
+        g, u = h @ w[f"layers.{i}.ff.gate_proj.weight"].t(), h @ w[f"layers.{i}.ff.up_proj.weight"].t()
+        return (torch.nn.functional.silu(g) * u) @ w[f"layers.{i}.ff.down_proj.weight"].t()
+
+    h = norm(x, "layers.0.pre_mix")
+    c, q = h @ w["layers.0.mix.wc"].t(), h @ w["layers.0.mix.wq"].t()
+    probs = torch.softmax(((q @ c.t()) * L ** -0.5).masked_fill(causal, float("-inf")), -1)
+    x = x + norm((probs @ c) @ w["layers.0.mix.wo"].t(), "layers.0.post_mix")
+    x = x + norm(ff(norm(x, "layers.0.pre_ff"), 0), "layers.0.post_ff")
+    h = norm(x, "layers.1.n1")
+    nh, nkv, hd = d["heads"], d["kv_heads"], d["head_dim"]
+    cos, sin = plain.rope_cos_sin(pos, hd, 10000.0)
+    qh = plain.apply_rope((h @ w["layers.1.attn.q_proj.weight"].t()).view(T, nh, hd).transpose(0, 1), cos, sin)
+    kh = plain.apply_rope((h @ w["layers.1.attn.k_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1), cos, sin)
+    vh = (h @ w["layers.1.attn.v_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1)
+    kh, vh = kh.repeat_interleave(nh // nkv, 0), vh.repeat_interleave(nh // nkv, 0)
+    probs = torch.softmax(((qh @ kh.transpose(1, 2)) * hd ** -0.5).masked_fill(causal[None], float("-inf")), -1)
+    x = x + (probs @ vh).transpose(0, 1).reshape(T, nh * hd) @ w["layers.1.attn.o_proj.weight"].t()
+    x = x + ff(norm(x, "layers.1.n2"), 1)
+    return norm(x, "final") @ w["embed.weight"].t()
+
+
+def test_toy_latent_cache_and_four_norm_block(tmp_path):
+    """A cache whose payload per token is a single vector of a width of its own, beside an attention layer's keys and
+    values (two groups of pages of different shapes and element types under one manager), and a block kind with four named
+    norms: registered here, built from a model folder and stepped through the unchanged step function."""
+    _register_toy_latent_and_sandwich()
+    from llm_pipeline_b200.cache import CacheManager, KVPagesSpec, TokenPagesSpec
+    from llm_pipeline_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    folder = write_random_model(TOY_LATENT, seed=31, out_dir=str(tmp_path), dtype=torch.float32, std=0.2)
+    weights = load_file(f"{folder}/model.safetensors")
+    assert {"layers.0.post_mix.weight", "layers.0.post_ff.weight", "layers.0.mix.wc"} <= set(weights)
+    runner = H.make_runner(folder, torch.float32, page_size=4, num_pages=40, max_request_tokens=256)
+    specs = runner.model.cache_specs()
+    assert isinstance(specs[0][0], TokenPagesSpec) and isinstance(specs[1][0], KVPagesSpec)
+    cache = runner.cache
+    assert len(cache.groups) == 2
+    assert tuple(cache.pages_tensor(0).shape) == (40, 4, 24) and cache.pages_tensor(0).dtype == torch.float32
+    assert tuple(cache.pages_tensor(1).shape) == (40, 2, 1, 4, 16)
+    # a page id costs what its group's payloads say: 24 float32 per token here, keys and values of one head of 16 there
+    assert CacheManager.bytes_per_page(specs, 4, torch.bfloat16) == [4 * 24 * 4, 4 * 2 * 16 * 2]
+    requests = {f"l{i}": H.random_tokens(TOY_LATENT["vocab_size"], n, 90 + i) for i, n in enumerate((37, 6, 22, 29, 14))}
+    want = {rid: toy_latent_reference(weights, ids) for rid, ids in requests.items()}
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, 1e-4, "latent whole")
+    H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=8)), want, 1e-4, "latent tail")
+    H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 1e-4, "latent mixed")
+    assert cache.pages_reused > 0 and cache.num_live == 0
+    # a block kind that is given too few norms says which are missing
+    from llm_pipeline_b200.parts import lookup
+    with pytest.raises(ValueError, match="post_mixer"):
+        lookup("block", "toy_sandwich")(None, None, object(), object())
