@@ -26,15 +26,7 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
-#include "tcgen05.cuh"
-
-#define GS_CWARPS 4
-#define GS_THREADS ((GS_CWARPS + 1) * 32)
-#define GS_MAX_RB 128
-#define GS_MAX_STAGES 24
-#define GS_SMEM_BUDGET (223 * 1024)                // ring and partial sums; 2 KB more go to alignment and over-reads
-#define GS_STAGE_LIMIT (48 * 1024)                // a stage may grow to half of this before KB stops doubling
+#include "gemm_stream.cuh"
 
 struct StreamParams {
     void* Y;
@@ -65,35 +57,6 @@ struct StreamParams {
     float* out_sumsq;
     int* error_flag;
 };
-
-__device__ __forceinline__ void gs_tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
-}
-
-__device__ __forceinline__ void gs_ldmatrix_x4(unsigned (&r)[4], const void* smem_ptr) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(smem_ptr);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-
-__device__ __forceinline__ void gs_ldmatrix_x2(unsigned (&r)[2], const void* smem_ptr) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(smem_ptr);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
-}
-
-__device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// 16 bytes of line `line` of a stage (lines of 128 bytes, counted from the stage's 1024-byte aligned start)
-// starting at 16-byte chunk `chunk`: the 128-byte swizzle exchanges the chunk index with the low bits of the line.
-__device__ __forceinline__ const unsigned char* gs_at(const unsigned char* stage, int line, int chunk) {
-    return stage + line * 128 + ((chunk ^ (line & 7)) << 4);
-}
 
 // MT: 16-row tiles of W per chunk (RB <= 16 MT). NT: 8-row tiles of X (M <= 8 NT).
 template <int MT, int NT>
@@ -236,15 +199,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                     for (int j = 0; j < NT; ++j)
                         gs_ldmatrix_x2(b[j], gs_at(stage, x_line + j * 8 + (lane & 7), chunk16 + ((lane >> 3) & 1)));
+                    // All fragments of W of this K step are asked for before the first product needs one: a warp issues in
+                    // order, so a load directly followed by the product that reads it costs the load's whole latency per tile.
+                    // Rows beyond RB in the last tile read the lines that follow (finite data of the stage or of the next
+                    // one); their sums are never stored.
+                    unsigned a[MT][4];
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                        if (mt * 16 < p.RB) gs_ldmatrix_x4(a[mt], gs_at(stage, w_line + mt * 16 + (lane & 15), chunk16 + (lane >> 4)));
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         if (mt * 16 < p.RB) {
-                            // rows beyond RB in the last tile read the lines that follow (finite data of the stage or of
-                            // the next one); their sums are never stored
-                            unsigned a[4];
-                            gs_ldmatrix_x4(a, gs_at(stage, w_line + mt * 16 + (lane & 15), chunk16 + (lane >> 4)));
 #pragma unroll
-                            for (int j = 0; j < NT; ++j) gs_mma(acc[mt][j], a, b[j][0], b[j][1]);
+                            for (int j = 0; j < NT; ++j) gs_mma(acc[mt][j], a[mt], b[j][0], b[j][1]);
                         }
                     }
                 }
@@ -377,14 +344,7 @@ int llmp_sm_count() {
     return sms;
 }
 
-// How a product is laid out: rows per block and chunk, blocks of K per stage, ring depth. False when the shape is
-// not taken.
-struct StreamPlan {
-    int per, grid, rb, nt, mt, kb, stages;
-    size_t stage_bytes, part_bytes, smem;
-};
-
-static bool stream_plan(int M, int N, int K, long ldx, long ldw, int glu_rows, StreamPlan* out) {
+bool llmp_stream_plan(int M, int N, int K, long ldx, long ldw, int glu_rows, StreamPlan* out) {
     if (!(M > 0 && M <= 64 && N > 0 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && ldw % 8 == 0)) return false;
     if (glu_rows && (N != 2 * glu_rows || M > 16)) return false;
     const int sms = llmp_sm_count();
@@ -421,7 +381,7 @@ static bool stream_plan(int M, int N, int K, long ldx, long ldw, int glu_rows, S
 // bytes' alignment.
 LLMP_API int llmp_gemm_stream_supports(int M, int N, int K, long ldx, long ldw) {
     StreamPlan q;
-    return stream_plan(M, N, K, ldx, ldw, 0, &q) ? 1 : 0;
+    return llmp_stream_plan(M, N, K, ldx, ldw, 0, &q) ? 1 : 0;
 }
 
 // X and W bfloat16, rows 16-byte aligned; out_dtype bfloat16 or float32; shapes as llmp_gemm_stream_supports says.
@@ -449,7 +409,7 @@ LLMP_API int llmp_gemm_stream(const void* X, const void* W, void* Y, int out_dty
 // Y[m, i] = silu(W[i] . X[m]) * (W[I + i] . X[m]), Y being [M, I]. M <= 16.
 LLMP_API int llmp_gemm_stream_swiglu_supports(int M, int I, int K, long ldx, long ldw) {
     StreamPlan q;
-    return stream_plan(M, 2 * I, K, ldx, ldw, I, &q) ? 1 : 0;
+    return llmp_stream_plan(M, 2 * I, K, ldx, ldw, I, &q) ? 1 : 0;
 }
 
 LLMP_API int llmp_gemm_stream_swiglu(const void* X, const void* W, void* Y, int out_dtype, int M, int I, int K, long ldx,
@@ -460,7 +420,7 @@ LLMP_API int llmp_gemm_stream_swiglu(const void* X, const void* W, void* Y, int 
 // Blocks that a product of these sizes is dealt out to (each leaves one row of out_sumsq); 0: the sizes are not taken.
 LLMP_API int llmp_gemm_stream_blocks(int M, int N, int K, long ldx, long ldw) {
     StreamPlan q;
-    return stream_plan(M, N, K, ldx, ldw, 0, &q) ? q.grid : 0;
+    return llmp_stream_plan(M, N, K, ldx, ldw, 0, &q) ? q.grid : 0;
 }
 
 // The streaming product between a norm and the residual sum, for at most 8 rows of X. Either part may be left out.
@@ -494,7 +454,7 @@ static int gemm_stream_launch(const void* X, const void* W, void* Y, int out_dty
                               long ldy, int glu_rows, const StreamExtras& extras, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     StreamPlan q;
-    LLMP_REQUIRE(stream_plan(M, N, K, ldx, ldw, glu_rows, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
+    LLMP_REQUIRE(llmp_stream_plan(M, N, K, ldx, ldw, glu_rows, &q), "gemm_stream: M=%d, N=%d, K=%d (a multiple of 64) or the row strides are not taken", M, N, K);
     LLMP_REQUIRE(((size_t)X % 16) == 0 && ((size_t)W % 16) == 0, "gemm_stream: operands must be 16-byte aligned");
     LLMP_REQUIRE(error_flag != nullptr, "gemm_stream: an error flag in device memory is required");
     StreamParams p;

@@ -14,6 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager
@@ -91,6 +92,7 @@ class ModelRunner:
         parts = list(model.parts()) if hasattr(model, "parts") else None
         self.use_graphs = bool(use_graphs and parts is not None and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self._staging: list = []             # pinned buffers for the index arrays of eager steps: (tensor, numpy view, event)
         self.graph_replays = 0
         self._context_limit = model.captured_context_limit() if hasattr(model, "captured_context_limit") else None
 
@@ -109,10 +111,15 @@ class ModelRunner:
                 n = len(e.tokens)
                 if n == 0:
                     raise ValueError(f"request {e.req_id!r} brings no tokens")
-                for t in e.tokens:
-                    if not 0 <= int(t) < self.vocab_size:
-                        raise ValueError(f"token id {t} of request {e.req_id!r} is outside the vocabulary "
-                                         f"of {self.vocab_size}")
+                if n > 16:
+                    ids = np.asarray(e.tokens)
+                    bad = (ids < 0) | (ids >= self.vocab_size)
+                    outside = [int(ids[int(bad.argmax())])] if bad.any() else []
+                else:
+                    outside = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+                if outside:
+                    raise ValueError(f"token id {outside[0]} of request {e.req_id!r} is outside the vocabulary "
+                                     f"of {self.vocab_size}")
                 for w in e.want:
                     if not 0 <= int(w) < n:
                         raise ValueError(f"request {e.req_id!r} wants logits at place {w} of {n} tokens")
@@ -138,63 +145,99 @@ class ModelRunner:
             assert ok
 
     # -- the step's index arrays ---------------------------------------------------------------
-    def _fill(self, ctx: StepContext, entries: Sequence[StepEntry], width: Optional[int] = None) -> List[int]:
+    def _fill(self, ctx: StepContext, entries: Sequence[StepEntry], width: Optional[int] = None) -> np.ndarray:
         """Host side of the context, and the flat int32 image of its device arrays:
         token ids, positions, request of each token, q_start, ctx_len, slots, logit rows, then per
-        cache group the slot mapping and the block tables (``width`` entries per request)."""
+        cache group the slot mapping and the block tables (``width`` entries per request). Long runs of
+        tokens (prompt portions) are filled as arrays, single tokens as scalars."""
         cache = self.cache
         ps = cache.page_size
-        token_ids: List[int] = []
-        positions: List[int] = []
-        token_request: List[int] = []
-        q_start = [0]
-        ctx_len, slots, rows = [], [], []
-        ctx.req_ids, ctx.starts, ctx.q_lens = [], [], []
-        for r, e in enumerate(entries):
-            start, n = cache.length(e.req_id), len(e.tokens)
-            ctx.req_ids.append(e.req_id)
-            ctx.starts.append(start)
-            ctx.q_lens.append(n)
-            token_ids.extend(int(t) for t in e.tokens)
-            positions.extend(range(start, start + n))
-            token_request.extend([r] * n)
-            rows.extend(q_start[-1] + int(w) for w in e.want)
-            q_start.append(q_start[-1] + n)
-            ctx_len.append(start + n)
-            slots.append(cache.slot_of(e.req_id))
-        ctx.num_tokens, ctx.num_requests = q_start[-1], len(entries)
-        ctx.max_q_len = max(ctx.q_lens)
+        R = len(entries)
+        starts = [cache.length(e.req_id) for e in entries]
+        q_lens = [len(e.tokens) for e in entries]
+        ctx_len = [s + n for s, n in zip(starts, q_lens)]
+        ctx.req_ids, ctx.starts, ctx.q_lens = [e.req_id for e in entries], starts, q_lens
+        first = [0] * (R + 1)
+        for r, n in enumerate(q_lens):
+            first[r + 1] = first[r] + n
+        N = first[R]
+        rows = [first[r] + int(w) for r, e in enumerate(entries) for w in e.want]
+        ctx.num_tokens, ctx.num_requests = N, R
+        ctx.max_q_len = max(q_lens)
         ctx.max_ctx_len = max(ctx_len)
         ctx.total_ctx = sum(ctx_len)
         lead = 0
-        while lead < len(ctx.q_lens) and ctx.q_lens[lead] == 1:
+        while lead < R and q_lens[lead] == 1:
             lead += 1
-        ctx.leading_single = lead if lead < len(ctx.q_lens) else 0       # a step of single tokens only is a decode step
+        ctx.leading_single = lead if lead < R else 0                     # a step of single tokens only is a decode step
         if ctx.leading_single:
             ctx.leading_longest, ctx.leading_keys = max(ctx_len[:lead]), sum(ctx_len[:lead])
         ctx.num_logit_rows = len(rows)
         if width is None:
             width = max(1, -(-ctx.max_ctx_len // ps))
         ctx.table_width = width
-        flat: List[int] = token_ids + positions + token_request + q_start + ctx_len + slots + rows
-        for g in range(len(cache.groups)):
-            mapping: List[int] = []
-            tables: List[int] = []
+        groups = len(cache.groups)
+        head = 3 * N + (R + 1) + 2 * R + len(rows)
+        flat = np.empty(head + groups * (N + R * width), dtype=np.int32)
+        token_ids, positions, token_request = flat[0:N], flat[N:2 * N], flat[2 * N:3 * N]
+        for r, e in enumerate(entries):
+            at, n, start = first[r], q_lens[r], starts[r]
+            if n == 1:
+                token_ids[at], positions[at], token_request[at] = e.tokens[0], start, r
+            else:
+                token_ids[at:at + n] = e.tokens
+                positions[at:at + n] = np.arange(start, start + n, dtype=np.int32)
+                token_request[at:at + n] = r
+        cursor = 3 * N
+        flat[cursor:cursor + R + 1] = first
+        cursor += R + 1
+        flat[cursor:cursor + R] = ctx_len
+        cursor += R
+        flat[cursor:cursor + R] = [cache.slot_of(e.req_id) for e in entries]
+        cursor += R
+        flat[cursor:cursor + len(rows)] = rows
+        cursor += len(rows)
+        for g in range(groups):
+            mapping = flat[cursor:cursor + N]
+            tables = flat[cursor + N:cursor + N + R * width].reshape(R, width)
+            tables.fill(-1)
             for r, e in enumerate(entries):
                 table = cache.block_table(e.req_id, g)
-                start, n = ctx.starts[r], ctx.q_lens[r]
+                at, n, start = first[r], q_lens[r], starts[r]
                 if n == 1:
                     page = table[start // ps]
-                    mapping.append(-1 if page < 0 else page * ps + start % ps)
+                    mapping[at] = -1 if page < 0 else page * ps + start % ps
                 else:
-                    for pos in range(start, start + n):
-                        page = table[pos // ps]
-                        mapping.append(-1 if page < 0 else page * ps + pos % ps)
-                tables.extend(table[:width])
-                tables.extend([-1] * (width - min(width, len(table))))
-            flat += mapping
-            flat += tables
+                    pos = positions[at:at + n]
+                    page = np.asarray(table, dtype=np.int32)[pos // ps]
+                    mapping[at:at + n] = np.where(page < 0, -1, page * ps + pos % ps)
+                k = min(width, len(table))
+                tables[r, :k] = table[:k]
+            cursor += N + R * width
         return flat
+
+    def _to_device(self, flat: np.ndarray) -> torch.Tensor:
+        """The step's index arrays on the device: through one of a few pinned staging buffers that are reused once
+        the copy out of them has completed (no pinned allocation per step), one asynchronous copy."""
+        n = flat.size
+        chosen = None
+        for buffer in self._staging:
+            if buffer[0].numel() >= n and buffer[2].query():
+                chosen = buffer
+                break
+        if chosen is None:
+            if len(self._staging) >= 4:
+                self._staging.pop(0)
+            host = torch.empty(max(4096, 2 * n), dtype=torch.int32).pin_memory()
+            chosen = (host, host.numpy(), torch.cuda.Event())
+            self._staging.append(chosen)
+        host, view, copied = chosen
+        view[:n] = flat
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        dev.copy_(host[:n], non_blocking=True)
+        copied.record()
+        self.last_h2d_bytes = n * 4
+        return dev
 
     def _bind(self, ctx: StepContext, dev: torch.Tensor) -> None:
         """Point the context's device arrays at their places in the flat buffer."""
@@ -236,11 +279,7 @@ class ModelRunner:
 
     def _prepare_reserved(self, entries: Sequence[StepEntry]) -> StepContext:
         ctx = StepContext(self.device, self.dtype)
-        flat = self._fill(ctx, entries)
-        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        self.last_h2d_bytes = host.numel() * 4
-        self._bind(ctx, dev)
+        self._bind(ctx, self._to_device(self._fill(ctx, entries)))
         return ctx
 
     def _run(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -271,16 +310,12 @@ class ModelRunner:
         slot.seen += 1
         if slot.seen == 1:
             # first step of this shape: run eagerly (this also lets libraries set themselves up)
-            ctx = StepContext(self.device, self.dtype)
-            flat = self._fill(ctx, entries)
-            host = torch.tensor(flat, dtype=torch.int32).pin_memory()
-            self.last_h2d_bytes = host.numel() * 4
-            self._bind(ctx, host.to(self.device, non_blocking=True))
+            ctx = self._prepare_reserved(entries)
             return self._finish(ctx, entries, self._run(ctx))
         if slot.graph is None:
             slot.ctx = StepContext(self.device, self.dtype)
             flat = self._fill(slot.ctx, entries, width)
-            slot.host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+            slot.host = torch.from_numpy(flat).pin_memory()
             slot.host_np = slot.host.numpy()
             self._remember(slot, entries)
             slot.dev = slot.host.to(self.device)
@@ -301,7 +336,7 @@ class ModelRunner:
                 self._refill(slot, entries, width)
             else:
                 flat = self._fill(slot.ctx, entries, width)
-                slot.host_np[:len(flat)] = flat
+                slot.host_np[:flat.size] = flat
                 self._remember(slot, entries)
             slot.dev.copy_(slot.host, non_blocking=True)
         slot.copied.record()

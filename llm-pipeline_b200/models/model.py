@@ -12,6 +12,7 @@ import torch
 
 from ..cache.spec import PagesSpec, StateSpec
 from ..config.base import ModelSpec, PartSpec
+from ..ops.linear import begin_step
 from ..parts import LayerCache, ResidualStream, lookup
 from ..weights.source import (ParamSpec, WeightSource, check_names_and_shapes, stored_dtype_policy)
 
@@ -115,6 +116,7 @@ class Model:
     def forward(self, ctx, caches) -> ResidualStream:
         """Run every scheduled layer on the step's tokens. ``caches.view(cache_id, writes)`` gives
         the ``LayerCache`` of an execution."""
+        begin_step()
         ctx.position_tables = {name: part.tables(ctx) for name, part in self.positions.items()}
         stream = ResidualStream(self.embedding.forward(ctx))
         for index, entry in enumerate(self.schedule):

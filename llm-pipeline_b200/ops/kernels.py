@@ -55,6 +55,7 @@ _SIGNATURES = {
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_bounded_wait_check": [_P, _I, _P, _P],
+    "llmp_gemm_stream_chain": [_P, _I, _I, _P, _P, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -401,6 +402,80 @@ def gemm_stream_fused(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tens
           _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
           dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), xw.stride(0) if xw is not None else 0,
           _ptr(out_sumsq), error_flag().data_ptr(), _stream())
+
+
+class ChainPhase(ctypes.Structure):
+    """One product of ``gemm_stream_chain`` as the library reads it (``LlmpChainPhase`` in csrc/gemm_stream_chain.cu)."""
+
+    _fields_ = [("X", _P), ("W", _P), ("Y", _P), ("ldx", _L), ("ldw", _L), ("ldy", _L),
+                ("N", _I), ("K", _I), ("out_dtype", _I), ("glu_rows", _I),
+                ("in_sumsq", _P), ("in_parts", _I), ("in_inv_width", _F), ("in_eps", _F),
+                ("residual", _P), ("ldr", _L), ("norm_w", _P), ("norm_w_dtype", _I),
+                ("xw", _P), ("ldxw", _L), ("out_sumsq", _P)]
+
+
+def chain_phase(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], *, glu: bool = False,
+                in_sumsq: Optional[torch.Tensor] = None, in_parts: int = 0, in_width: int = 0, in_eps: float = 0.0,
+                residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                xw: Optional[torch.Tensor] = None, out_sumsq: Optional[torch.Tensor] = None) -> ChainPhase:
+    """A phase of a chain, with the arguments of ``gemm_stream_fused``."""
+    K = x.shape[1]
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == K,
+          "a chain takes row-major bfloat16 operands that match")
+    phase = ChainPhase()
+    phase.X, phase.W, phase.Y = _ptr(x), _ptr(w), _ptr(out)
+    phase.ldx, phase.ldw, phase.ldy = x.stride(0), w.stride(0), out.stride(0) if out is not None else 0
+    phase.N, phase.K, phase.out_dtype = N, K, dtype_code(out.dtype) if out is not None else BF16
+    phase.glu_rows = N // 2 if glu else 0
+    phase.in_sumsq, phase.in_parts = _ptr(in_sumsq), int(in_parts)
+    phase.in_inv_width, phase.in_eps = (1.0 / in_width if in_width else 0.0), float(in_eps)
+    phase.residual, phase.ldr = _ptr(residual), residual.stride(0) if residual is not None else 0
+    phase.norm_w = _ptr(norm_weight)
+    phase.norm_w_dtype = dtype_code(norm_weight.dtype) if norm_weight is not None else F32
+    phase.xw, phase.ldxw = _ptr(xw), xw.stride(0) if xw is not None else 0
+    phase.out_sumsq = _ptr(out_sumsq)
+    return phase
+
+
+_chain_counters: dict = {}
+_chain_max_phases: Optional[int] = None
+
+
+def gemm_stream_chain_max_phases() -> int:
+    global _chain_max_phases
+    if _chain_max_phases is None:
+        fn = library().llmp_gemm_stream_chain_max_phases
+        fn.argtypes = []
+        fn.restype = _I
+        _chain_max_phases = int(fn())
+    return _chain_max_phases
+
+
+def gemm_stream_chain_supports(phases: Sequence[ChainPhase], M: int) -> bool:
+    fn = library().llmp_gemm_stream_chain_supports
+    fn.argtypes = [_P, _I, _I]
+    fn.restype = _I
+    array = (ChainPhase * len(phases))(*phases)
+    return bool(fn(ctypes.cast(array, _P), len(phases), M))
+
+
+def gemm_stream_chain(phases: Sequence[ChainPhase], M: int, device: torch.device) -> None:
+    """The products of ``phases`` (at most 8 rows of X each, every phase reading what the phase before wrote) in one
+    persistent cooperative launch whose ring of weight boxes never drains between them; the results are those of
+    ``gemm_stream_fused`` called phase by phase, bit for bit. The blocks tell each other through counters in global
+    memory that a phase is complete; one set per device, so chains on a device must follow one another in one stream."""
+    key = torch.device(device).index or 0
+    counters = _chain_counters.get(key)
+    if counters is None:
+        _need(not torch.cuda.is_current_stream_capturing(), "the chain's counters must exist before a graph is captured")
+        fn = library().llmp_gemm_stream_chain_counters
+        fn.argtypes = []
+        fn.restype = _I
+        counters = _chain_counters[key] = torch.zeros(int(fn()), dtype=torch.int32, device=device)
+    array = (ChainPhase * len(phases))(*phases)
+    _call("llmp_gemm_stream_chain", ctypes.cast(array, _P), len(phases), int(M), _ptr(counters), error_flag().data_ptr(),
+          _stream())
 
 
 def gemm_stream_swiglu_supports(M: int, I: int, K: int, ldx: int, ldw: int) -> bool:

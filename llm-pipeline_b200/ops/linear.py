@@ -37,13 +37,100 @@ FUSE_NORM = os.environ.get("LLMP_B200_FUSE_NORM", "1") == "1"
 
 class PendingProduct:
     """``x @ weight^T`` that has not been taken yet. A norm that can fold the product into its own work asks for
-    ``x`` and ``weight``; everybody else calls ``value()``."""
+    ``x`` (a tensor, or ``LazyRows``) and ``weight``; everybody else calls ``value()``."""
 
-    def __init__(self, x: torch.Tensor, weight: torch.Tensor):
+    def __init__(self, x, weight: torch.Tensor):
         self.x, self.weight = x, weight
 
     def value(self) -> torch.Tensor:
         return linear(self.x, self.weight)
+
+
+# ---- several products of a decode step in one launch ------------------------------------------------------------
+# The products of a decode step of at most 8 rows follow one another, each needing the whole result of the one before:
+# o -> (residual, norm) -> gate/up with SwiGLU -> down -> (residual, norm) -> the next layer's qkv. Launched one by one,
+# each drains its ring of weight boxes and the next fills its own again. ``kernels.gemm_stream_chain`` runs up to four
+# of them as phases of one persistent launch whose ring never drains. The parts do not know of it: the functions below
+# (``residual_product``, ``gate_up_swiglu``, ``pending_product``, ``linear``) do not launch a product whose only
+# reader will be the next of them, but note it in the open chain and hand out a handle (``ScaledRows`` or ``LazyRows``
+# with ``chain`` set); a product whose result leaves as a tensor ends the chain and launches it. Whoever needs a tensor
+# from a handle calls ``value()``, which launches what is noted first. A chain gives the same bits as its products
+# launched one by one. It is off unless LLMP_B200_CHAIN=1: measured on a B200 (Qwen3-8B shape, batch 8) a step through
+# chains takes 4.55 ms against 3.63 ms, because as dependent launches the separate products already fill their rings
+# while the kernel before them ends, each with a ring of its own stage size (see csrc/gemm_stream_chain.cu).
+CHAIN = os.environ.get("LLMP_B200_CHAIN", "0") == "1"
+
+
+class _Chain:
+    def __init__(self, rows: int, device: torch.device):
+        self.rows, self.device = rows, device
+        self.noted = []                 # (x tensor, weight, out tensor or None, keyword arguments of gemm_stream_fused)
+        self.launched = False
+
+    def has_room(self) -> bool:
+        return not self.launched and len(self.noted) < kernels.gemm_stream_chain_max_phases()
+
+    def note(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor], **extras) -> None:
+        self.noted.append((x, weight, out, extras))
+
+    def launch(self) -> None:
+        global _open_chain
+        if self.launched:
+            return
+        self.launched = True
+        if _open_chain is self:
+            _open_chain = None
+        if len(self.noted) == 1:
+            x, weight, out, extras = self.noted[0]
+            kernels.gemm_stream_fused(x, weight, out, **extras)
+        elif self.noted:
+            kernels.gemm_stream_chain([kernels.chain_phase(x, weight, out, **extras) for x, weight, out, extras in self.noted],
+                                      self.rows, self.device)
+        self.noted = []
+
+
+_open_chain: Optional[_Chain] = None
+_chain_shapes: dict = {}                # (rows, shapes of the phases) -> whether they run as one chain
+
+
+def begin_step() -> None:
+    """A step begins: a chain that an abandoned step left open is dropped (nobody waits for its results)."""
+    global _open_chain
+    _open_chain = None
+
+
+def _chain_takes(chain: _Chain, x: torch.Tensor, weight: torch.Tensor, glu: bool) -> bool:
+    """Whether the open chain can take one more product of these sizes (the plans of all its phases fit one ring)."""
+    if not chain.has_room():
+        return False
+    shapes = tuple((w.shape[0], w.shape[1], a.stride(0), w.stride(0), bool(e.get("glu", False))) for a, w, _o, e in chain.noted)
+    shapes += ((weight.shape[0], weight.shape[1], x.stride(0), weight.stride(0), glu),)
+    key = (chain.rows, shapes)
+    ok = _chain_shapes.get(key)
+    if ok is None:
+        phases = []
+        for N, K, ldx, ldw, g in shapes:
+            phase = kernels.ChainPhase()
+            phase.N, phase.K, phase.ldx, phase.ldw, phase.glu_rows = N, K, ldx, ldw, (N // 2 if g else 0)
+            phases.append(phase)
+        ok = _chain_shapes[key] = kernels.gemm_stream_chain_supports(phases, chain.rows)
+    return ok
+
+
+class LazyRows:
+    """Rows [M, width] that a product noted in an open chain will write: ``values`` is their tensor, valid once the
+    chain is launched. ``linear()`` and ``pending_product()`` take the handle; everybody else calls ``value()``."""
+
+    def __init__(self, values: torch.Tensor, chain: _Chain):
+        self.values, self.chain = values, chain
+
+    shape = property(lambda self: self.values.shape)
+    dtype = property(lambda self: self.values.dtype)
+    device = property(lambda self: self.values.device)
+
+    def value(self) -> torch.Tensor:
+        self.chain.launch()
+        return self.values
 
 
 class ScaledRows:
@@ -51,10 +138,12 @@ class ScaledRows:
     rsqrt(sum(sumsq[:parts, m]) / width + eps). A product that can apply the factors to its result takes the fields;
     everybody else calls ``value()``, which has ``materialise`` (given by whoever made the rows) build the finished rows."""
 
-    def __init__(self, values: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float, materialise: Callable[[], torch.Tensor]):
+    def __init__(self, values: torch.Tensor, sumsq: torch.Tensor, parts: int, eps: float, materialise: Callable[[], torch.Tensor],
+                 chain: Optional[_Chain] = None):
         self.values, self.sumsq, self.parts, self.eps = values, sumsq, int(parts), float(eps)
         self._materialise = materialise
         self._value: Optional[torch.Tensor] = None
+        self.chain = chain              # set while the product that writes ``values`` and ``sumsq`` is only noted in a chain
 
     shape = property(lambda self: self.values.shape)
     dtype = property(lambda self: self.values.dtype)
@@ -62,6 +151,8 @@ class ScaledRows:
 
     def value(self) -> torch.Tensor:
         if self._value is None:
+            if self.chain is not None:
+                self.chain.launch()
             self._value = self._materialise()
         return self._value
 
@@ -70,9 +161,10 @@ def pending_product(x: torch.Tensor, weight: torch.Tensor):
     """``x @ weight^T`` as a PendingProduct where a following norm could fold it in (the sizes of the streaming
     product for at most 8 bfloat16 rows), else the product itself."""
     M, K = x.shape
-    if (FUSE_NORM and STREAM_GEMM and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and 0 < M <= 8 and
-            x.stride(1) == 1 and weight.stride(1) == 1 and not x.data_ptr() % 16 and not weight.data_ptr() % 16 and
-            kernels.gemm_stream_blocks(M, weight.shape[0], K, x.stride(0), weight.stride(0)) > 0):
+    rows = x.values if isinstance(x, LazyRows) else x
+    if (FUSE_NORM and STREAM_GEMM and isinstance(rows, torch.Tensor) and rows.dtype == torch.bfloat16 and 0 < M <= 8 and
+            rows.stride(1) == 1 and weight.stride(1) == 1 and not rows.data_ptr() % 16 and not weight.data_ptr() % 16 and
+            kernels.gemm_stream_blocks(M, weight.shape[0], K, rows.stride(0), weight.stride(0)) > 0):
         return PendingProduct(x, weight)
     return linear(x, weight)
 
@@ -80,11 +172,26 @@ def pending_product(x: torch.Tensor, weight: torch.Tensor):
 def residual_product(product: PendingProduct, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
                      materialise: Callable[[], torch.Tensor]) -> ScaledRows:
     """residual += product; returns residual * norm_weight with the rows' factors still to be applied."""
+    global _open_chain
     x, weight = product.x, product.weight
     M, N = x.shape[0], weight.shape[0]
+    chain = None
+    if isinstance(x, LazyRows):
+        # the rows come out of the open chain: one more phase of it, if it takes one
+        if CHAIN and x.chain is _open_chain and _chain_takes(x.chain, x.values, weight, False):
+            chain, x = x.chain, x.values
+        else:
+            x = x.value()
+    elif CHAIN:
+        if _open_chain is not None:
+            _open_chain.launch()
+        chain = _open_chain = _Chain(M, x.device)
     blocks = kernels.gemm_stream_blocks(M, N, x.shape[1], x.stride(0), weight.stride(0))
     xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     sumsq = torch.empty((blocks, 8), dtype=torch.float32, device=x.device)
+    if chain is not None:
+        chain.note(x, weight, None, residual=residual, norm_weight=norm_weight, xw=xw, out_sumsq=sumsq)
+        return ScaledRows(xw, sumsq, blocks, eps, materialise, chain)
     kernels.gemm_stream_fused(x, weight, None, residual=residual, norm_weight=norm_weight, xw=xw, out_sumsq=sumsq)
     return ScaledRows(xw, sumsq, blocks, eps, materialise)
 
@@ -101,6 +208,15 @@ def _scaled_stream(x: ScaledRows, weight: torch.Tensor, glu: bool) -> Optional[t
     elif not kernels.gemm_stream_supports(M, N, K, values.stride(0), weight.stride(0)):
         return None
     out = torch.empty((M, N // 2 if glu else N), dtype=values.dtype, device=values.device)
+    chain = x.chain
+    if chain is not None and chain is _open_chain and _chain_takes(chain, values, weight, glu):
+        chain.note(values, weight, out, glu=glu, in_sumsq=x.sumsq, in_parts=x.parts, in_width=K, in_eps=x.eps)
+        if glu:
+            return LazyRows(out, chain)         # its reader is the next product
+        chain.launch()                          # plain rows leave as a tensor: the chain ends here
+        return out
+    if chain is not None:
+        chain.launch()
     kernels.gemm_stream_fused(values, weight, out, glu=glu, in_sumsq=x.sumsq, in_parts=x.parts, in_width=K, in_eps=x.eps)
     return out
 
@@ -236,7 +352,16 @@ register_bf16_kernel(_tensor_memory_prefill)
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type). ``x`` may be ScaledRows."""
+    """x [M, K], weight [N, K] -> [M, N] in ``out_dtype`` (default: x's type). ``x`` may be ScaledRows or LazyRows."""
+    if isinstance(x, LazyRows):
+        chain, values = x.chain, x.values
+        if (bias is None and out_dtype in (None, values.dtype) and chain is _open_chain and weight.stride(1) == 1 and
+                not weight.data_ptr() % 16 and _chain_takes(chain, values, weight, False)):
+            out = torch.empty((values.shape[0], weight.shape[0]), dtype=values.dtype, device=values.device)
+            chain.note(values, weight, out)
+            chain.launch()
+            return out
+        x = x.value()
     if isinstance(x, ScaledRows):
         if bias is None and out_dtype in (None, x.dtype):
             out = _scaled_stream(x, weight, glu=False)

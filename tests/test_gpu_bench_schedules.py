@@ -95,7 +95,7 @@ def recorded_kernels(log):
     weight rows or None, uneven or None) while the block runs."""
     from llm_pipeline_b200.ops import kernels
     names = ("gemm_stream", "gemm_stream_fused", "gemm_stream_swiglu", "gemm_stream_tc", "gemm_tc", "gemm_skinny",
-             "gemm_simt", "decode_attention")
+             "gemm_simt", "decode_attention", "gemm_stream_chain")
     saved = {name: getattr(kernels, name) for name in names}
     library_mm = torch.mm
 
@@ -103,6 +103,8 @@ def recorded_kernels(log):
         def call(*args, **kwargs):
             if name == "decode_attention":
                 log.append((name, args[2].shape[0], None, bool(kwargs.get("uneven", False))))
+            elif name == "gemm_stream_chain":
+                log.append((name, args[1], len(args[0]), None))          # rows, phases
             else:
                 log.append((name, args[0].shape[0], args[1].shape[0], None))
             return fn(*args, **kwargs)
@@ -257,3 +259,29 @@ def test_logits_do_not_depend_on_the_company(case, dtype):
               f"alone against the oracle {float(noise.abs().max()):.3e} and {float(noise.pow(2).mean().sqrt()):.3e}; largest logit {largest:.2f}")
         assert float(diff.abs().max()) <= float(noise.abs().max()), name
         assert float(diff.pow(2).mean().sqrt()) <= 1.5 * float(noise.pow(2).mean().sqrt()), name
+
+
+def test_products_of_a_decode_step_as_one_chain_give_the_same_bits(case, monkeypatch):
+    """The optional path that runs the products between two attentions as phases of one persistent launch
+    (``ops.linear.CHAIN``): the same logits, bit for bit, as the products launched one by one, eagerly and replayed."""
+    from llm_pipeline_b200.engine import StepEntry
+    import importlib
+    linear = importlib.import_module("llm_pipeline_b200.ops.linear")      # (the package also exports the function of that name)
+    contexts, tokens = case["contexts"], case["tokens"]
+    got = {}
+    for chained in (False, True):
+        monkeypatch.setattr(linear, "CHAIN", chained)
+        runner = runner_for(case, torch.bfloat16, num_pages=512, max_requests=8)
+        for i in range(1, 8):
+            prefill(runner, i, tokens[i][:contexts[i]])
+        rows, log = [], []
+        with recorded_kernels(log):
+            for s in range(3):
+                rows.append(runner.step([StepEntry(i, [tokens[i][contexts[i] + s]], [0]) for i in range(1, 8)]).clone())
+        got[chained] = torch.stack(rows)
+        chains = [entry for entry in log if entry[0] == "gemm_stream_chain"]
+        assert (len(chains) > 0) == chained
+        if chained:
+            assert ("gemm_stream_chain", 7, 4, None) in log and ("gemm_stream_chain", 7, 3, None) in log     # the last layer's: three
+        del runner
+    assert torch.equal(got[False], got[True])

@@ -587,3 +587,67 @@ def test_a_wait_that_runs_out_reaches_the_host_and_the_next_launch_works():
     assert torch.allclose(out, x.float() @ w.float().t(), atol=1e-3, rtol=1e-3)
     with pytest.raises(KernelError):
         k.bounded_wait_check(limit=0)
+
+
+@pytest.mark.parametrize("M,H,Q,I,QKV", [(8, 4096, 4096, 12288, 6144), (1, 1024, 2048, 3072, 4096), (5, 5120, 8192, 25600, 10240),
+                                         (3, 192, 128, 320, 384), (8, 4096, 4096, 12288, 0)])
+def test_gemm_stream_chain_gives_the_bits_of_its_products(M, H, Q, I, QKV):
+    """Output projection (into the residual, next norm folded in) -> gate/up with SwiGLU -> down projection (into the
+    residual) -> the next q/k/v projection as phases of one persistent launch, against the same four products launched
+    one by one: the same bits everywhere, and the plain float32 reference within rounding. QKV = 0: three phases, the
+    last one with plain rows."""
+    k = K()
+    attn = rnd(M, Q, dtype=torch.bfloat16, seed=1)
+    w_o, w_gu = rnd(H, Q, dtype=torch.bfloat16, seed=2, scale=0.05), rnd(2 * I, H, dtype=torch.bfloat16, seed=3, scale=0.05)
+    w_d = rnd(H, I, dtype=torch.bfloat16, seed=4, scale=0.05)
+    w_qkv = rnd(QKV, H, dtype=torch.bfloat16, seed=5, scale=0.05) if QKV else None
+    n1, n2 = (1 + 0.1 * rnd(H, seed=6)), (1 + 0.1 * rnd(H, seed=7))
+    residual0 = rnd(M, H, seed=8)
+    eps = 1e-6
+
+    def run(chained):
+        residual = residual0.clone()
+        blocks = k.gemm_stream_blocks(M, H, Q, Q, Q)
+        blocks_d = k.gemm_stream_blocks(M, H, I, I, I)
+        xw1, ss1 = torch.empty(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(blocks, 8, device=DEV)
+        act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        xw2, ss2 = torch.empty(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(blocks_d, 8, device=DEV)
+        last = torch.empty(M, QKV, dtype=torch.bfloat16, device=DEV) if QKV else torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        calls = [(attn, w_o, None, dict(residual=residual, norm_weight=n1, xw=xw1, out_sumsq=ss1)),
+                 (xw1, w_gu, act, dict(glu=True, in_sumsq=ss1, in_parts=blocks, in_width=H, in_eps=eps))]
+        if QKV:
+            calls += [(act, w_d, None, dict(residual=residual, norm_weight=n2, xw=xw2, out_sumsq=ss2)),
+                      (xw2, w_qkv, last, dict(in_sumsq=ss2, in_parts=blocks_d, in_width=H, in_eps=eps))]
+        else:
+            calls += [(act, w_d, last, {})]
+        if chained:
+            phases = [k.chain_phase(x, w, out, **extras) for x, w, out, extras in calls]
+            assert k.gemm_stream_chain_supports(phases, M)
+            k.gemm_stream_chain(phases, M, torch.device(DEV))
+        else:
+            for x, w, out, extras in calls:
+                k.gemm_stream_fused(x, w, out, **extras)
+        torch.cuda.synchronize()
+        k.check_error_flag()
+        return residual, xw1, ss1, act, xw2, ss2, last
+
+    one_by_one = run(False)
+    for attempt in range(3):                                    # the counters of the chain are left zero: launch after launch
+        chained = run(True)
+        for name, a, b in zip(("residual", "xw1", "sumsq1", "act", "xw2", "sumsq2", "last"), one_by_one, chained):
+            if QKV or name not in ("xw2", "sumsq2"):
+                assert torch.equal(a, b), (name, attempt, float((a.float() - b.float()).abs().max()))
+    # and the whole against plain float32 arithmetic on the same bfloat16 operands
+    r1 = residual0 + attn.float() @ w_o.float().t()
+    x1 = plain.rms_norm(r1, n1, eps)
+    gu = x1 @ w_gu.float().t()
+    a_ref = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    d_ref = a_ref @ w_d.float().t()
+    assert torch.allclose(chained[3].float(), a_ref, atol=3e-2 * float(a_ref.abs().max()), rtol=3e-2)
+    if QKV:
+        r2 = r1 + d_ref
+        q_ref = plain.rms_norm(r2, n2, eps) @ w_qkv.float().t()
+        assert torch.allclose(chained[0], r2, atol=3e-2 * float(r2.abs().max()))
+        assert torch.allclose(chained[6].float(), q_ref, atol=4e-2 * float(q_ref.abs().max()))
+    else:
+        assert torch.allclose(chained[6].float(), d_ref, atol=3e-2 * float(d_ref.abs().max()))

@@ -70,19 +70,23 @@ def test_random_configuration_with_widths_in_multiples_of_64(tmp_path, seed):
     longest = max(len(t) for t in requests.values())
     runner = H.make_runner(folder, dtype, page_size=page, num_pages=4 * (-(-longest // page)))
     from llm_pipeline_b200.ops import kernels
-    folded, launch = [], kernels.gemm_stream_fused
+    folded, launch, launch_chain = [], kernels.gemm_stream_fused, kernels.gemm_stream_chain
 
     def counting(*args, **kwargs):
         folded.append(1)
         return launch(*args, **kwargs)
 
-    kernels.gemm_stream_fused = counting
+    def counting_chain(*args, **kwargs):
+        folded.append(len(args[0]))
+        return launch_chain(*args, **kwargs)
+
+    kernels.gemm_stream_fused, kernels.gemm_stream_chain = counting, counting_chain
     try:
         H.assert_close(H.replay(runner, H.cut_portions(requests, (1,))), want, H.TOL[dtype], f"token by token ({config})")
         H.assert_close(H.replay(runner, H.cut_portions(requests, (3, 8, 2, 9))), want, H.TOL[dtype], f"portions ({config})")
         H.assert_close(H.replay(runner, H.cut_mixed(requests, (2, 3, 5, 16), max_live=4)), want, H.TOL[dtype], f"mixed ({config})")
     finally:
-        kernels.gemm_stream_fused = launch
+        kernels.gemm_stream_fused, kernels.gemm_stream_chain = launch, launch_chain
     # a product with a bias is not handed to the norm, and the last layer's goes to the final norm as a tensor
     assert folded or (config["attention_bias"] and config["num_hidden_layers"] == 1)
     assert runner.cache.num_live == 0
