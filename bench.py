@@ -10,7 +10,8 @@ for every request of the batch, from the embedding to the sampled token id. It p
 through the Python entry point (``GenerationEngine.step``: host token lists in, host token ids out,
 the index arrays copied from pinned memory every step); ``prefill`` is one 2,048-token prompt in one
 step; ``roofline`` is the decode step against the bytes it must read; ``points`` are decode at batch
-1 and 64 and at batch 8 with pages of 32 tokens. ``breakdown`` gives, for one decode step of the batch
+1 and 64, at batch 8 with pages of 32 tokens, and two further sizes at their full depth (the Qwen3-0.6B shape under a
+continuous-batching mix of 64 requests, decode at batch 8 at the Qwen3-32B shape). ``breakdown`` gives, for one decode step of the batch
 and for the prefill step, the device time of every kernel class (CUDA events around every launch of
 an eager step that is queued behind a sleeping kernel, so that launches do not wait for the host) with
 the achieved GB/s of the weight-streaming products and the decode attention and the TFLOP/s of the
@@ -494,15 +495,13 @@ def selfcheck(cfg, batches=(8, 64), prompt_tokens=48, new_tokens=4):
     return report
 
 
-def run_mix(args):
+def mix_workload(cfg, layers):
     """A continuous-batching mix through the Python entry point: 64 requests with prompt lengths uniform in
-    [16, 2048] and 128 decoded tokens each (seeded), context up to 4,096; reports total tokens per second."""
+    [16, 2048] and 128 decoded tokens each (seeded), context up to 4,096; returns its figures."""
     import torch
 
     from llm_pipeline_b200.sampling import SamplingConfig
 
-    name, cfg = SHAPES[args.shape]
-    layers = args.layers or cfg["num_hidden_layers"]
     engine = build_ours(cfg, layers, 64, torch.bfloat16, tokens_per_request=2048 + 128 + 16)
     gen = torch.Generator().manual_seed(7)
     lengths = torch.randint(16, 2049, (64,), generator=gen).tolist()
@@ -522,11 +521,38 @@ def run_mix(args):
     seconds = time.perf_counter() - t0
     total = sum(lengths) + 64 * 128
     stats = engine.stats()
-    print(json.dumps({"workload": "mix", "model": name, "layers": layers, "requests": 64, "prompt_tokens": sum(lengths),
-                      "decoded_tokens": 64 * 128, "seconds": round(seconds, 3), "tokens_per_s": round(total / seconds, 1),
-                      "decoded_tokens_per_s": round(64 * 128 / seconds, 1), "steps": steps,
-                      "mean_step_ms": round(seconds * 1e3 / steps, 3), "preemptions": stats["preemptions"]}))
+    del engine
+    torch.cuda.empty_cache()
+    return {"requests": 64, "prompt_tokens": sum(lengths), "decoded_tokens": 64 * 128, "seconds": round(seconds, 3),
+            "tokens_per_s": round(total / seconds, 1), "decoded_tokens_per_s": round(64 * 128 / seconds, 1), "steps": steps,
+            "mean_step_ms": round(seconds * 1e3 / steps, 3), "preemptions": stats["preemptions"]}
+
+
+def run_mix(args):
+    name, cfg = SHAPES[args.shape]
+    layers = args.layers or cfg["num_hidden_layers"]
+    print(json.dumps({"workload": "mix", "model": name, "layers": layers, **mix_workload(cfg, layers)}))
     return 0
+
+
+def further_points(args):
+    """Other sizes through the same engine, each at its full depth: the Qwen3-0.6B shape under the continuous-batching
+    mix (total tokens per second through the Python entry point), and decode at batch 8 and 2,048 tokens of context
+    at the Qwen3-32B shape (65 GB of weights)."""
+    import torch
+
+    out = {}
+    _name, small = SHAPES["0.6b"]
+    out["qwen3_0.6b_mix_64_requests"] = mix_workload(small, small["num_hidden_layers"])["tokens_per_s"]
+    _name, large = SHAPES["32b"]
+    engine = build_ours(large, large["num_hidden_layers"], 8, torch.bfloat16)
+    r = time_decode(engine, 8, 8, args.warmup, seed=40, e2e=False)
+    out["qwen3_32b_decode_b8"] = round(r["tok_s"], 1)
+    step_bytes = weight_bytes(large, large["num_hidden_layers"]) + 8 * (CONTEXT + args.warmup + 4) * kv_bytes_per_token(engine)
+    out["qwen3_32b_decode_b8_gbs"] = round(step_bytes / (r["ms"] * 1e-3) / 1e9, 1)
+    del engine
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args):
@@ -588,6 +614,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         baselines = {"plain_pytorch": plain_baseline(cfg, layers, CONTEXT)}
         check = selfcheck(cfg)
+        if args.shape == "8b" and not args.layers:
+            points.update(further_points(args))
     step_bytes = weight_bytes(cfg, layers) + args.batch * (CONTEXT + args.warmup + args.steps // 2) * kv_per_token
     achieved = step_bytes / (main["ms"] * 1e-3) / 1e9
     line = {

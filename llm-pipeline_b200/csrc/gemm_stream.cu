@@ -156,9 +156,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // The rows' factors, while the boxes of X are on their way: the sums of squares that the blocks of the
             // product before left, added in a fixed order (16 threads a row, each its parts in turn, then a tree).
             pdl_wait();
+            // (every part's sum is asked for before the first is added: ten dependent trips to L2 one after the other
+            // would cost some 3 us right where the product waits for its rows' factors; the order of the additions stays)
             float sum = 0.f;
-            if (row16 < p.M)
-                for (int b = part16; b < p.in_parts; b += 16) sum += p.in_sumsq[(size_t)b * 8 + row16];
+            for (int b0 = part16; b0 < p.in_parts; b0 += 16 * 12) {
+                float part_sum[12];
+#pragma unroll
+                for (int i = 0; i < 12; ++i) {
+                    const int b = b0 + 16 * i;
+                    part_sum[i] = (row16 < p.M && b < p.in_parts) ? __ldcg(p.in_sumsq + (size_t)b * 8 + row16) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 12; ++i) sum += part_sum[i];
+            }
 #pragma unroll
             for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
             if (part16 == 0 && row16 < p.M) row_factor[row16] = rsqrtf(sum * p.in_inv_width + p.in_eps);

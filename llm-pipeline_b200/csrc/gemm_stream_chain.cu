@@ -135,8 +135,18 @@ __device__ __forceinline__ void gc_phase(const ChainParams& p, const int ph, uns
             float block_squares = 0.f;
             if (q.in_sumsq != nullptr) {
                 float sum = 0.f;
-                if (row16 < p.M)
-                    for (int b = part16; b < q.in_parts; b += 16) sum += __ldcg(q.in_sumsq + (size_t)b * 8 + row16);
+                const int in_parts = q.in_parts;
+                const float* const in_sumsq = q.in_sumsq;
+                for (int b0 = part16; b0 < in_parts; b0 += 16 * 12) {          // (all loads first: see gemm_stream.cu)
+                    float part_sum[12];
+#pragma unroll
+                    for (int i = 0; i < 12; ++i) {
+                        const int b = b0 + 16 * i;
+                        part_sum[i] = (row16 < p.M && b < in_parts) ? __ldcg(in_sumsq + (size_t)b * 8 + row16) : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 12; ++i) sum += part_sum[i];
+                }
 #pragma unroll
                 for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
                 if (part16 == 0 && row16 < p.M) row_factor[row16] = rsqrtf(sum * q.in_inv_width + q.in_eps);
