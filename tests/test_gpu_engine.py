@@ -155,3 +155,65 @@ def test_a_request_name_that_comes_back_gets_its_own_block_table(tmp_path, dtype
     assert torch.allclose(got["a"], want["a"][32:], atol=H.TOL[dtype]), float((got["a"] - want["a"][32:]).abs().max())
     assert torch.allclose(got["b"], want["b"][28:], atol=H.TOL[dtype])
     assert runner.graph_replays > 0 and runner.cache.num_live == 0
+
+
+NEEDLE_CONFIG = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 256,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 512, "vocab_size": 384,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "attention_bias": False,
+    "max_position_embeddings": 2048, "hidden_act": "silu",
+}
+
+
+def test_a_planted_far_key_through_the_decode_graph_in_bfloat16(tmp_path):
+    """Random weights spread a softmax over hundreds of keys, and a far key that a kernel drops changes the logits by
+    less than bfloat16 rounding does. Here the embedding of one token is made so that, as the first token of a long
+    prompt, its key in the first layer is exactly what the decoded token's query looks for at one position (cosine 1
+    where random keys reach 0.3): one head's attention sits on the key at position 0, in the first page, hundreds of
+    keys away. The step that must find it runs head size 128 in bfloat16 as a replayed graph with the norms folded
+    into the streaming products, beside two other requests; without the key the oracle's logits differ by many times
+    the tolerance, so a kernel that lost it would fail."""
+    cfg = NEEDLE_CONFIG
+    dtype = torch.bfloat16
+    d, H_, nkv = cfg["head_dim"], cfg["hidden_size"], cfg["num_key_value_heads"]
+    weights = plain.random_weights(cfg, 21, std=0.05)
+    needle, query_token, far = 7, 11, 600                       # token ids; the query's position
+    # the query of head 0 of the first layer for `query_token` at position `far`
+    x = plain.rms_norm(weights["model.embed_tokens.weight"][query_token], weights["model.layers.0.input_layernorm.weight"], 1e-6)
+    q = (weights["model.layers.0.self_attn.q_proj.weight"] @ x)[:d]
+    q = plain.rms_norm(q, weights["model.layers.0.self_attn.q_norm.weight"], 1e-6)
+    cos, sin = plain.rope_cos_sin(torch.tensor([far]), d, cfg["rope_theta"])
+    target = plain.apply_rope(q[None, None, :], cos, sin)[0, 0]            # the key at position 0 is not rotated
+    # an embedding whose key (head 0 of the key/value heads) is parallel to the target: Wk (ln1 * e / rms) ~ target / k_norm
+    wk = weights["model.layers.0.self_attn.k_proj.weight"][:d]
+    wanted = target / weights["model.layers.0.self_attn.k_norm.weight"]
+    e = torch.linalg.pinv(wk) @ wanted / weights["model.layers.0.input_layernorm.weight"]
+    weights["model.embed_tokens.weight"][needle] = e * (0.05 * H_ ** 0.5 / e.norm())
+    weights = {k: v.to(dtype).float() for k, v in weights.items()}
+    folder = H.write_model_dir(str(tmp_path), cfg, weights, dtype)
+
+    filler = [t for t in H.random_tokens(cfg["vocab_size"], far + 40, 77) if t not in (needle, query_token)][:far - 1]
+    with_key = [needle] + filler + [query_token] * 4             # the query token lands on positions far .. far + 3
+    without = [filler[5]] + filler + [query_token] * 4
+    want = plain.forward_logits(cfg, weights, with_key, dtype=torch.float64).float()[far:]
+    blind = plain.forward_logits(cfg, weights, without, dtype=torch.float64).float()[far:]
+    tol = H.TOL[dtype] * max(1.0, float(want.abs().max()))          # the bound of the tiny models (logits up to 1), scaled to these logits (2)
+    assert float((want[0] - blind[0]).abs().max()) > 8 * tol        # the key matters far more than rounding does
+
+    from llm_pipeline_b200.engine import StepEntry
+    runner = H.make_runner(folder, dtype, page_size=16, num_pages=128, max_request_tokens=1024)
+    others = {"u": H.random_tokens(cfg["vocab_size"], 150, 5), "v": H.random_tokens(cfg["vocab_size"], 33, 6)}
+    for rid, toks in others.items():
+        runner.step([StepEntry(rid, toks[:-8], [])])
+    for at in range(0, far, 97):                                   # the prompt in portions that cross the 128-key tiles
+        runner.step([StepEntry("n", with_key[at:min(at + 97, far)], [])])
+    rows = []
+    for s in range(4):                                             # eager, captured, replayed, replayed
+        entries = [StepEntry("u", [others["u"][-8 + s]], []), StepEntry("n", [with_key[far + s]], [0]), StepEntry("v", [others["v"][-8 + s]], [])]
+        rows.append(runner.step(entries)[0].float().cpu().clone())
+    got = torch.stack(rows)
+    assert runner.graph_replays >= 2
+    assert float((got - want).abs().max()) <= tol, float((got - want).abs().max())
+    assert float((got[0] - blind[0]).abs().max()) > 6 * tol
+    from llm_pipeline_b200.ops import kernels
+    kernels.check_error_flag()
