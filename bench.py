@@ -605,7 +605,7 @@ def run_ours(args):
                      f"prefill_{PREFILL_TOKENS}": prefill_breakdown(engine, cfg, peak, PREFILL_TOKENS)}
         # the same batch with pages of 32 tokens (half as many TMA boxes in the decode attention stream)
         other_page = 32 if PAGE_SIZE != 32 else 16
-        wide = build_ours(cfg, layers, args.batch, dtype, tokens_per_request=max(CONTEXT + 256, room), page_size=other_page,
+        wide = build_ours(cfg, layers, max(64, args.batch), dtype, tokens_per_request=max(CONTEXT + 256, room), page_size=other_page,
                           model=engine.model)
         r = time_decode(wide, args.batch, max(5, args.steps // 2), args.warmup, seed=30, e2e=False)
         points[f"decode_b{args.batch}_page{other_page}"] = round(r["tok_s"], 1)
