@@ -31,8 +31,9 @@ class CacheError(RuntimeError):
 
 
 class PagePool:
-    """Page ids 0..n-1 with a LIFO free list: the page freed last is handed out first, so reuse
-    happens early and deterministically. Double frees and foreign ids are errors."""
+    """Page ids 0..n-1 with a LIFO free list: the pages freed last are handed out first (in the order
+    in which their holder held them), so reuse happens early and deterministically. Double frees and
+    foreign ids are errors."""
 
     def __init__(self, num_pages: int):
         if num_pages <= 0:
@@ -68,7 +69,10 @@ class PagePool:
                 raise CacheError(f"page {p} does not belong to this pool")
             if self._is_free[p]:
                 raise CacheError(f"page {p} freed twice")
-        for p in pages:
+        # In reverse, so that the pages of a run come out again in the order in which they were held: a request that
+        # gets the pages of one that ended holds ascending ids again, and the attention kernels bring pages whose ids
+        # follow one another in one TMA box.
+        for p in reversed(pages):
             self._is_free[p] = True
             self._free.append(p)
 

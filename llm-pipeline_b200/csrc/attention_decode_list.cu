@@ -465,7 +465,7 @@ int llmp_launch_decode_list(const void* q, long q_stride, void* out, long out_st
     p.page_size = page_size; p.num_pages = num_pages; p.box_tokens = page_size < DT_STAGE_KEYS ? page_size : DT_STAGE_KEYS;
     p.window = window; p.scale = scale; p.partials = scratch; p.arrivals = counters; p.error_flag = error_flag;
     CUtensorMap map;
-    if (llmp_pages_tensor_map(pages, nkv, page_size, num_pages, p.box_tokens, 2, &map)) return 1;
+    if (llmp_pages_tensor_map(pages, nkv, page_size, num_pages, p.box_tokens, 2, 1, &map)) return 1;
     const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + (size_t)(DT_CWARPS + 1) * DT_MAX_HEADS * DT_QSTRIDE * sizeof(bf16) +
                         (size_t)DT_CWARPS * DT_MAX_HEADS * DT_D * sizeof(float) + 1024;
     LLMP_ALLOW_SMEM(decode_attention_list_kernel, smem);

@@ -109,8 +109,8 @@ EncodeTiledFn llmp_tensor_map_encoder();
 
 // Tensor map over bfloat16 pages [num_pages, 2, nkv, page_size, 128], cached per tensor: boxes of box_tokens
 // tokens of one page and key/value head and 64 elements, 128-byte swizzle; box_kv = 2 takes keys and values in one
-// box (attention_prefill_tc.cu).
-int llmp_pages_tensor_map(const void* pages, int nkv, int page_size, int num_pages, int box_tokens, int box_kv,
+// box; box_pages > 1 takes box_pages pages of consecutive page ids in one box (attention_prefill_tc.cu).
+int llmp_pages_tensor_map(const void* pages, int nkv, int page_size, int num_pages, int box_tokens, int box_kv, int box_pages,
                           CUtensorMap* out);
 
 // Five-dimensional box of the pages into shared memory: x = first element (0 or 64), token within the page,
