@@ -14,7 +14,8 @@ from ..cache.spec import PagesSpec, StateSpec
 from ..config.base import ModelSpec, PartSpec
 from ..ops.linear import begin_step
 from ..parts import LayerCache, ResidualStream, lookup
-from ..weights.source import (ParamSpec, WeightSource, check_names_and_shapes, stored_dtype_policy)
+from ..weights.source import (ParamSpec, TiedWeightError, WeightSource, check_names_and_shapes,
+                              stored_dtype_policy)
 
 
 def _make(family: str, spec: PartSpec):
@@ -90,6 +91,11 @@ class Model:
             raise ValueError(f"the engine computes in float32 or bfloat16, not {dtype}")
         expected = self.expected_params()
         check_names_and_shapes(expected, source)
+        have = set(source.names())
+        for part in self.parts():
+            for name, original in part.copies().items():
+                if name in have and not torch.equal(source.get(name), source.get(original)):
+                    raise TiedWeightError(name, original)
         self.device, self.dtype = torch.device(device), dtype
         # A tensor two parts read (the table of a tied head) is moved to the device once.
         tied_to = self.spec.head.args.get("tied_to")

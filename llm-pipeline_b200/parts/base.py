@@ -93,6 +93,11 @@ class Part:
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 
+    def copies(self) -> Dict[str, str]:
+        """Names of optional tensors of this part that, where a checkpoint holds them, must repeat
+        another tensor: {own name: the name it repeats}. The loader compares the two."""
+        return {}
+
     def load(self, get: TensorGetter) -> None:
         pass
 

@@ -44,8 +44,13 @@ class LinearHead(Head):
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        # A tied head has no tensor of its own; a checkpoint may still carry a copy, which is ignored.
+        # A tied head has no tensor of its own; a checkpoint may still carry a copy, which must be one.
         return {f"{self.prefix}.weight": ParamSpec((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
+
+    def copies(self) -> Dict[str, str]:
+        # The reference makes the head's parameter the embedding's own tensor when tie_word_embeddings is set
+        # (models/qwen3/custom_builder.py:389-391), so a checkpoint it wrote holds the same values under both names.
+        return {f"{self.prefix}.weight": f"{self.tied_to}.weight"} if self.tied_to else {}
 
     def load(self, get: TensorGetter) -> None:
         name = f"{self.tied_to}.weight" if self.tied_to else f"{self.prefix}.weight"

@@ -35,6 +35,15 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class TiedWeightError(ValueError):
+    """The checkpoint holds a tensor that the model reads under another name, with other values."""
+
+    def __init__(self, name: str, original: str):
+        self.name, self.original = name, original
+        super().__init__(f"the checkpoint's {name} differs from {original}, which the model uses in its place "
+                         f"(tied weights): one of the two is not what the configuration says")
+
+
 @dataclass(frozen=True)
 class ParamSpec:
     """A tensor a part expects. ``role``: "matrix" (operand of a matrix product, kept in the

@@ -53,6 +53,19 @@ def test_tied_head_is_optional_and_untied_head_is_required():
         check_names_and_shapes(untied, DictSource(w))
 
 
+def test_a_copy_of_a_tied_head_must_repeat_the_embedding():
+    # The reference's tied head is the embedding's own tensor (models/qwen3/custom_builder.py:389-391): a checkpoint
+    # that holds other values under lm_head.weight contradicts its configuration, and loading says so.
+    from llm_pipeline_b200.weights import TiedWeightError
+    w = plain.random_weights(plain.TINY_A, 0)
+    model = build_model(resolve_config(plain.TINY_A))
+    model.load(DictSource({**w, "lm_head.weight": w["model.embed_tokens.weight"].clone()}), torch.device("cpu"), torch.float32)
+    assert model.head.weight is model.embedding.weight
+    with pytest.raises(TiedWeightError, match="lm_head.weight differs from model.embed_tokens.weight"):
+        build_model(resolve_config(plain.TINY_A)).load(
+            DictSource({**w, "lm_head.weight": w["model.embed_tokens.weight"] + 1.0}), torch.device("cpu"), torch.float32)
+
+
 def test_random_model_folder_round_trips(tmp_path):
     folder = write_random_model(plain.TINY_C, seed=7, out_dir=str(tmp_path / "m"), dtype=torch.bfloat16)
     assert sorted(os.listdir(folder)) == ["config.json", "model.safetensors"]
