@@ -45,7 +45,8 @@ class StepContext:
         self.leading_keys = 0                # the keys they see together
         # device side (int32)
         self.token_ids: torch.Tensor = None  # [N]
-        self.positions: torch.Tensor = None  # [N]
+        self.positions: torch.Tensor = None  # [N]: each token's place in its request (where its keys go in the cache)
+        self.position_ids: torch.Tensor = None  # [streams, N]: what position encodings read; one stream: the places
         self.q_start: torch.Tensor = None    # [R + 1]
         self.ctx_len: torch.Tensor = None    # [R] keys visible to the request after this step
         self.slots: torch.Tensor = None      # [R] state slot of each request

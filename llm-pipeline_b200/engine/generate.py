@@ -76,7 +76,10 @@ class GenerationEngine:
     # -- requests --------------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], max_tokens: int = 16,
                     sampling: Optional[SamplingConfig] = None, eos_token_ids: Optional[Sequence[int]] = None,
-                    ignore_eos: bool = False, req_id: Optional[Hashable] = None) -> Hashable:
+                    ignore_eos: bool = False, req_id: Optional[Hashable] = None,
+                    position_ids: Optional[Sequence[Sequence[int]]] = None) -> Hashable:
+        """``position_ids``: for a model whose position encoding reads several streams of positions, the prompt's
+        position ids, one sequence per stream (see ``Request.position_ids``)."""
         req_id = next(self._ids) if req_id is None else req_id
         if req_id in self._requests and self._requests[req_id].status != "finished":
             raise ValueError(f"request id {req_id!r} is in use")
@@ -85,8 +88,13 @@ class GenerationEngine:
                 raise ValueError(f"token id {t} is outside the vocabulary of {self.model.spec.vocab_size}")
         if eos_token_ids is None:
             eos_token_ids = self.config.eos_token_ids() if self.config is not None else []
+        streams = self.runner.position_streams
+        if position_ids is not None and (len(position_ids) != streams or any(len(row) != len(prompt_token_ids) for row in position_ids)):
+            raise ValueError(f"position ids must be [{streams}][{len(prompt_token_ids)}]: one row for each stream of the "
+                             "model's position encoding, one id for each prompt token")
         request = Request(req_id, [int(t) for t in prompt_token_ids], sampling or self.sampler.config,
-                          int(max_tokens), set(int(t) for t in eos_token_ids), ignore_eos)
+                          int(max_tokens), set(int(t) for t in eos_token_ids), ignore_eos,
+                          position_ids=None if position_ids is None else [[int(x) for x in row] for row in position_ids])
         self.scheduler.add(request)
         self._requests[req_id] = request
         return req_id
@@ -103,7 +111,7 @@ class GenerationEngine:
             if not finished and self.scheduler.has_unfinished():
                 raise RuntimeError("the scheduler could not plan a step although requests are unfinished")
             return finished
-        entries = [StepEntry(e.request.req_id, e.token_ids, [e.count - 1] if e.samples else []) for e in plan.entries]
+        entries = [StepEntry(e.request.req_id, e.token_ids, [e.count - 1] if e.samples else [], e.positions) for e in plan.entries]
         logits = self.runner.step(entries)
         sampled: Dict[Hashable, int] = {}
         due = [e for e in plan.entries if e.samples]

@@ -11,6 +11,7 @@ the paged cache that earlier steps left, and computes the output head for the wa
 
 from __future__ import annotations
 
+import copy
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -20,7 +21,7 @@ import torch
 from ..cache import CacheManager
 from ..models.model import Model
 from ..ops import kernels
-from ..parts import LayerCache
+from ..parts import LayerCache, ResidualStream
 from .context import StepContext, StepShape
 
 
@@ -31,11 +32,14 @@ class OutOfPages(RuntimeError):
 @dataclass
 class StepEntry:
     """The next ``tokens`` of request ``req_id``; ``want`` lists the places among these tokens
-    (0-based) whose logits are asked for."""
+    (0-based) whose logits are asked for. ``positions``: for a model whose position encoding reads more than one
+    stream of positions (``PositionEncoding.streams``), the position ids of these tokens, one sequence per stream;
+    None: every stream holds the tokens' places in the request, which is what a one-stream encoding always reads."""
 
     req_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)
+    positions: Optional[Sequence[Sequence[int]]] = None
 
 
 class _CacheViews:
@@ -63,15 +67,29 @@ class _DecodeGraph:
         self.host_np = None          # the pinned buffer as a numpy array (same memory)
         self.req_ids = None          # the requests of the last step in row order, each with its admission number
         self.table_lens = None       # per cache group and row: pages of the block table already in the buffer
+        self.pieces = None           # a model that is captured in pieces: [_Piece] in the order of the schedule
+
+
+class _Piece:
+    """A run of scheduled layers of a captured decode step: either a CUDA graph (``graph``; it reads the float32
+    residual ``inlet`` unless it is the first piece, and leaves ``outlet``: the residual after its layers, or the
+    logits if it is the last piece) or layers that run eagerly every step (``graph`` None)."""
+
+    def __init__(self, first: int, end: int):
+        self.first, self.end = first, end
+        self.graph = None
+        self.inlet = None
+        self.outlet = None
 
 
 class ModelRunner:
     """``use_graphs``: steps in which every request brings exactly one token are captured in CUDA
     graphs, one per (number of requests, wanted rows, block-table width rounded up to
-    ``GRAPH_WIDTH_STEP`` pages), and replayed; the first step of a shape runs eagerly. Models with
+    ``GRAPH_WIDTH_STEP`` pages), and replayed; the first step of a shape runs eagerly. Layers with
     a part that does not declare ``graph_safe`` (a mixer that updates per-request state, a
-    feed-forward whose launches depend on the data) always run eagerly. The logits a replayed step returns
-    live in the graph's static buffer and are valid until the next step of the same shape."""
+    feed-forward whose launches depend on the data) run eagerly every step, between graphs of the runs of layers
+    before and after them (``Model.pieces``); a model without a capturable layer runs eagerly as a whole. The logits
+    a replayed step returns live in the graph's static buffer and are valid until the next step of the same shape."""
 
     GRAPH_WIDTH_STEP = 32
     CONTEXT_BOUND_STEP = 128
@@ -89,12 +107,13 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0
-        parts = list(model.parts()) if hasattr(model, "parts") else None
-        self.use_graphs = bool(use_graphs and parts is not None and all(getattr(p, "graph_safe", False) for p in parts))
+        self._pieces = model.pieces() if hasattr(model, "pieces") else []
+        self.use_graphs = bool(use_graphs and any(capturable for _first, _end, capturable in self._pieces))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self._staging: list = []             # pinned buffers for the index arrays of eager steps: (tensor, numpy view, event)
         self.graph_replays = 0
         self._context_limit = model.captured_context_limit() if hasattr(model, "captured_context_limit") else None
+        self.position_streams = int(getattr(model, "position_streams", 1))
 
     # -- pages for the step's tokens -----------------------------------------------------------
     def _reserve(self, entries: Sequence[StepEntry]) -> None:
@@ -123,6 +142,10 @@ class ModelRunner:
                 for w in e.want:
                     if not 0 <= int(w) < n:
                         raise ValueError(f"request {e.req_id!r} wants logits at place {w} of {n} tokens")
+                if e.positions is not None and (len(e.positions) != self.position_streams or
+                                                any(len(row) != n for row in e.positions)):
+                    raise ValueError(f"request {e.req_id!r} brings position ids of another shape than "
+                                     f"[{self.position_streams}][{n}], one row for each stream of the model's position encoding")
                 if e.req_id not in cache:
                     cache.admit(e.req_id)
                     admitted.append(e.req_id)
@@ -148,7 +171,8 @@ class ModelRunner:
     def _fill(self, ctx: StepContext, entries: Sequence[StepEntry], width: Optional[int] = None) -> np.ndarray:
         """Host side of the context, and the flat int32 image of its device arrays:
         token ids, positions, request of each token, q_start, ctx_len, slots, logit rows, then per
-        cache group the slot mapping and the block tables (``width`` entries per request). Long runs of
+        cache group the slot mapping and the block tables (``width`` entries per request), and at the end, for a
+        model with several streams of positions, the position ids stream by stream. Long runs of
         tokens (prompt portions) are filled as arrays, single tokens as scalars."""
         cache = self.cache
         ps = cache.page_size
@@ -178,7 +202,8 @@ class ModelRunner:
         ctx.table_width = width
         groups = len(cache.groups)
         head = 3 * N + (R + 1) + 2 * R + len(rows)
-        flat = np.empty(head + groups * (N + R * width), dtype=np.int32)
+        streams = self.position_streams if self.position_streams > 1 else 0
+        flat = np.empty(head + groups * (N + R * width) + streams * N, dtype=np.int32)
         token_ids, positions, token_request = flat[0:N], flat[N:2 * N], flat[2 * N:3 * N]
         for r, e in enumerate(entries):
             at, n, start = first[r], q_lens[r], starts[r]
@@ -214,6 +239,11 @@ class ModelRunner:
                 k = min(width, len(table))
                 tables[r, :k] = table[:k]
             cursor += N + R * width
+        if streams:
+            ids = flat[cursor:cursor + streams * N].reshape(streams, N)
+            for r, e in enumerate(entries):
+                at, n = first[r], q_lens[r]
+                ids[:, at:at + n] = positions[at:at + n] if e.positions is None else np.asarray(e.positions, dtype=np.int32)
         return flat
 
     def _to_device(self, flat: np.ndarray) -> torch.Tensor:
@@ -257,6 +287,8 @@ class ModelRunner:
         for _g in range(len(self.cache.groups)):
             ctx.slot_mapping.append(take(N))
             ctx.block_tables.append(take(R * width).view(R, width))
+        streams = self.position_streams
+        ctx.position_ids = take(streams * N).view(streams, N) if streams > 1 else ctx.positions.view(1, N)
 
     @classmethod
     def decode_graph_shape(cls, longest: int, page_size: int, max_request_tokens: int, limit: Optional[int] = None):
@@ -323,13 +355,16 @@ class ModelRunner:
             slot.ctx.decode_ctx_bound = bound
             slot.copied = torch.cuda.Event()
             torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count
-            with torch.cuda.graph(graph):
-                slot.logits = self._run(slot.ctx)
+            if len(self._pieces) == 1:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    slot.logits = self._run(slot.ctx)
+                slot.graph = graph
+            else:
+                self._capture_pieces(slot)
             slot.launches = kernels.launch_count - before
             kernels.launch_count = before
-            slot.graph = graph
         else:
             slot.copied.synchronize()            # the previous copy out of the pinned buffer is done
             if slot.req_ids == [(e.req_id, cache.admission(e.req_id)) for e in entries]:
@@ -341,10 +376,64 @@ class ModelRunner:
             slot.dev.copy_(slot.host, non_blocking=True)
         slot.copied.record()
         self.last_h2d_bytes = slot.host.numel() * 4
-        slot.graph.replay()
+        if slot.pieces is None:
+            slot.graph.replay()
+        else:
+            self._replay_pieces(slot)
         kernels.launch_count += slot.launches    # every replay launches the captured kernels again
         self.graph_replays += 1
         return self._finish(slot.ctx, entries, slot.logits)
+
+    def _capture_pieces(self, slot: _DecodeGraph) -> None:
+        """A graph for every capturable run of layers of the model, all from one memory pool. What crosses from one
+        piece to the next is the residual stream settled into one float32 tensor: a graph leaves it where the eager
+        layers after it read it; eager layers' result is copied to where the graph after them expects it. What comes
+        before the first layer (position tables, embedding) and after the last (final norm, head) is always captured:
+        as part of the first and last run of layers if those are capturable, else as pieces of their own."""
+        ctx, model = slot.ctx, self.model
+        layers = len(model.schedule)
+        runs = list(self._pieces)
+        if not runs[0][2]:
+            runs.insert(0, (0, 0, True))
+        if not runs[-1][2]:
+            runs.append((layers, layers, True))
+        pool = torch.cuda.graph_pool_handle()
+        slot.pieces = []
+        for k, (first, end, capturable) in enumerate(runs):
+            piece = _Piece(first, end)
+            slot.pieces.append(piece)
+            if not capturable:
+                continue
+            if k > 0:
+                piece.inlet = torch.empty((ctx.num_tokens, model.spec.hidden_size), dtype=torch.float32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            piece.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(piece.graph, pool=pool):
+                stream = model.begin(ctx) if k == 0 else ResidualStream(piece.inlet)
+                model.run_layers(ctx, self._views, stream, first, end)
+                if k + 1 < len(runs):
+                    piece.outlet = stream.settle()
+                elif ctx.logit_rows is not None:
+                    piece.outlet = model.logits(ctx, stream, ctx.logit_rows)
+        slot.graph = slot.pieces[0].graph
+
+    def _replay_pieces(self, slot: _DecodeGraph) -> None:
+        ctx, model = slot.ctx, self.model
+        residual = None
+        for piece in slot.pieces:
+            if piece.graph is not None:
+                if piece.inlet is not None:
+                    piece.inlet.copy_(residual)
+                piece.graph.replay()
+                residual = piece.outlet
+                continue
+            # eager layers: the step's arrays are the captured step's; what the layers note for themselves is not kept
+            eager = copy.copy(ctx)
+            eager.memo = {}
+            stream = ResidualStream(residual)
+            model.run_layers(eager, self._views, stream, piece.first, piece.end)
+            residual = stream.settle()
+        slot.logits = slot.pieces[-1].outlet
 
     def _remember(self, slot: _DecodeGraph, entries: Sequence[StepEntry]) -> None:
         slot.req_ids = [(e.req_id, self.cache.admission(e.req_id)) for e in entries]
@@ -381,6 +470,10 @@ class ModelRunner:
                     buf[at + r * width:at + r * width + n] = table[:n]
                     lens[r] = len(table)
             at += R * width
+        if self.position_streams > 1:
+            for s in range(self.position_streams):
+                buf[at:at + R] = [start if e.positions is None else int(e.positions[s][0]) for e, start in zip(entries, starts)]
+                at += R
 
     def _finish(self, ctx: StepContext, entries: Sequence[StepEntry], logits):
         for r, e in enumerate(entries):

@@ -41,10 +41,22 @@ class Request:
     status: str = "waiting"            # waiting | running | finished
     finish_reason: Optional[str] = None
     preemptions: int = 0
+    # For a model whose position encoding reads several streams of positions: the prompt's position ids, one list per
+    # stream. Generated tokens go on from the largest position id of the prompt, by one per token, in every stream.
+    position_ids: Optional[List[List[int]]] = None
 
     @property
     def tokens(self) -> List[int]:
         return self.prompt + self.output
+
+    def positions_of(self, start: int, count: int) -> Optional[List[List[int]]]:
+        """Position ids of the tokens start .. start + count - 1, stream by stream; None without ``position_ids``."""
+        if self.position_ids is None:
+            return None
+        n = len(self.prompt)
+        after = 1 + max(max(row) for row in self.position_ids) if n else 0
+        tail = [after + i - n for i in range(max(start, n), start + count)]
+        return [list(row[start:min(start + count, n)]) + tail for row in self.position_ids]
 
     @property
     def num_pending(self) -> int:
@@ -61,6 +73,10 @@ class PlannedEntry:
     @property
     def token_ids(self) -> List[int]:
         return self.request.tokens[self.start:self.start + self.count]
+
+    @property
+    def positions(self) -> Optional[List[List[int]]]:
+        return self.request.positions_of(self.start, self.count)
 
 
 @dataclass

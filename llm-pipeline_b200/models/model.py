@@ -28,6 +28,7 @@ class Model:
         self.spec = spec
         self.embedding = _make("embedding", spec.embedding)
         self.positions = {name: _make("position", p) for name, p in spec.positions.items()}
+        self.position_streams = max([int(getattr(p, "streams", 1)) for p in self.positions.values()] or [1])
         self.blocks = []
         for layer in spec.layers:
             block_cls = lookup("block", layer.block)
@@ -122,13 +123,40 @@ class Model:
     def forward(self, ctx, caches) -> ResidualStream:
         """Run every scheduled layer on the step's tokens. ``caches.view(cache_id, writes)`` gives
         the ``LayerCache`` of an execution."""
+        stream = self.begin(ctx)
+        self.run_layers(ctx, caches, stream, 0, len(self.schedule))
+        return stream
+
+    def begin(self, ctx) -> ResidualStream:
+        """What comes before the first layer: the position tables of the step and the embedded tokens."""
         begin_step()
         ctx.position_tables = {name: part.tables(ctx) for name, part in self.positions.items()}
-        stream = ResidualStream(self.embedding.forward(ctx))
-        for index, entry in enumerate(self.schedule):
+        return ResidualStream(self.embedding.forward(ctx))
+
+    def run_layers(self, ctx, caches, stream: ResidualStream, first: int, end: int) -> None:
+        """The scheduled executions first .. end - 1 on ``stream``."""
+        for index in range(first, end):
+            entry = self.schedule[index]
             cache = caches.view(entry.cache, writes=self._owner[entry.cache] == index)
             self.blocks[entry.layer].forward(stream, ctx, cache)
-        return stream
+
+    def pieces(self) -> List[Tuple[int, int, bool]]:
+        """The schedule as runs (first, end, capturable): consecutive executions whose blocks are all ``graph_safe``
+        (their work for a step of fixed shape can be captured in a CUDA graph and replayed) and the runs between
+        them, which must run eagerly every step. Empty when what surrounds the layers (embedding, position
+        encodings, final norm, head) is not capturable: such a model runs eagerly as a whole."""
+        safe = lambda part: bool(getattr(part, "graph_safe", False))   # noqa: E731
+        around = [self.embedding, self.final_norm, self.head] + list(self.positions.values())
+        if not all(safe(part) for part in around):
+            return []
+        out: List[Tuple[int, int, bool]] = []
+        for index, entry in enumerate(self.schedule):
+            ok = all(safe(part) for part in self.blocks[entry.layer].parts())
+            if out and out[-1][2] == ok:
+                out[-1] = (out[-1][0], index + 1, ok)
+            else:
+                out.append((index, index + 1, ok))
+        return out
 
     def logits(self, ctx, stream: ResidualStream, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the given token rows of the step."""

@@ -74,6 +74,17 @@ class ResidualStream:
     def pending(self, delta) -> None:
         self._pending = delta
 
+    def settle(self) -> torch.Tensor:
+        """Add what is pending into the residual and return it: the whole state of the stream in one float32 tensor
+        (between pieces of a step that are captured apart; the norms fold the addend in on their own otherwise)."""
+        pending = self.pending
+        if pending is not None:
+            self.residual = self.residual + pending.float()
+            if self.pending_bias is not None:
+                self.residual = self.residual + self.pending_bias.float()
+            self._pending, self.pending_bias = None, None
+        return self.residual
+
     def take_pending_product(self) -> Optional[PendingProduct]:
         """The pending addend if it is a product not yet taken and without bias, which is then the caller's to add;
         else None, and nothing changes."""
@@ -108,6 +119,11 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # Streams of position ids the encoding reads for every token: ``ctx.position_ids`` is [streams of the model, N].
+    # With one stream (the default) that is each token's place in its request; an encoding with more (a place along
+    # several axes) gets what the request brought (``StepEntry.positions``), or the place in every stream.
+    streams: int = 1
+
     def tables(self, ctx):
         raise NotImplementedError
 

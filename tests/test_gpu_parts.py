@@ -300,6 +300,19 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     H.assert_close(H.replay(runner, H.cut_whole(requests)), want, 1e-4, "toy whole")
     H.assert_close(H.replay(runner, H.cut_portions(requests, (5, 2, 9, 1))), want, 1e-4, "toy portions")
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 1e-4, "toy mixed")
+    # Steps of single tokens: the attention layer between the two runs of the stateful layer is replayed from a CUDA
+    # graph, as are the embedding before and the head after them; the stateful layer runs eagerly every step.
+    assert runner.use_graphs and runner.model.pieces() == [(0, 1, False), (1, 2, True), (2, 3, False)]
+    before = runner.graph_replays
+    H.assert_close(H.replay(runner, H.cut_tail_one_by_one(requests, tail=12)), want, 1e-4, "toy tail, token by token")
+    assert runner.graph_replays >= before + 5 * 10
+    two = {rid: requests[rid] for rid in ("t0", "t3")}                    # two requests decoding side by side
+    steps = [([(rid, toks[:len(toks) - 9], [len(toks) - 10]) for rid, toks in two.items()], [])]
+    steps += [([(rid, [toks[len(toks) - 9 + i]], [0]) for rid, toks in two.items()], []) for i in range(9)]
+    steps[-1] = (steps[-1][0], list(two))
+    got = H.replay(runner, steps)
+    for rid, toks in two.items():
+        assert float((got[rid] - want[rid][len(toks) - 10:]).abs().max()) < 1e-4, rid
     # the windowed group never held more pages per request than the window needs
     assert runner.cache.groups[0].pool.high_water < 32 and runner.cache.pages_reused > 0
 
@@ -614,3 +627,181 @@ def test_toy_latent_cache_and_four_norm_block(tmp_path):
     from llm_pipeline_b200.parts import lookup
     with pytest.raises(ValueError, match="post_mixer"):
         lookup("block", "toy_sandwich")(None, None, object(), object())
+
+
+# ------------------------------------------------------------------------------------------
+# A toy position encoding that reads two streams of positions, registered from this file: a token has a row and a
+# column; the lower half of the rotation frequencies turns with the row, the upper half with the column. Requests
+# bring their position ids with their tokens; the cache goes on counting places as always.
+# ------------------------------------------------------------------------------------------
+
+def _register_toy_grid_positions():
+    from llm_pipeline_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
+                                          register_architecture)
+    from llm_pipeline_b200.parts import PositionEncoding, register_position
+
+    @register_position("toy_row_column_rotary")
+    class RowColumnRotary(PositionEncoding):
+        streams = 2
+        graph_safe = True                  # torch operations on the step's static arrays only
+
+        def __init__(self, prefix, rotary_dim, theta):
+            self.rotary_dim, self.theta = rotary_dim, theta
+
+        def tables(self, ctx):
+            half = self.rotary_dim // 2
+            j = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32, device=ctx.device)
+            inv_freq = 1.0 / (self.theta ** (j / self.rotary_dim))
+            ids = ctx.position_ids.float()                                   # [2, N]
+            which = (torch.arange(half, device=ctx.device) >= half // 2).long()       # frequency j reads stream which[j]
+            angles = ids[which].t() * inv_freq[None, :]                      # [N, half]
+            return angles.cos().contiguous(), angles.sin().contiguous()
+
+    class ToyGridConfig(ModelConfig):
+        architecture = "ToyGridForCausalLM"
+
+        def __init__(self, data):
+            self.data = data
+
+        @classmethod
+        def from_json(cls, data):
+            return cls(dict(data))
+
+        def to_json(self):
+            return dict(self.data)
+
+        def model_spec(self):
+            d = self.data
+            H, V, hd = d["hidden_size"], d["vocab_size"], d["head_dim"]
+            norm = {"size": H, "eps": d["eps"]}
+            layers = []
+            for i in range(d["layers"]):
+                attn = PartSpec("attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"], "head_dim": hd,
+                                              "scale": hd ** -0.5, "qk_norm": True, "qk_norm_eps": d["eps"], "position": "grid"},
+                                f"blocks.{i}.attn")
+                ff = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["intermediate_size"]}, f"blocks.{i}.mlp")
+                layers.append(LayerSpec("pre_norm_residual", attn, ff, PartSpec("rms_norm", norm, f"blocks.{i}.n1"),
+                                        PartSpec("rms_norm", norm, f"blocks.{i}.n2")))
+            return ModelSpec("ToyGridForCausalLM", V, H, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "embed"),
+                             {"grid": PartSpec("toy_row_column_rotary", {"rotary_dim": hd, "theta": 300.0})},
+                             tuple(layers), tuple(ScheduleEntry(i, i) for i in range(d["layers"])),
+                             PartSpec("rms_norm", norm, "final"), PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tied_to": None}, "head"), 512)
+
+    register_architecture("ToyGridForCausalLM", ToyGridConfig)
+
+
+TOY_GRID = {"architectures": ["ToyGridForCausalLM"], "hidden_size": 64, "vocab_size": 173, "intermediate_size": 80, "heads": 4,
+            "kv_heads": 2, "head_dim": 32, "eps": 1e-5, "layers": 2}
+
+
+def toy_grid_reference(w, ids, rows, cols):
+    d = TOY_GRID
+    T, nh, nkv, hd = len(ids), d["heads"], d["kv_heads"], d["head_dim"]
+    x = w["embed.weight"][torch.tensor(ids)]
+    half = hd // 2
+    inv_freq = 1.0 / (300.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    place = torch.stack([torch.tensor(rows).float()] * (half // 2) + [torch.tensor(cols).float()] * (half - half // 2), dim=1)
+    angles = place * inv_freq[None, :]
+    cos, sin = torch.cat((angles.cos(), angles.cos()), -1), torch.cat((angles.sin(), angles.sin()), -1)
+
+    def rope(t):                                   # t [heads, T, hd]
+        return t * cos[None] + plain.rotate_half(t) * sin[None]
+
+    for i in range(d["layers"]):
+        p = f"blocks.{i}"
+        h = plain.rms_norm(x, w[f"{p}.n1.weight"], d["eps"])
+        q = (h @ w[f"{p}.attn.q_proj.weight"].t()).view(T, nh, hd).transpose(0, 1)
+        k = (h @ w[f"{p}.attn.k_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1)
+        v = (h @ w[f"{p}.attn.v_proj.weight"].t()).view(T, nkv, hd).transpose(0, 1)
+        q = rope(plain.rms_norm(q, w[f"{p}.attn.q_norm.weight"], d["eps"]))
+        k = rope(plain.rms_norm(k, w[f"{p}.attn.k_norm.weight"], d["eps"]))
+        k, v = k.repeat_interleave(nh // nkv, 0), v.repeat_interleave(nh // nkv, 0)
+        pos = torch.arange(T)
+        scores = ((q @ k.transpose(1, 2)) * hd ** -0.5).masked_fill((pos[None, :] > pos[:, None])[None], float("-inf"))
+        x = x + (torch.softmax(scores, -1) @ v).transpose(0, 1).reshape(T, nh * hd) @ w[f"{p}.attn.o_proj.weight"].t()
+        h = plain.rms_norm(x, w[f"{p}.n2.weight"], d["eps"])
+        I = d["intermediate_size"]
+        x = x + (torch.nn.functional.silu(h @ w[f"{p}.mlp.gate_proj.weight"].t()) * (h @ w[f"{p}.mlp.up_proj.weight"].t())) \
+            @ w[f"{p}.mlp.down_proj.weight"].t()
+        assert w[f"{p}.mlp.gate_proj.weight"].shape[0] == I
+    return plain.rms_norm(x, w["final.weight"], d["eps"]) @ w["head.weight"].t()
+
+
+def test_toy_position_encoding_with_two_streams_of_positions(tmp_path):
+    """A position encoding that reads a row and a column for every token, registered from this file: requests bring
+    both with their tokens through the unchanged step function (whole, in portions, mixed, the tail token by token
+    through replayed graphs), and through the generation engine, where generated tokens go on from the largest id of
+    the prompt. Without position ids every stream holds the tokens' places."""
+    _register_toy_grid_positions()
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.engine.generate import GenerationEngine
+    from llm_pipeline_b200.models import load_model
+    from llm_pipeline_b200.sampling import SamplingConfig
+    from llm_pipeline_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    folder = write_random_model(TOY_GRID, seed=33, out_dir=str(tmp_path), dtype=torch.float32, std=0.2)
+    weights = load_file(f"{folder}/model.safetensors")
+    runner = H.make_runner(folder, torch.float32, page_size=8, num_pages=40, max_request_tokens=256)
+    assert runner.position_streams == 2 and runner.use_graphs
+    requests = {f"g{i}": H.random_tokens(TOY_GRID["vocab_size"], n, 60 + i) for i, n in enumerate((45, 8, 52, 27))}
+    # a grid of 7 columns, row by row, the second request starting in the middle of the grid
+    place = {rid: ([(t + 3 * i) // 7 for t in range(len(toks))], [(t + 3 * i) % 7 for t in range(len(toks))])
+             for i, (rid, toks) in enumerate(requests.items())}
+    want = {rid: toy_grid_reference(weights, toks, *place[rid]) for rid, toks in requests.items()}
+
+    def replay(steps):
+        rows, done = {}, {rid: 0 for rid in requests}
+        for entries, end in steps:
+            batch = []
+            for rid, toks, wanted in entries:
+                a, b = done[rid], done[rid] + len(toks)
+                batch.append(StepEntry(rid, toks, wanted, [place[rid][0][a:b], place[rid][1][a:b]]))
+                done[rid] = b
+            logits = runner.step(batch)
+            cursor = 0
+            for rid, _toks, wanted in entries:
+                rows.setdefault(rid, []).append(logits[cursor:cursor + len(wanted)].float().cpu())
+                cursor += len(wanted)
+            for rid in end:
+                runner.release(rid)
+            runner.cache.check()
+        return {rid: torch.cat(parts) for rid, parts in rows.items()}
+
+    H.assert_close(replay(H.cut_whole(requests)), want, 2e-4, "grid whole")
+    H.assert_close(replay(H.cut_portions(requests, (5, 2, 9, 1))), want, 2e-4, "grid portions")
+    H.assert_close(replay(H.cut_mixed(requests, (5, 2, 9, 3), max_live=3)), want, 2e-4, "grid mixed")
+    before = runner.graph_replays
+    H.assert_close(replay(H.cut_tail_one_by_one(requests, tail=20)), want, 2e-4, "grid tail")
+    assert runner.graph_replays > before + 40
+    # without position ids: the place in the request in both streams
+    toks = requests["g1"]
+    got = runner.step([StepEntry("plain", toks, list(range(len(toks))))]).float().cpu()
+    runner.release("plain")
+    assert float((got - toy_grid_reference(weights, toks, list(range(len(toks))), list(range(len(toks))))).abs().max()) < 2e-4
+    with pytest.raises(ValueError, match="position ids of another shape"):
+        runner.step([StepEntry("bad", toks, [0], [list(range(len(toks)))])])
+    # through the generation engine: greedy tokens against the plain formulas, generated tokens at max id + 1, + 2, ...
+    config, model = load_model(folder, "cuda:0", torch.float32)
+    engine = GenerationEngine(model, config, page_size=8, num_pages=40, max_num_seqs=4, max_num_batched_tokens=16, max_model_len=256)
+    greedy = SamplingConfig(temperature=0.0)
+    ids = {}
+    for rid in ("g0", "g3"):
+        ids[rid] = engine.add_request(requests[rid], max_tokens=6, sampling=greedy, ignore_eos=True, position_ids=place[rid])
+    outputs = {}
+    while engine.has_unfinished():
+        for request in engine.step():
+            outputs[request.req_id] = list(request.output)
+    for rid in ("g0", "g3"):
+        toks, rows, cols = list(requests[rid]), list(place[rid][0]), list(place[rid][1])
+        after = 1 + max(max(rows), max(cols))
+        for step in range(6):
+            logits = toy_grid_reference(weights, toks, rows, cols)[-1]
+            top2 = logits.topk(2).values
+            token = int(logits.argmax())
+            if float(top2[0] - top2[1]) > 1e-3:                       # a near tie may fall either way
+                assert outputs[ids[rid]][step] == token, (rid, step)
+            toks.append(outputs[ids[rid]][step])
+            rows.append(after + step)
+            cols.append(after + step)
+    with pytest.raises(ValueError, match="position ids must be"):
+        engine.add_request(requests["g1"], position_ids=[place["g1"][0]])

@@ -161,3 +161,16 @@ def test_abort_frees_pages():
     sched.add(request("a", 9))
     run_step(cache, sched)
     assert sched.abort("a").finish_reason == "abort" and cache.num_live == 0 and not sched.has_unfinished()
+
+
+def test_position_ids_of_a_portion_go_on_after_the_prompts_largest_id():
+    """A request may bring position ids in several streams for its prompt; portions take their slices, and generated
+    tokens (also when a preempted request is recomputed from prompt plus output) count on from the largest id."""
+    r = Request("a", [5, 6, 7, 8], SamplingConfig(), 8, position_ids=[[0, 0, 1, 1], [0, 1, 0, 9]])
+    assert r.positions_of(0, 4) == [[0, 0, 1, 1], [0, 1, 0, 9]]
+    assert r.positions_of(1, 2) == [[0, 1], [1, 0]]
+    r.output = [3, 3, 3]
+    assert r.positions_of(4, 1) == [[10], [10]]
+    assert r.positions_of(6, 1) == [[12], [12]]
+    assert r.positions_of(2, 4) == [[1, 1, 10, 11], [0, 9, 10, 11]]
+    assert Request("b", [1, 2], SamplingConfig(), 4).positions_of(0, 2) is None
