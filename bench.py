@@ -264,103 +264,42 @@ def time_prefill(engine, tokens, repeats, warmup):
     return times[len(times) // 2]
 
 
-class KernelTimes:
-    """CUDA events around every kernel launch of an eager step: this library's entry points (all go through
-    ``kernels._call``) and the library matrix product (``torch.mm``). The step is queued behind a sleeping kernel, so
-    the launches wait on the device, not for the host, and an interval is the kernel's own time (plus the events')."""
+def product_labels(cfg):
+    """Names the matrix products of a step after what they are in this model (for ``ops.timing.KernelTimes``)."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    qkv = q + 2 * cfg["num_key_value_heads"] * cfg["head_dim"]
 
-    GEMMS = ("llmp_gemm_stream", "llmp_gemm_stream_fused", "llmp_gemm_stream_swiglu", "llmp_gemm_stream_tc", "llmp_gemm_tc",
-             "llmp_gemm_skinny")
+    def label(name, work):
+        if work is None:
+            return name
+        _M, N, K = work
+        kind = ("product_head" if N == V else "product_gate_up" if N == 2 * I else "product_qkv" if N == qkv and K == H
+                else "product_down" if N == H and K == I else "product_o" if N == H and K == q else "product_other")
+        return kind + ("+swiglu" if name.endswith("+swiglu") else "") + (" (library)" if name == "mm" else "")
+    return label
 
-    def __init__(self, cfg):
-        self.cfg = cfg
-        self.items = []
 
-    def product_class(self, N, K):
-        cfg = self.cfg
-        H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
-        q = cfg["num_attention_heads"] * cfg["head_dim"]
-        qkv = q + 2 * cfg["num_key_value_heads"] * cfg["head_dim"]
-        if N == V:
-            return "product_head"
-        if N == 2 * I:
-            return "product_gate_up"
-        if N == qkv and K == H:
-            return "product_qkv"
-        if N == H and K == I:
-            return "product_down"
-        if N == H and K == q:
-            return "product_o"
-        return "product_other"
-
-    def __enter__(self):
-        import torch
-
-        from llm_pipeline_b200.ops import kernels
-        self._call, self._mm = kernels._call, torch.mm
-        outer = self
-
-        def timed(label, work, fn, *args, **kwargs):
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            out = fn(*args, **kwargs)
-            stop.record()
-            outer.items.append((label, work, start, stop))
-            return out
-
-        def call(name, *args):
-            label, work = name[5:], None
-            if name in self.GEMMS:
-                M, N, K = args[4], args[5], args[6]
-                if name == "llmp_gemm_stream_swiglu":
-                    N *= 2
-                label, work = outer.product_class(N, K) + ("+swiglu" if name == "llmp_gemm_stream_swiglu" or
-                                                           (name == "llmp_gemm_stream_fused" and args[10]) else ""), (M, N, K)
-            return timed(label, work, outer._call, name, *args)
-
-        def mm(a, b, **kwargs):
-            M, K, N = a.shape[0], a.shape[1], b.shape[1]
-            return timed(outer.product_class(N, K) + " (library)", (M, N, K), outer._mm, a, b, **kwargs)
-
-        kernels._call, torch.mm = call, mm
-        return self
-
-    def __exit__(self, *exc):
-        import torch
-
-        from llm_pipeline_b200.ops import kernels
-        kernels._call, torch.mm = self._call, self._mm
-
-    def summary(self, peak, attention_bytes=0.0, attention_flops=0.0):
-        """Per class: launches, microseconds, and for the products and the attention kernels what they achieved over the
-        measured peak (GB/s of the bytes they must read when the rows are few, TFLOP/s otherwise)."""
-        classes = {}
-        for label, work, start, stop in self.items:
-            entry = classes.setdefault(label, {"launches": 0, "us": 0.0, "bytes": 0.0, "flops": 0.0, "rows": 0})
-            entry["launches"] += 1
-            entry["us"] += start.elapsed_time(stop) * 1e3
-            if work is not None:
-                M, N, K = work
-                entry["bytes"] += 2.0 * N * K + 2.0 * M * K + 2.0 * M * N
-                entry["flops"] += 2.0 * M * N * K
-                entry["rows"] = M
-        out = {}
-        total = sum(e["us"] for e in classes.values())
-        for label, e in sorted(classes.items(), key=lambda kv: -kv[1]["us"]):
-            row = {"launches": e["launches"], "us": round(e["us"], 1), "share": round(e["us"] / total, 3)}
-            seconds = e["us"] * 1e-6
-            if label == "decode_attention" and attention_bytes:
-                e["bytes"], e["rows"] = attention_bytes, 1
-            if label == "paged_attention" and attention_flops:
-                e["flops"], e["rows"] = attention_flops, 1 << 20
-            if e["bytes"] and e["rows"] <= 64:
-                row["gbs"] = round(e["bytes"] / seconds / 1e9, 1)
-                row["frac_hbm"] = round(e["bytes"] / seconds / 1e9 / peak["hbm_gbs"], 3)
-            elif e["flops"]:
-                row["tflops"] = round(e["flops"] / seconds / 1e12, 1)
-                row["frac_bf16_burst"] = round(e["flops"] / seconds / 1e12 / peak["bf16_tflops_burst"], 3)
-            out[label] = row
-        return {"kernel_us": round(total, 1), "classes": out}
+def breakdown_summary(table, peak, attention_bytes=0.0, attention_flops=0.0):
+    """Per class: launches, microseconds, and for the products and the attention kernels what they achieved over the
+    measured peak (GB/s of the bytes they must read when the rows are few, TFLOP/s otherwise)."""
+    out = {}
+    total = sum(e["us"] for e in table.values())
+    for label, e in table.items():
+        row = {"launches": e["launches"], "us": round(e["us"], 1), "share": round(e["us"] / total, 3)}
+        seconds = e["us"] * 1e-6
+        if label == "decode_attention" and attention_bytes:
+            e["bytes"], e["rows"] = attention_bytes, 1
+        if label == "paged_attention" and attention_flops:
+            e["flops"], e["rows"] = attention_flops, 1 << 20
+        if e["bytes"] and e["rows"] <= 64:
+            row["gbs"] = round(e["bytes"] / seconds / 1e9, 1)
+            row["frac_hbm"] = round(e["bytes"] / seconds / 1e9 / peak["hbm_gbs"], 3)
+        elif e["flops"]:
+            row["tflops"] = round(e["flops"] / seconds / 1e12, 1)
+            row["frac_bf16_burst"] = round(e["flops"] / seconds / 1e12 / peak["bf16_tflops_burst"], 3)
+        out[label] = row
+    return {"kernel_us": round(total, 1), "classes": out}
 
 
 def breakdown_of_a_step(engine, cfg, peak, entries_of, attention_bytes=0.0, attention_flops=0.0, release=()):
@@ -372,7 +311,8 @@ def breakdown_of_a_step(engine, cfg, peak, entries_of, attention_bytes=0.0, atte
     try:
         runner.step(entries_of(0))                      # untimed: first-call set-up of every kernel of the shape
         torch.cuda.synchronize()
-        times = KernelTimes(cfg)
+        from llm_pipeline_b200.ops.timing import KernelTimes
+        times = KernelTimes(product_labels(cfg))
         torch.cuda._sleep(int(1.5e8))                   # some 80 ms at the SM clock: the whole step queues up behind it
         with times:
             runner.step(entries_of(1))
@@ -381,7 +321,7 @@ def breakdown_of_a_step(engine, cfg, peak, entries_of, attention_bytes=0.0, atte
         runner.use_graphs = graphs
         for rid in release:
             runner.release(rid)
-    return times.summary(peak, attention_bytes, attention_flops)
+    return breakdown_summary(times.table(), peak, attention_bytes, attention_flops)
 
 
 def decode_breakdown(engine, cfg, peak, batch):

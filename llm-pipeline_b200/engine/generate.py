@@ -154,4 +154,6 @@ class GenerationEngine:
         out = {"steps": self.steps, "tokens_prefilled": self.tokens_prefilled, "tokens_decoded": self.tokens_decoded}
         out.update(self.scheduler.stats())
         out.update(self.cache.stats())
+        if self.runner.kernel_times is not None:             # LLMP_B200_KERNEL_TIMES=1
+            out["kernel_times"] = self.runner.kernel_times.table()
         return out

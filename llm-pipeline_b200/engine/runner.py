@@ -20,7 +20,7 @@ import torch
 
 from ..cache import CacheManager
 from ..models.model import Model
-from ..ops import kernels
+from ..ops import kernels, timing
 from ..parts import LayerCache, ResidualStream
 from .context import StepContext, StepShape
 
@@ -108,6 +108,9 @@ class ModelRunner:
         self.tokens_run = 0
         self.last_h2d_bytes = 0
         self._pieces = model.pieces() if hasattr(model, "pieces") else []
+        # LLMP_B200_KERNEL_TIMES=1: CUDA events around every launch of every step, which then runs eagerly
+        self.kernel_times = timing.KernelTimes() if timing.TIME_KERNELS else None
+        use_graphs = use_graphs and self.kernel_times is None
         self.use_graphs = bool(use_graphs and any(capturable for _first, _end, capturable in self._pieces))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self._staging: list = []             # pinned buffers for the index arrays of eager steps: (tensor, numpy view, event)
@@ -490,10 +493,16 @@ class ModelRunner:
         entries = list(entries)
         if not entries:
             return None
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), timing.nvtx_range(f"step of {sum(len(e.tokens) for e in entries)} tokens"):
             if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
                 return self._decode_graph_step(entries)
             ctx = self._prepare(entries)
+            if self.kernel_times is not None:
+                with self.kernel_times:
+                    logits = self._run(ctx)
+                if len(self.kernel_times.items) > 50000:
+                    self.kernel_times.fold()
+                return self._finish(ctx, entries, logits)
             return self._finish(ctx, entries, self._run(ctx))
 
     def release(self, req_id: Hashable) -> None:

@@ -13,6 +13,7 @@ import torch
 from ..cache.spec import PagesSpec, StateSpec
 from ..config.base import ModelSpec, PartSpec
 from ..ops.linear import begin_step
+from ..ops.timing import nvtx_range
 from ..parts import LayerCache, ResidualStream, lookup
 from ..weights.source import (ParamSpec, TiedWeightError, WeightSource, check_names_and_shapes,
                               stored_dtype_policy)
@@ -130,15 +131,17 @@ class Model:
     def begin(self, ctx) -> ResidualStream:
         """What comes before the first layer: the position tables of the step and the embedded tokens."""
         begin_step()
-        ctx.position_tables = {name: part.tables(ctx) for name, part in self.positions.items()}
-        return ResidualStream(self.embedding.forward(ctx))
+        with nvtx_range("positions and embedding"):
+            ctx.position_tables = {name: part.tables(ctx) for name, part in self.positions.items()}
+            return ResidualStream(self.embedding.forward(ctx))
 
     def run_layers(self, ctx, caches, stream: ResidualStream, first: int, end: int) -> None:
         """The scheduled executions first .. end - 1 on ``stream``."""
         for index in range(first, end):
             entry = self.schedule[index]
             cache = caches.view(entry.cache, writes=self._owner[entry.cache] == index)
-            self.blocks[entry.layer].forward(stream, ctx, cache)
+            with nvtx_range(f"layer {entry.layer} (execution {index})"):
+                self.blocks[entry.layer].forward(stream, ctx, cache)
 
     def pieces(self) -> List[Tuple[int, int, bool]]:
         """The schedule as runs (first, end, capturable): consecutive executions whose blocks are all ``graph_safe``
@@ -160,5 +163,6 @@ class Model:
 
     def logits(self, ctx, stream: ResidualStream, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the given token rows of the step."""
-        normed = self.final_norm.add_norm(stream, ctx, rows=rows)
-        return self.head.forward(normed, ctx)
+        with nvtx_range("final norm and head"):
+            normed = self.final_norm.add_norm(stream, ctx, rows=rows)
+            return self.head.forward(normed, ctx)

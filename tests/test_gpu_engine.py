@@ -217,3 +217,39 @@ def test_a_planted_far_key_through_the_decode_graph_in_bfloat16(tmp_path):
     assert float((got[0] - blind[0]).abs().max()) > 6 * tol
     from llm_pipeline_b200.ops import kernels
     kernels.check_error_flag()
+
+
+def test_kernel_times_and_nvtx_ranges_of_steps(tmp_path, monkeypatch):
+    """CUDA events around every launch (``ops.timing.KernelTimes``): as a block around one step, and for every step of
+    a runner when the switch is on (graphs are then off); with NVTX ranges pushed around step, layers and head. The
+    logits are what they are without any of it."""
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.ops import timing
+    tiny = plain.TINY_D
+    folder, weights = H.make_case(tmp_path, tiny, 3, torch.bfloat16)
+    layers = tiny["num_hidden_layers"]
+    runner = H.make_runner(folder, torch.bfloat16, page_size=16, num_pages=16)
+    tokens = H.random_tokens(tiny["vocab_size"], 40, 9)
+    plain_logits = runner.step([StepEntry("a", tokens, [39])]).float().cpu()
+    runner.release("a")
+    monkeypatch.setattr(timing, "NVTX", True)
+    with timing.KernelTimes() as times:
+        timed_logits = runner.step([StepEntry("a", tokens, [39])]).float().cpu()
+    assert torch.equal(plain_logits, timed_logits)
+    table = times.table()
+    assert table["qkv_post"]["launches"] == layers and table["paged_attention"]["launches"] == layers
+    assert table["embedding"]["launches"] == 1 and all(row["us"] > 0 for row in table.values())
+    products = sum(row["launches"] for name, row in table.items() if row["flops"] > 0)
+    assert products == 4 * layers + 1                       # q/k/v, output, gate/up, down per layer; the head
+    assert list(table) == sorted(table, key=lambda name: -table[name]["us"])
+    runner.release("a")
+    # the switch: every step of a new runner is timed, none is captured
+    monkeypatch.setattr(timing, "TIME_KERNELS", True)
+    timed = H.make_runner(folder, torch.bfloat16, page_size=16, num_pages=16)
+    assert timed.kernel_times is not None and not timed.use_graphs
+    timed.step([StepEntry("b", tokens, [])])
+    for i in range(4):
+        timed.step([StepEntry("b", [tokens[i]], [0])])
+    totals = timed.kernel_times.table()
+    assert totals["decode_attention"]["launches"] == 4 * layers and totals["paged_attention"]["launches"] == layers
+    assert timed.graph_replays == 0
