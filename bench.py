@@ -276,7 +276,8 @@ def product_labels(cfg):
         _M, N, K = work
         kind = ("product_head" if N == V else "product_gate_up" if N == 2 * I else "product_qkv" if N == qkv and K == H
                 else "product_down" if N == H and K == I else "product_o" if N == H and K == q else "product_other")
-        return kind + ("+swiglu" if name.endswith("+swiglu") else "") + (" (library)" if name == "mm" else "")
+        return (kind + ("+swiglu" if name.endswith("+swiglu") else "") + (" (library)" if name == "mm" else "") +
+                (" (library, into the residual)" if name == "mm+residual" else ""))
     return label
 
 

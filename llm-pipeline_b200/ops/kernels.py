@@ -205,6 +205,58 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     return out
 
 
+# ---- the library product into a float32 residual ---------------------------------------------------------------------
+_cublas = None
+_CUDA_R_16BF, _CUDA_R_32F, _CUBLAS_COMPUTE_32F, _CUBLAS_OP_N, _CUBLAS_OP_T, _CUBLAS_GEMM_DEFAULT = 14, 0, 68, 0, 1, -1
+
+
+def _cublas_gemm_ex():
+    """cuBLAS's cublasGemmEx from the library that torch has loaded (None when it cannot be had)."""
+    global _cublas
+    if _cublas is None:
+        _cublas = False
+        for name in ("libcublas.so.12", "libcublas.so"):
+            try:
+                fn = ctypes.CDLL(name).cublasGemmEx
+            except (OSError, AttributeError):
+                continue
+            fn.restype = ctypes.c_int
+            fn.argtypes = [_P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I]
+            _cublas = fn
+            break
+    return _cublas or None
+
+
+_ONE = ctypes.c_float(1.0)
+_ONE_REF = ctypes.byref(_ONE)
+
+
+def library_add_product(residual: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """residual[M, N] (float32) += x[M, K] @ w[N, K]^T (bfloat16 operands, float32 sums) by the library's matrix
+    product with the residual as its float32 C operand: the product is never rounded to bfloat16 and the norm kernel
+    after it has nothing to add. On torch's cuBLAS handle and current stream, like ``torch.mm``; where the engine uses
+    a library product for the rows of a prompt portion (the reference's ``nn.Linear`` is the same library,
+    src/llm_pipeline/models/qwen3/custom_builder.py:124-131). False, and nothing done, when the operands are not of
+    these types, not row-major, not 16-byte aligned, or the library cannot be had."""
+    gemm = _cublas or _cublas_gemm_ex()
+    M, K = x.shape
+    N = w.shape[0]
+    if (not gemm or residual.dtype != torch.float32 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M == 0 or
+            not residual.is_cuda or x.stride(1) != 1 or w.stride(1) != 1 or residual.stride(1) != 1 or w.shape[1] != K or
+            residual.shape != (M, N)):
+        return False
+    xp, wp, rp = x.data_ptr(), w.data_ptr(), residual.data_ptr()
+    if (xp | wp | rp) % 16:
+        return False
+    # row-major residual[M, N] is column-major [N, M]: (w as [K, N] column-major, transposed) times (x as [K, M])
+    rc = gemm(torch.cuda.current_blas_handle(), _CUBLAS_OP_T, _CUBLAS_OP_N, N, M, K, _ONE_REF, wp, _CUDA_R_16BF, w.stride(0),
+              xp, _CUDA_R_16BF, x.stride(0), _ONE_REF, rp, _CUDA_R_32F, residual.stride(0), _CUBLAS_COMPUTE_32F,
+              _CUBLAS_GEMM_DEFAULT)
+    if rc != 0:
+        raise KernelError(f"cublasGemmEx failed with status {rc}")
+    return True
+
+
 def qkv_post(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, *,
              bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
              eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,

@@ -39,8 +39,11 @@ class PendingProduct:
     """``x @ weight^T`` that has not been taken yet. A norm that can fold the product into its own work asks for
     ``x`` (a tensor, or ``LazyRows``) and ``weight``; everybody else calls ``value()``."""
 
-    def __init__(self, x, weight: torch.Tensor):
+    def __init__(self, x, weight: torch.Tensor, accumulate: bool = False):
         self.x, self.weight = x, weight
+        # True: many rows; whoever adds the product to a float32 residual may let the library's product do the adding
+        # (``kernels.library_add_product``) instead of taking the value and adding it
+        self.accumulate = accumulate
 
     def value(self) -> torch.Tensor:
         return linear(self.x, self.weight)
@@ -59,6 +62,13 @@ class PendingProduct:
 # chains takes 4.55 ms against 3.63 ms, because as dependent launches the separate products already fill their rings
 # while the kernel before them ends, each with a ring of its own stage size (see csrc/gemm_stream_chain.cu).
 CHAIN = os.environ.get("LLMP_B200_CHAIN", "0") == "1"
+# Rows from which a product that is an addend of the residual (output and down projection) is left to the library's
+# product with the float32 residual as its C operand (0: never): the norm after it then only reads the residual.
+# Measured on a B200 (Qwen3-8B shape): a 2,048-token prefill 27.2 -> 26.6 ms. The call costs the host a few
+# microseconds more than torch.mm, which a step that waits for the host pays for in full (the continuous-batching mix
+# at the Qwen3-0.6B shape: 85 -> 75 thousand tokens/s with it), so it is taken only for many rows of a large matrix.
+ACCUMULATE_MIN_ROWS = int(os.environ.get("LLMP_B200_ACCUMULATE_MIN_M", "1024"))
+ACCUMULATE_MIN_WEIGHTS = 1 << 24
 
 
 class _Chain:
@@ -166,6 +176,9 @@ def pending_product(x: torch.Tensor, weight: torch.Tensor):
             rows.stride(1) == 1 and weight.stride(1) == 1 and not rows.data_ptr() % 16 and not weight.data_ptr() % 16 and
             kernels.gemm_stream_blocks(M, weight.shape[0], K, rows.stride(0), weight.stride(0)) > 0):
         return PendingProduct(x, weight)
+    if (ACCUMULATE_MIN_ROWS and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and M >= ACCUMULATE_MIN_ROWS and
+            weight.numel() >= ACCUMULATE_MIN_WEIGHTS and x.is_cuda and x.stride(1) == 1 and weight.stride(1) == 1 and not x.data_ptr() % 16 and not weight.data_ptr() % 16):
+        return PendingProduct(x, weight, accumulate=True)
     return linear(x, weight)
 
 

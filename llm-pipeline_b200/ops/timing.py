@@ -47,7 +47,8 @@ class KernelTimes:
     """``with KernelTimes() as times: runner.step(...)`` then ``times.table()``.
 
     ``label(name, work)`` may rename a launch: ``name`` is the entry point without its ``llmp_`` prefix (or ``"mm"`` for
-    the library product), ``work`` is (M, N, K) for a matrix product and None otherwise. Events are kept until
+    the library product, ``"mm+residual"`` for the library product that adds into the float32 residual), ``work`` is
+    (M, N, K) for a matrix product and None otherwise. Events are kept until
     ``fold()`` (called by ``table()``), which waits for the device and adds the intervals up; a long-running user calls
     ``fold()`` now and then."""
 
@@ -64,8 +65,8 @@ class KernelTimes:
         self._depth += 1
         if self._depth > 1:
             return self
-        self._saved = (kernels._call, torch.mm)
-        call_before, mm_before = self._saved
+        self._saved = (kernels._call, torch.mm, kernels.library_add_product)
+        call_before, mm_before, add_before = self._saved
         outer = self
 
         def timed(label, work, fn, *args, **kwargs):
@@ -91,14 +92,19 @@ class KernelTimes:
             work = (a.shape[0], b.shape[1], a.shape[1])
             return timed(outer._label("mm", work) if outer._label else "mm (library)", work, mm_before, a, b, **kwargs)
 
-        kernels._call, torch.mm = call, mm
+        def add_product(residual, x, w):
+            work = (x.shape[0], w.shape[0], x.shape[1])
+            label = outer._label("mm+residual", work) if outer._label else "mm into the residual (library)"
+            return timed(label, work, add_before, residual, x, w)
+
+        kernels._call, torch.mm, kernels.library_add_product = call, mm, add_product
         return self
 
     def __exit__(self, *exc):
         from . import kernels
         self._depth -= 1
         if self._depth == 0:
-            kernels._call, torch.mm = self._saved
+            kernels._call, torch.mm, kernels.library_add_product = self._saved
             self._saved = None
 
     # -- results -----------------------------------------------------------------------------

@@ -48,6 +48,11 @@ class RMSNorm(Norm):
         if product is None:
             return self.add_norm(stream, ctx)
         residual = stream.residual
+        if product.accumulate:
+            # many rows: the library's product adds itself into the residual, the norm kernel only reads it
+            if not kernels.library_add_product(residual, product.x, product.weight):
+                stream.add(product.value())
+            return self.add_norm(stream, ctx)
 
         def finished() -> torch.Tensor:
             # for a consumer that cannot apply the factors: the norm of the residual as it now is

@@ -253,3 +253,29 @@ def test_kernel_times_and_nvtx_ranges_of_steps(tmp_path, monkeypatch):
     totals = timed.kernel_times.table()
     assert totals["decode_attention"]["launches"] == 4 * layers and totals["paged_attention"]["launches"] == layers
     assert timed.graph_replays == 0
+
+
+@pytest.mark.parametrize("config,seed", [(plain.TINY_A, 0), (plain.TINY_D, 3)], ids=["a", "d"])
+def test_prompt_portions_whose_products_add_themselves_into_the_residual(tmp_path, monkeypatch, config, seed):
+    """Many rows of a large matrix leave the sum of residual and product to the library's product (float32 C operand).
+    With the limits lowered so that the tiny models take that way: whole prompts, portions on both sides of the limit
+    and mixed batches give the plain implementation's logits, and the way was taken."""
+    import importlib
+    linear = importlib.import_module("llm_pipeline_b200.ops.linear")
+    from llm_pipeline_b200.ops import kernels
+    monkeypatch.setattr(linear, "ACCUMULATE_MIN_ROWS", 16)
+    monkeypatch.setattr(linear, "ACCUMULATE_MIN_WEIGHTS", 0)
+    calls = []
+    real = kernels.library_add_product
+    monkeypatch.setattr(kernels, "library_add_product", lambda r, x, w: calls.append(x.shape[0]) or real(r, x, w))
+    folder, weights = H.make_case(tmp_path, config, seed, torch.bfloat16)
+    runner = H.make_runner(folder, torch.bfloat16, page_size=16, num_pages=24)
+    requests = {f"r{i}": H.random_tokens(config["vocab_size"], n, 900 + i) for i, n in enumerate((70, 17, 45, 33))}
+    want = H.expected_logits(config, weights, requests)
+    tol = H.TOL[torch.bfloat16]
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, tol, "accumulate whole")
+    assert calls and min(calls) >= 16
+    whole = len(calls)
+    H.assert_close(H.replay(runner, H.cut_portions(requests, (20, 5, 16, 31))), want, tol, "accumulate portions")
+    H.assert_close(H.replay(runner, H.cut_mixed(requests, (18, 3, 40, 16), max_live=3)), want, tol, "accumulate mixed")
+    assert len(calls) > whole and min(calls) >= 16

@@ -651,3 +651,25 @@ def test_gemm_stream_chain_gives_the_bits_of_its_products(M, H, Q, I, QKV):
         assert torch.allclose(chained[6].float(), q_ref, atol=4e-2 * float(q_ref.abs().max()))
     else:
         assert torch.allclose(chained[6].float(), d_ref, atol=3e-2 * float(d_ref.abs().max()))
+
+
+@pytest.mark.parametrize("M,N,Kd", [(2048, 4096, 4096), (300, 1000, 520), (1, 64, 8), (77, 4104, 264)])
+def test_library_product_adds_into_the_float32_residual(M, N, Kd):
+    """The library's product with the float32 residual as its C operand: residual += x w^T with float32 sums, the
+    product itself never rounded to bfloat16; refused (False, nothing touched) for other types or unaligned rows."""
+    x = rnd(M, Kd, dtype=torch.bfloat16, seed=1, scale=0.5)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=2, scale=0.1)
+    residual = rnd(M, N, seed=3)
+    want = residual.double() + x.double() @ w.double().t()
+    got = residual.clone()
+    assert K().library_add_product(got, x, w)
+    scale = float(want.abs().max())
+    assert float((got.double() - want).abs().max()) <= 2e-6 * scale * max(1, Kd // 64)      # float32 sums over K
+    # closer than adding the product rounded to bfloat16 would be
+    rounded = residual.double() + (x.double() @ w.double().t()).to(torch.bfloat16).double()
+    if Kd >= 264:
+        assert float((got.double() - want).abs().max()) < float((rounded - want).abs().max())
+    untouched = residual.clone()
+    assert not K().library_add_product(untouched, x.float(), w)
+    assert not K().library_add_product(untouched[:, 1:], x, w[1:])
+    assert torch.equal(untouched, residual)
