@@ -279,3 +279,43 @@ def test_prompt_portions_whose_products_add_themselves_into_the_residual(tmp_pat
     H.assert_close(H.replay(runner, H.cut_portions(requests, (20, 5, 16, 31))), want, tol, "accumulate portions")
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (18, 3, 40, 16), max_live=3)), want, tol, "accumulate mixed")
     assert len(calls) > whole and min(calls) >= 16
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_context_of_several_thousand_tokens_in_portions_and_decoded(tmp_path, dtype):
+    """A request of 6,300 tokens at head size 128 beside a short one: the prompt in portions of 2,048, 1,500, 37 and 2
+    tokens (a few new tokens over thousands of cached keys: in bfloat16 the tiles of such a portion share their keys),
+    then tokens decoded one by one beside the other request's (the longer request is read by many SMs), against the
+    plain implementation in float64 on the same device, at the last place of every portion and at every decoded one."""
+    from llm_pipeline_b200.engine import StepEntry
+    config = dict(plain.TINY_D, max_position_embeddings=8192)
+    folder, weights = H.make_case(tmp_path, config, 5, dtype)
+    runner = H.make_runner(folder, dtype, page_size=16, num_pages=420, max_request_tokens=6400)
+    long_ids, short_ids = H.random_tokens(config["vocab_size"], 6300, 71), H.random_tokens(config["vocab_size"], 150, 72)
+    cuts = [2048, 2048, 1500, 600, 37, 2, 57]                       # 6,292 tokens of prompt, then 8 decoded
+    assert sum(cuts) == 6292
+    got, rows, done = [], [], 0
+    for i, n in enumerate(cuts):
+        entries = [StepEntry("long", long_ids[done:done + n], [n - 1])]
+        if i == 3:
+            entries.append(StepEntry("short", short_ids[:142], []))                  # joins in the middle of the long prompt
+        got.append(runner.step(entries).float().cpu())
+        done += n
+        rows.append(done - 1)
+    for i in range(8):
+        logits = runner.step([StepEntry("long", [long_ids[6292 + i]], [0]), StepEntry("short", [short_ids[142 + i]], [0])])
+        got.append(logits[:1].float().cpu())
+        rows.append(6292 + i)
+        short_row = logits[1:].float().cpu()
+    device_weights = {k: v.cuda() for k, v in weights.items()}
+    want = plain.forward_logits(config, device_weights, long_ids, dtype=torch.float64, rows=rows).float().cpu()
+    want_short = plain.forward_logits(config, device_weights, short_ids, dtype=torch.float64, rows=[149]).float().cpu()
+    tol = H.TOL[dtype] * max(1.0, float(want.abs().max()))
+    worst = float((torch.cat(got) - want).abs().max())
+    assert worst <= tol, (worst, tol)
+    assert float((short_row - want_short).abs().max()) <= tol
+    assert runner.graph_replays >= 5
+    runner.release("long")
+    runner.release("short")
+    runner.cache.check()
+    assert runner.cache.num_live == 0
