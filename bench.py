@@ -192,21 +192,26 @@ def time_decode(engine, batch, steps, warmup, seed, e2e=True, contexts=None):
         for at in range(0, len(prompt), PREFILL_TOKENS):
             runner.step([StepEntry(rid, prompt[at:at + PREFILL_TOKENS], [])])
     last = [p[-1] for p in prompts]
-    out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    outs = [torch.empty(batch, dtype=torch.int32, device=engine.device) for _ in range(2)]
 
-    def one_step(tokens):
-        logits = runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)])
-        return kernels.argmax(logits, out)
+    # As the engine steps: the ids a step samples stay on the device, where the next step takes them from
+    # (``StepEntry.device_token``); the host reads them a step late (the end-to-end figure below has that read in it).
+    def one_step(k, before):
+        if before is None:
+            entries = [StepEntry(rid, [t], [0]) for rid, t in zip(ids, last)]
+        else:
+            entries = [StepEntry(rid, [0], [0], None, (before, i)) for i, rid in enumerate(ids)]
+        return kernels.argmax(runner.step(entries), outs[k & 1])
 
-    tokens = last
-    for _ in range(warmup):
-        tokens = one_step(tokens).tolist()
+    tokens = None
+    for k in range(warmup):
+        tokens = one_step(k, tokens)
     torch.cuda.synchronize()
     launches_before = kernels.launch_count
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(steps):
-        tokens = one_step(tokens).tolist()       # the sampled ids go to the host and come back as the next input
+    for k in range(warmup, warmup + steps):
+        tokens = one_step(k, tokens)
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps

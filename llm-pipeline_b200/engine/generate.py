@@ -11,6 +11,7 @@ then one token per model call, stopping at EOS or ``max_tokens``.
 from __future__ import annotations
 
 import itertools
+import os
 import time
 from dataclasses import dataclass, field, replace
 from typing import Dict, Hashable, List, Optional, Sequence, Union
@@ -23,7 +24,7 @@ from ..models import Model, build_model, load_model
 from ..ops import kernels
 from ..sampling import Sampler, SamplingConfig
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, Scheduler, StepPlan
+from .scheduler import PENDING, Request, Scheduler, StepPlan
 
 
 @dataclass
@@ -40,7 +41,8 @@ class GenerationEngine:
     def __init__(self, model: Model, config: Optional[ModelConfig] = None, *, page_size: int = 16,
                  num_pages: Optional[int] = None, memory_fraction: float = 0.8, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048, max_model_len: Optional[int] = None,
-                 max_prefill_chunk: Optional[int] = None, sampling: Optional[SamplingConfig] = None):
+                 max_prefill_chunk: Optional[int] = None, sampling: Optional[SamplingConfig] = None,
+                 lookahead: Optional[bool] = None):
         self.model, self.config = model, config
         self.device, self.dtype = model.device, model.dtype
         max_model_len = int(max_model_len or model.spec.max_position)
@@ -54,6 +56,9 @@ class GenerationEngine:
         self.sampler = Sampler(sampling)
         self._ids = itertools.count()
         self._requests: Dict[Hashable, Request] = {}
+        self.lookahead = os.environ.get("LLMP_B200_LOOKAHEAD", "1") != "0" if lookahead is None else bool(lookahead)
+        self._in_flight = None                   # (sampled ids on the device, their requests, their landing place) of the step not read back yet
+        self._landing: list = []                 # pinned host buffers with an event each, for the sampled ids' way to the host
         self.steps = 0
         self.tokens_prefilled = 0
         self.tokens_decoded = 0
@@ -100,35 +105,102 @@ class GenerationEngine:
         return req_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        # (ids still in flight for requests that are all finished, stopped or aborted meanwhile, are nobody's business)
+        return self.scheduler.has_unfinished() or (self._in_flight is not None and
+                                                   any(r.status != "finished" for r in self._in_flight[1]))
 
     # -- one step --------------------------------------------------------------------------
     def step(self) -> List[Request]:
-        """Plan, run and record one batch; returns the requests that finished in it."""
+        """Plan and launch one batch, then read back what the batch before it sampled; returns the requests that are
+        finished with all their tokens known.
+
+        The engine runs one step ahead of what it has read (``lookahead``): a step's sampled ids stay on the device,
+        the next step takes them from there (``StepEntry.device_token``) and is planned and queued while the device
+        still works on this one; only then does the host wait for this step's ids. So the device never waits for the
+        host between steps. What the plan of the next step needs of a token it cannot see is only that it exists
+        (``Request.in_flight``); a request that an end-of-sequence token ends was then planned one step too far, and
+        what that step sampled for it is dropped. A request with a repetition penalty needs its tokens on the host
+        before the next is sampled: while one is running or waiting, every step is read back before the next is planned."""
+        finished: List[Request] = []
+        ahead = self.lookahead and not any(r.sampling.repetition_penalty != 1.0
+                                           for r in list(self.scheduler.running) + list(self.scheduler.waiting))
+        if not ahead:
+            finished += self._read_back()
         plan: StepPlan = self.scheduler.schedule()
-        finished = list(plan.aborted)
+        finished += plan.aborted
         if not plan.entries:
+            if self._in_flight is not None:
+                return finished + self._read_back()
             if not finished and self.scheduler.has_unfinished():
                 raise RuntimeError("the scheduler could not plan a step although requests are unfinished")
             return finished
-        entries = [StepEntry(e.request.req_id, e.token_ids, [e.count - 1] if e.samples else [], e.positions) for e in plan.entries]
+        entries = []
+        for e in plan.entries:
+            tokens, on_device = e.token_ids, None
+            if tokens[-1] == PENDING:
+                # the id is among those the step before sampled
+                source, rows, _landing = self._in_flight
+                on_device = (source, rows.index(e.request))
+                tokens = [0]
+                if e.count != 1:
+                    raise RuntimeError("a token that is still on the device can only be a step's single token")
+            entries.append(StepEntry(e.request.req_id, tokens, [e.count - 1] if e.samples else [], e.positions, on_device))
         logits = self.runner.step(entries)
-        sampled: Dict[Hashable, int] = {}
         due = [e for e in plan.entries if e.samples]
+        launched = None
         if due:
             tokens = self.sampler.sample_rows(
-                logits, [e.request.sampling for e in due], [len(e.request.output) for e in due],
+                logits, [e.request.sampling for e in due], [len(e.request.output) + e.request.in_flight for e in due],
                 [e.request.output if e.request.sampling.repetition_penalty != 1.0 else None for e in due])
-            for e, token in zip(due, tokens.tolist()):
-                sampled[e.request.req_id] = token
-            kernels.check_error_flag()                  # after the copy above: the step's kernels have run
+            # to the host at once, behind this step and before the next is queued: reading it back later then waits
+            # for this step only (a copy asked for later would queue behind the step after it)
+            landing = self._landing.pop() if self._landing else (torch.empty(self.scheduler.max_num_seqs, dtype=torch.int32).pin_memory(),
+                                                                 torch.cuda.Event())
+            landing[0][:tokens.numel()].copy_(tokens, non_blocking=True)
+            landing[1].record()
+            launched = (tokens, [e.request for e in due], landing)
         self.steps += 1
         for e in plan.entries:
-            if e.count == 1 and e.request.output:
+            if e.count == 1 and (e.request.output or e.request.in_flight):
                 self.tokens_decoded += 1
             else:
                 self.tokens_prefilled += e.count
-        finished += self.scheduler.finish_step(plan, sampled)
+        finished += self.scheduler.finish_step(plan, {e.request.req_id: None for e in due})
+        # the step before: its ids are on their way or there; this step is queued behind it
+        finished += self._read_back()
+        self._in_flight = launched
+        if not ahead:
+            finished += self._read_back()
+        return finished
+
+    def abort(self, req_id: Hashable) -> Optional[Request]:
+        """Take the request out wherever it is; its pages go back. What is still in flight for it is dropped."""
+        request = self.scheduler.abort(req_id)
+        if request is None:
+            request = self._requests.get(req_id)
+            if request is None or request.status != "draining":
+                return None
+            request.status, request.finish_reason = "finished", "abort"     # its last token was on its way
+        return request
+
+    def drain(self) -> List[Request]:
+        """Read back what is in flight without launching anything; returns the requests this finishes."""
+        return self._read_back()
+
+    def _read_back(self) -> List[Request]:
+        """The sampled ids of the step in flight, to the host and into their requests."""
+        if self._in_flight is None:
+            return []
+        tokens, requests, landing = self._in_flight
+        self._in_flight = None
+        finished = []
+        landing[1].synchronize()
+        values = landing[0][:len(requests)].tolist()
+        self._landing.append(landing)
+        for request, token in zip(requests, values):
+            if self.scheduler.late_token(request, token):
+                finished.append(request)
+        kernels.check_error_flag()                      # after the copy above: the step's kernels have run
         return finished
 
     # -- whole generations -------------------------------------------------------------------

@@ -40,6 +40,10 @@ class StepEntry:
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)
     positions: Optional[Sequence[Sequence[int]]] = None
+    # For an entry of one token whose id is still on the device (sampled by the step before, not read back yet):
+    # (int32 tensor of sampled ids, index into it). ``tokens`` then holds any valid id as a stand-in; the step copies
+    # the real one into its token array on the device before it runs.
+    device_token: Optional[tuple] = None
 
 
 class _CacheViews:
@@ -117,6 +121,7 @@ class ModelRunner:
         self.graph_replays = 0
         self._context_limit = model.captured_context_limit() if hasattr(model, "captured_context_limit") else None
         self.position_streams = int(getattr(model, "position_streams", 1))
+        self._token_index: Dict[tuple, tuple] = {}     # index tensors of _device_tokens, by (rows, sources)
 
     # -- pages for the step's tokens -----------------------------------------------------------
     def _reserve(self, entries: Sequence[StepEntry]) -> None:
@@ -145,6 +150,8 @@ class ModelRunner:
                 for w in e.want:
                     if not 0 <= int(w) < n:
                         raise ValueError(f"request {e.req_id!r} wants logits at place {w} of {n} tokens")
+                if e.device_token is not None and n != 1:
+                    raise ValueError(f"request {e.req_id!r}: only a single token can still be on the device")
                 if e.positions is not None and (len(e.positions) != self.position_streams or
                                                 any(len(row) != n for row in e.positions)):
                     raise ValueError(f"request {e.req_id!r} brings position ids of another shape than "
@@ -272,6 +279,28 @@ class ModelRunner:
         self.last_h2d_bytes = n * 4
         return dev
 
+    def _device_tokens(self, token_ids: torch.Tensor, entries: Sequence[StepEntry], first_rows: Sequence[int]) -> None:
+        """Copy the ids that are still on the device (``StepEntry.device_token``) into the step's token array, on the
+        stream, after the array's copy from the host and before the model runs."""
+        rows = [(first_rows[r], e.device_token) for r, e in enumerate(entries) if e.device_token is not None]
+        if not rows:
+            return
+        source = rows[0][1][0]
+        if (len(rows) == source.numel() and all(src is source for _row, (src, _i) in rows) and
+                all(row == rows[0][0] + k and i == k for k, (row, (_src, i)) in enumerate(rows))):
+            token_ids[rows[0][0]:rows[0][0] + len(rows)].copy_(source)        # the usual case: the same requests go on
+            return
+        for src in {id(t): t for _row, (t, _i) in rows}.values():
+            mine = [(row, i) for row, (t, i) in rows if t is src]
+            key = (id(src.device), tuple(mine))
+            index = self._token_index.get(key)
+            if index is None:
+                if len(self._token_index) > 256:
+                    self._token_index.clear()
+                index = self._token_index[key] = (torch.tensor([row for row, _ in mine], dtype=torch.long, device=self.device),
+                                                  torch.tensor([i for _, i in mine], dtype=torch.long, device=self.device))
+            token_ids.index_copy_(0, index[0], src.index_select(0, index[1]))
+
     def _bind(self, ctx: StepContext, dev: torch.Tensor) -> None:
         """Point the context's device arrays at their places in the flat buffer."""
         N, R, width = ctx.num_tokens, ctx.num_requests, ctx.table_width
@@ -315,6 +344,12 @@ class ModelRunner:
     def _prepare_reserved(self, entries: Sequence[StepEntry]) -> StepContext:
         ctx = StepContext(self.device, self.dtype)
         self._bind(ctx, self._to_device(self._fill(ctx, entries)))
+        if any(e.device_token is not None for e in entries):
+            first, at = [], 0
+            for e in entries:
+                first.append(at)
+                at += len(e.tokens)
+            self._device_tokens(ctx.token_ids, entries, first)
         return ctx
 
     def _run(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -379,6 +414,7 @@ class ModelRunner:
             slot.dev.copy_(slot.host, non_blocking=True)
         slot.copied.record()
         self.last_h2d_bytes = slot.host.numel() * 4
+        self._device_tokens(slot.ctx.token_ids, entries, range(len(entries)))
         if slot.pieces is None:
             slot.graph.replay()
         else:

@@ -28,6 +28,9 @@ from ..cache import CacheManager
 from ..sampling import SamplingConfig
 
 
+PENDING = -1                  # stands for a sampled token that is still on the device (``Request.in_flight``)
+
+
 @dataclass(eq=False)          # a request is itself: lists of requests are searched by identity, not by comparing fields
 class Request:
     req_id: Hashable
@@ -38,7 +41,11 @@ class Request:
     ignore_eos: bool = False
     output: List[int] = field(default_factory=list)
     computed: int = 0                  # tokens whose keys/values are in the cache
-    status: str = "waiting"            # waiting | running | finished
+    status: str = "waiting"            # waiting | running | draining | finished
+    # Tokens that were sampled for this request in steps whose result has not reached the host yet (the engine runs
+    # one step ahead of what it has read back). They count as tokens of the request everywhere, but ``output`` holds
+    # only tokens the host knows. "draining": the request has left the scheduler (its last token is among these).
+    in_flight: int = 0
     finish_reason: Optional[str] = None
     preemptions: int = 0
     # For a model whose position encoding reads several streams of positions: the prompt's position ids, one list per
@@ -47,7 +54,11 @@ class Request:
 
     @property
     def tokens(self) -> List[int]:
-        return self.prompt + self.output
+        return self.prompt + self.output + [PENDING] * self.in_flight
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output) + self.in_flight
 
     def positions_of(self, start: int, count: int) -> Optional[List[List[int]]]:
         """Position ids of the tokens start .. start + count - 1, stream by stream; None without ``position_ids``."""
@@ -60,7 +71,7 @@ class Request:
 
     @property
     def num_pending(self) -> int:
-        return len(self.prompt) + len(self.output) - self.computed
+        return len(self.prompt) + len(self.output) + self.in_flight - self.computed
 
 
 @dataclass
@@ -154,8 +165,7 @@ class Scheduler:
             if any(short):
                 spare = [a + b for a, b in zip(spare, short)]
             budget -= count
-            plan.entries.append(PlannedEntry(request, request.computed, count, request.computed + count ==
-                                             len(request.prompt) + len(request.output)))
+            plan.entries.append(PlannedEntry(request, request.computed, count, request.computed + count == request.num_tokens))
             return True
 
         # 1. running requests: those that decode first, then those still in their prompt
@@ -206,31 +216,63 @@ class Scheduler:
         return plan
 
     # -- after the step ran ------------------------------------------------------------------
-    def finish_step(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
+    def finish_step(self, plan: StepPlan, sampled: Dict[Hashable, Optional[int]]) -> List[Request]:
         """Record the step: portions are now cached, sampled tokens are appended, finished requests
-        leave and give their pages back. Returns the requests that finished."""
+        leave and give their pages back. Returns the requests that finished. A token given as None was
+        sampled but has not reached the host (``late_token`` brings it): it counts towards the lengths,
+        and a request whose last token it is leaves the scheduler as "draining"."""
         finished: List[Request] = []
         for entry in plan.entries:
             request = entry.request
             request.computed = entry.start + entry.count
             if not entry.samples:
                 continue
-            token = int(sampled[request.req_id])
-            request.output.append(token)
+            token = sampled[request.req_id]
             reason = None
-            if not request.ignore_eos and token in request.eos_token_ids:
-                reason = "stop"
-            elif len(request.output) >= request.max_tokens:
-                reason = "length"
-            elif len(request.prompt) + len(request.output) >= self.max_model_len:
+            if token is None:
+                request.in_flight += 1
+            else:
+                request.output.append(int(token))
+                if not request.ignore_eos and int(token) in request.eos_token_ids:
+                    reason = "stop"
+            generated = len(request.output) + request.in_flight
+            if reason is None and (generated >= request.max_tokens or len(request.prompt) + generated >= self.max_model_len):
                 reason = "length"
             if reason:
-                request.status, request.finish_reason = "finished", reason
+                request.finish_reason = reason
                 self.running.remove(request)
                 self._release(request)
                 self.num_finished += 1
-                finished.append(request)
+                if request.in_flight:
+                    request.status = "draining"
+                else:
+                    request.status = "finished"
+                    finished.append(request)
         return finished
+
+    def late_token(self, request: Request, token: int) -> bool:
+        """The oldest of the request's tokens in flight has reached the host. True when the request is finished by it:
+        it was the last one of a draining request, or it ends the request (an end-of-sequence token; what was computed
+        for the request after it was computed in vain and is dropped when it arrives)."""
+        request.in_flight -= 1
+        if request.status == "finished":
+            return False                           # stopped or aborted before this token: dropped
+        token = int(token)
+        request.output.append(token)
+        if not request.ignore_eos and token in request.eos_token_ids:
+            if request.status == "running":
+                self.running.remove(request)
+                self._release(request)
+                self.num_finished += 1
+            elif request.status == "waiting":      # preempted with the token in flight
+                self.waiting.remove(request)
+                self.num_finished += 1
+            request.status, request.finish_reason = "finished", "stop"
+            return True
+        if request.status == "draining" and request.in_flight == 0:
+            request.status = "finished"
+            return True
+        return False
 
     def abort(self, req_id: Hashable) -> Optional[Request]:
         for request in list(self.running):

@@ -193,7 +193,7 @@ class Qwen3InferenceEngine:
         finally:
             # a caller that stops iterating (or closes the generator) must not leave the request running with its pages
             if request.status != "finished":
-                self.engine.scheduler.abort(req_id)
+                self.engine.abort(req_id)
             self.engine._requests.pop(req_id, None)
 
     def get_stats(self):
@@ -202,5 +202,8 @@ class Qwen3InferenceEngine:
     def cleanup(self) -> None:
         """Abort whatever is still queued or running and give its pages back."""
         for request in list(self.engine.scheduler.running) + list(self.engine.scheduler.waiting):
-            self.engine.scheduler.abort(request.req_id)
+            self.engine.abort(request.req_id)
+        for req_id in list(self.engine._requests):
+            self.engine.abort(req_id)                        # requests whose last token is still on its way
+        self.engine.drain()
         self.engine._requests.clear()

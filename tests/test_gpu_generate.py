@@ -315,3 +315,38 @@ def test_cli_infer_with_token_ids(tmp_path):
                           capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [int(t) for t in proc.stdout.split()] == plain.greedy_generate(tiny, weights, prompt, 6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_step_ahead_gives_what_reading_every_step_back_gives(tmp_path, dtype):
+    """The engine plans and queues a step before it has read what the step before sampled (the ids go from the sampler
+    to the next step on the device). The same tokens and finish reasons as with every step read back before the next is
+    planned: with an end-of-sequence id that greedy generation meets (a request that stops was planned one step too
+    far), with so few pages that requests are preempted while a token of theirs is in flight, with seeded sampling,
+    and with a repetition penalty (which needs the tokens on the host: such steps are read back at once)."""
+    tiny = plain.TINY_B
+    folder, weights = H.make_case(tmp_path, tiny, 1, dtype, std=0.08)
+    prompts = [H.random_tokens(tiny["vocab_size"], n, 640 + n) for n in (1, 33, 7, 52, 18, 26)]
+    free = engine_for(folder, dtype, block_size=8, num_blocks=512).generate(prompts, max_tokens=30, temperature=0.0)
+    flat = [t for out in free for t in out]
+    eos = max(set(flat), key=flat.count)
+    stops = preemptions = 0
+    for blocks, kwargs in ((512, dict(temperature=0.0)), (14, dict(temperature=0.0)), (16, dict(temperature=0.8, top_k=0, top_p=1.0, seed=3)),
+                           (512, dict(temperature=0.0, repetition_penalty=1.3))):
+        outs = []
+        for ahead in (False, True):
+            # (in bfloat16 a preempted request's tokens are recomputed as a prompt, with other rounding than when they were
+            # decoded, and the two ways of stepping preempt at different moments: few pages only in float32)
+            engine = engine_for(folder, dtype, block_size=8, num_blocks=blocks if dtype == torch.float32 else 512, eos_token_id=eos,
+                                max_batch_size=4, max_num_batched_tokens=32)
+            engine.engine.lookahead = ahead
+            results = engine.generate_ids(prompts, max_tokens=30, **kwargs)
+            outs.append([(r.token_ids, r.finish_reason) for r in results])
+            assert engine.engine.cache.num_live == 0 and not engine.engine.has_unfinished()
+            engine.engine.cache.check()
+            if ahead:
+                preemptions += engine.engine.scheduler.num_preemptions
+        assert outs[0] == outs[1], (blocks, kwargs)
+        stops += sum(1 for _tokens, reason in outs[1] if reason == "stop")
+        assert all(len(tokens) <= 30 and (reason != "stop" or tokens[-1] == eos) for tokens, reason in outs[1])
+    assert stops >= 2 and (preemptions >= 1 or dtype != torch.float32)

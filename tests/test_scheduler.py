@@ -174,3 +174,46 @@ def test_position_ids_of_a_portion_go_on_after_the_prompts_largest_id():
     assert r.positions_of(6, 1) == [[12], [12]]
     assert r.positions_of(2, 4) == [[1, 1, 10, 11], [0, 9, 10, 11]]
     assert Request("b", [1, 2], SamplingConfig(), 4).positions_of(0, 2) is None
+
+
+def test_tokens_that_reach_the_host_a_step_late():
+    """The engine may plan a step before it has read what the step before sampled: a token given as None counts
+    towards the lengths and is planned as the request's next input; ``late_token`` brings its value. A request that is
+    full leaves as "draining" and is finished when its last token arrives; an end-of-sequence token that arrives late
+    ends its request there and then, and what was sampled after it is dropped."""
+    from llm_pipeline_b200.engine.scheduler import PENDING
+    cache, sched = make(num_pages=16, budget=64, max_len=64)
+
+    def run(cache, plan):
+        for e in plan.entries:
+            if e.request.req_id not in cache:
+                cache.admit(e.request.req_id)
+            assert cache.reserve(e.request.req_id, e.start + e.count)
+            cache.commit(e.request.req_id, e.start + e.count)
+
+    a = Request("a", [1, 2, 3], SamplingConfig(), 3, eos_token_ids={9})
+    b = Request("b", [4, 5], SamplingConfig(), 8, eos_token_ids={9})
+    sched.add(a)
+    sched.add(b)
+    plan = sched.schedule()
+    assert [(e.request.req_id, e.count, e.samples) for e in plan.entries] == [("a", 3, True), ("b", 2, True)]
+    run(cache, plan)
+    assert sched.finish_step(plan, {"a": None, "b": None}) == []
+    assert a.in_flight == 1 and a.output == [] and a.tokens == [1, 2, 3, PENDING] and a.num_pending == 1
+    plan2 = sched.schedule()                                   # planned without knowing the tokens
+    assert [(e.request.req_id, e.token_ids, e.samples) for e in plan2.entries] == [("a", [PENDING], True), ("b", [PENDING], True)]
+    run(cache, plan2)
+    assert sched.finish_step(plan2, {"a": None, "b": None}) == []
+    assert not sched.late_token(a, 7)
+    assert sched.late_token(b, 9)                              # b's first token ends it
+    assert b.status == "finished" and b.finish_reason == "stop" and b.output == [9] and b.in_flight == 1 and "b" not in cache
+    assert a.output == [7] and a.in_flight == 1 and a.status == "running"
+    plan3 = sched.schedule()                                   # a's third and last token
+    assert [e.request.req_id for e in plan3.entries] == ["a"]
+    run(cache, plan3)
+    assert sched.finish_step(plan3, {"a": None}) == [] and a.status == "draining" and "a" not in cache
+    assert not sched.has_unfinished()
+    assert not sched.late_token(b, 5) and b.output == [9] and b.in_flight == 0        # sampled in vain: dropped
+    assert not sched.late_token(a, 8) and a.status == "draining"
+    assert sched.late_token(a, 6) and a.status == "finished" and a.finish_reason == "length" and a.output == [7, 8, 6]
+    cache.check()
