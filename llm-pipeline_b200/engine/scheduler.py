@@ -60,6 +60,20 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output) + self.in_flight
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """``tokens[start:start + count]`` without putting the whole list together (a decode step asks for one token
+        of every request, step after step)."""
+        n, end = len(self.prompt), start + count
+        if end <= n:
+            return self.prompt[start:end]
+        known = n + len(self.output)
+        out = self.prompt[start:] if start < n else []
+        if start < known:
+            out = out + self.output[max(start - n, 0):min(end, known) - n]
+        if end > known:
+            out = out + [PENDING] * (min(end, known + self.in_flight) - max(start, known))
+        return out
+
     def positions_of(self, start: int, count: int) -> Optional[List[List[int]]]:
         """Position ids of the tokens start .. start + count - 1, stream by stream; None without ``position_ids``."""
         if self.position_ids is None:
@@ -83,7 +97,7 @@ class PlannedEntry:
 
     @property
     def token_ids(self) -> List[int]:
-        return self.request.tokens[self.start:self.start + self.count]
+        return self.request.token_slice(self.start, self.count)
 
     @property
     def positions(self) -> Optional[List[List[int]]]:

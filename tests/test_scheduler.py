@@ -217,3 +217,18 @@ def test_tokens_that_reach_the_host_a_step_late():
     assert not sched.late_token(a, 8) and a.status == "draining"
     assert sched.late_token(a, 6) and a.status == "finished" and a.finish_reason == "length" and a.output == [7, 8, 6]
     cache.check()
+
+
+def test_a_portion_of_a_requests_tokens_without_putting_them_all_together():
+    import random
+    from llm_pipeline_b200.engine.scheduler import PENDING
+    rng = random.Random(0)
+    for _ in range(500):
+        r = Request("a", [rng.randrange(100) for _ in range(rng.randrange(1, 8))], SamplingConfig(), 10)
+        r.output = [rng.randrange(100) for _ in range(rng.randrange(0, 6))]
+        r.in_flight = rng.randrange(0, 3)
+        whole = r.tokens
+        assert whole[len(whole) - r.in_flight:] == [PENDING] * r.in_flight
+        start = rng.randrange(0, len(whole) + 1)
+        count = rng.randrange(0, len(whole) - start + 2)
+        assert r.token_slice(start, count) == whole[start:start + count]
