@@ -135,12 +135,15 @@ class GenerationEngine:
                 raise RuntimeError("the scheduler could not plan a step although requests are unfinished")
             return finished
         entries = []
+        source, where = None, {}
+        if self._in_flight is not None:
+            source = self._in_flight[0]
+            where = {id(request): row for row, request in enumerate(self._in_flight[1])}
         for e in plan.entries:
             tokens, on_device = e.token_ids, None
             if tokens[-1] == PENDING:
                 # the id is among those the step before sampled
-                source, rows, _landing = self._in_flight
-                on_device = (source, rows.index(e.request))
+                on_device = (source, where[id(e.request)])
                 tokens = [0]
                 if e.count != 1:
                     raise RuntimeError("a token that is still on the device can only be a step's single token")
