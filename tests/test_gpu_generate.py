@@ -350,3 +350,53 @@ def test_one_step_ahead_gives_what_reading_every_step_back_gives(tmp_path, dtype
         stops += sum(1 for _tokens, reason in outs[1] if reason == "stop")
         assert all(len(tokens) <= 30 and (reason != "stop" or tokens[-1] == eos) for tokens, reason in outs[1])
     assert stops >= 2 and (preemptions >= 1 or dtype != torch.float32)
+
+
+@pytest.mark.parametrize("seed", [3, 8, 20])
+def test_requests_that_arrive_and_are_aborted_while_the_engine_is_a_step_ahead(tmp_path, seed):
+    """Requests added while others run (in their prompts, decoding, with a token in flight), some aborted on the way,
+    few pages, seeded sampling and an end-of-sequence id: every request that is not aborted ends with the tokens and
+    the reason it has when every step is read back before the next is planned; nothing is left in the cache."""
+    import random
+    from llm_pipeline_b200.sampling import SamplingConfig
+    rng = random.Random(5000 + seed)
+    tiny = plain.TINY_B
+    folder, weights = H.make_case(tmp_path, tiny, seed, torch.float32, std=0.08)
+    n = 10
+    prompts = [H.random_tokens(tiny["vocab_size"], rng.randrange(1, 50), 300 + 13 * seed + i) for i in range(n)]
+    limits = [rng.choice([1, 2, 5, 17, 30]) for _ in range(n)]
+    arrive = sorted(rng.randrange(0, 25) for _ in range(n))                  # the step at which each request is added
+    aborts = {i: arrive[i] + rng.randrange(1, 12) for i in range(n) if rng.random() < 0.3}
+    free = engine_for(folder, torch.float32, block_size=8, num_blocks=512).generate(prompts, max_tokens=30, temperature=0.0)
+    flat = [t for out in free for t in out]
+    eos = max(set(flat), key=flat.count)
+    outs = []
+    for ahead in (False, True):
+        engine = engine_for(folder, torch.float32, block_size=8, num_blocks=24, eos_token_id=eos, max_batch_size=4,
+                            max_num_batched_tokens=24).engine
+        engine.lookahead = ahead
+        ids, step = {}, 0
+        while len(ids) < n or engine.has_unfinished():
+            for i in range(n):
+                if i not in ids and arrive[i] <= step:
+                    ids[i] = engine.add_request(prompts[i], max_tokens=limits[i], eos_token_ids=[eos],
+                                                sampling=SamplingConfig(temperature=0.9, top_k=0, top_p=1.0, seed=7 + i))
+            for i, at in aborts.items():
+                if at == step and i in ids:
+                    engine.abort(ids[i])
+            if engine.has_unfinished():
+                engine.step()
+            step += 1
+            assert step < 1000
+        engine.drain()
+        result = []
+        for i in range(n):
+            request = engine._requests[ids[i]]
+            assert request.status == "finished" and request.in_flight == 0
+            result.append((list(request.output) if request.finish_reason != "abort" else None, request.finish_reason))
+        assert engine.cache.num_live == 0
+        engine.cache.check()
+        outs.append(result)
+    for one, other in zip(*outs):
+        assert one == other or "abort" in (one[1], other[1])
+    assert any(reason == "abort" for _tokens, reason in outs[1]) and any(reason == "length" for _tokens, reason in outs[1])
