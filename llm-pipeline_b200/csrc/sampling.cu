@@ -329,3 +329,37 @@ LLMP_API int llmp_sample(const float* logits, long stride, int M, int V, const v
     sample_kernel<<<M, SAMPLE_THREADS, 0, stream>>>(logits, stride, V, (const SampleRow*)params, out, out_u);
     return llmp_check_launch("sample");
 }
+
+// ------------------------------------------------------------------------------------------
+// Entropy of softmax(logits / temperature) per row, in nats, float32 (what Mirostat v2 steers by):
+//   H = log Z - (sum_i e_i z_i) / Z   with z_i = x_i / T - max, e_i = exp(z_i), Z = sum_i e_i.
+// One block per row; fixed-order block sums. temperature <= 0: the logits as they are.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(SAMPLE_THREADS) entropy_kernel(const float* __restrict__ logits, long stride, int V,
+                                                                 float temperature, float* __restrict__ out) {
+    __shared__ float scratch[32];
+    const float* row = logits + (size_t)blockIdx.x * stride;
+    const float inv = temperature > 0.f ? 1.f / temperature : 1.f;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i] * inv);
+    mx = block_max(mx, scratch);
+    float z = 0.f, ez = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float d = row[i] * inv - mx;
+        if (d > -INFINITY) {                                       // a removed token (-inf) adds nothing
+            const float e = expf(d);
+            z += e;
+            ez = fmaf(e, d, ez);
+        }
+    }
+    z = block_sum(z, scratch);
+    ez = block_sum(ez, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = logf(z) - ez / z;
+}
+
+LLMP_API int llmp_entropy(const float* logits, long stride, int M, int V, float temperature, float* out, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    LLMP_REQUIRE(V > 0, "entropy: bad vocabulary size %d", V);
+    entropy_kernel<<<M, SAMPLE_THREADS, 0, stream>>>(logits, stride, V, temperature, out);
+    return llmp_check_launch("entropy");
+}

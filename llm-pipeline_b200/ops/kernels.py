@@ -54,6 +54,7 @@ _SIGNATURES = {
     "llmp_argmax": [_P, _L, _I, _I, _P, _P, _P],
     "llmp_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "llmp_sample": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "llmp_entropy": [_P, _L, _I, _I, _F, _P, _P],
     "llmp_bounded_wait_check": [_P, _I, _P, _P],
     "llmp_gemm_stream_chain": [_P, _I, _I, _P, _P, _P],
 }
@@ -691,6 +692,16 @@ def repetition_penalty(logits: torch.Tensor, tokens: torch.Tensor, offsets: torc
     _need(penalty.dtype == torch.float32 and penalty.numel() == logits.shape[0], "one penalty per row")
     _call("llmp_repetition_penalty", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(tokens),
           _ptr(offsets), _ptr(penalty), _stream())
+
+
+def entropy(logits: torch.Tensor, temperature: float) -> torch.Tensor:
+    """Entropy in nats of softmax(logits / temperature) for every row of float32 ``logits [rows, vocab]`` (the logits
+    as they are when ``temperature`` is not positive); float32 ``[rows]``."""
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be float32 rows")
+    out = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+    _call("llmp_entropy", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature), _ptr(out),
+          _stream())
+    return out
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, out_u: Optional[torch.Tensor] = None) -> torch.Tensor:

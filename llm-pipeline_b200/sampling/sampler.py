@@ -7,7 +7,8 @@ top-p, min-p, typical-p, softmax and one draw. ``do_sample`` is carried and, as 
 draw is an inverse-CDF pick with a uniform number from a counter-based generator keyed by the
 request's ``seed`` and its count of sampled tokens, so a request's tokens do not depend on what
 else is in the batch (the reference draws with ``torch.multinomial`` from the global generator,
-:85). Mirostat (:240-279) is not called by the reference's engine and is not provided.
+:85). Mirostat v2 (:240-279), which the reference's sampler offers and its engine never calls, is
+``sample_mirostat_v2`` here, with the same arithmetic.
 
 Typical-p: the reference's entropy is NaN as soon as an earlier filter has removed a token
 (0 * -inf at :226), which leaves only the most likely token; here the entropy is taken over the
@@ -121,6 +122,30 @@ class Sampler:
         out = self.sample_rows(logits.float().contiguous(), rows, [step] * logits.shape[0],
                                [generated_tokens] * logits.shape[0])
         return out.long()
+
+    def sample_mirostat_v2(self, logits: torch.Tensor, config_override: Optional[Dict[str, Any]] = None,
+                           previous_entropy: Optional[float] = None, step: int = 0):
+        """Mirostat v2 as in src/llm_pipeline/inference/sampling.py:240-279, for one row of ``logits [1, vocab]``: the
+        entropy H of softmax(logits / temperature); ``previous_entropy`` (H itself at the first call) moves by
+        ``-mirostat_eta * (H - mirostat_tau)``; while it is positive the draw is among the ``int(exp(previous_entropy))``
+        most likely tokens (at least one), else among all. Returns (token ids ``[1]`` int64, the new value to pass in
+        at the next call). The entropy and the draw are this library's kernels; the draw uses the request's seed and
+        ``step`` like every other draw here (the reference draws with ``torch.multinomial``, :277)."""
+        import math
+        cfg = self.config.merged(config_override)
+        if logits.dim() != 2 or logits.shape[0] != 1:
+            raise ValueError("Mirostat steers one sequence: logits must be [1, vocab] (the reference reads the entropy "
+                             "with .item(), :266-269)")
+        logits = logits.float().contiguous()
+        current = float(kernels.entropy(logits, cfg.temperature)[0])
+        if previous_entropy is None:
+            previous_entropy = current
+        previous_entropy -= cfg.mirostat_eta * (current - cfg.mirostat_tau)
+        top_k = max(1, int(math.exp(previous_entropy))) if previous_entropy > 0 else 0
+        draw = replace(cfg, temperature=cfg.temperature if cfg.temperature > 0 else 1.0, top_k=min(top_k, logits.shape[1]),
+                       top_p=1.0, min_p=0.0, typical_p=1.0, repetition_penalty=1.0)
+        out = self.sample_rows(logits, [draw], [step], None)
+        return out.long(), previous_entropy
 
     def get_sampling_info(self) -> Dict[str, Any]:
         c = self.config

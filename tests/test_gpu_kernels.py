@@ -673,3 +673,39 @@ def test_library_product_adds_into_the_float32_residual(M, N, Kd):
     assert not K().library_add_product(untouched, x.float(), w)
     assert not K().library_add_product(untouched[:, 1:], x, w[1:])
     assert torch.equal(untouched, residual)
+
+
+def test_mirostat_v2_follows_the_reference_arithmetic():
+    """inference/sampling.py:240-279: the entropy of softmax(logits / T), the running value moved by -eta (H - tau), a
+    draw among the int(exp(value)) most likely tokens while the value is positive. Entropy kernel against float64
+    (also with removed tokens, at a vocabulary that is no power of two); five calls in a row against the same
+    arithmetic done by hand, the draw being this library's seeded draw with that top-k."""
+    import math
+    from llm_pipeline_b200.sampling import Sampler, SamplingConfig
+    V = 10007
+    logits = rnd(3, V, seed=3, scale=2.0)
+    logits[1, 17:4000] = float("-inf")
+    for T in (1.0, 0.7, 0.0):
+        z = logits.double() / (T if T > 0 else 1.0)
+        p = torch.softmax(z, dim=-1)
+        want = -(p * torch.where(p > 0, torch.log_softmax(z, dim=-1), torch.zeros_like(z))).sum(-1)
+        got = K().entropy(logits, T)
+        assert torch.allclose(got.double().cpu(), want.cpu(), atol=2e-5), (T, got, want)
+    cfg = SamplingConfig(temperature=0.8, mirostat_tau=3.0, mirostat_eta=0.3, seed=11)
+    sampler = Sampler(cfg)
+    value, by_hand = None, None
+    for step in range(5):
+        row = rnd(1, V, seed=40 + step, scale=3.0)
+        z = row.double() / 0.8
+        p = torch.softmax(z, dim=-1)
+        H = float(-(p * torch.log_softmax(z, dim=-1)).sum())
+        by_hand = H if by_hand is None else by_hand
+        by_hand -= 0.3 * (H - 3.0)
+        k = max(1, int(math.exp(by_hand))) if by_hand > 0 else 0
+        token, value = sampler.sample_mirostat_v2(row, previous_entropy=value, step=step)
+        assert abs(value - by_hand) < 1e-4 and token.shape == (1,) and token.dtype == torch.int64
+        assert int(token) in set(torch.topk(row[0], k).indices.tolist()) if k else True
+        same = sampler.sample_rows(row, [SamplingConfig(temperature=0.8, top_k=k, top_p=1.0, seed=11)], [step])
+        assert int(same[0]) == int(token)
+    with pytest.raises(ValueError, match="one sequence"):
+        sampler.sample_mirostat_v2(logits)
