@@ -83,6 +83,8 @@ class Qwen3InferenceEngine:
             max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=config.max_sequence_length,
             max_prefill_chunk=config.max_prefill_chunk, sampling=sampling)
         self.model_config = self.engine.config
+        self._continuous: dict = {}              # add_continuous_request: id -> (prompt as given, time it was added)
+        self._continuous_done: dict = {}         # id -> time its result was first seen finished
         self.tokenizer = self._load_tokenizer(config.model_path)
         if self.tokenizer is not None:
             if config.pad_token_id is None:
@@ -199,6 +201,95 @@ class Qwen3InferenceEngine:
     def get_stats(self):
         return self.engine.stats()
 
+    # -- the reference's calls around its batcher and its caches (qwen3_engine.py:614-712) -------------------------
+    # Here there is one engine, always paged and continuously batched, and no thread of its own: a request that was
+    # added runs in the steps of whoever drives the engine next (a generate call, a stream, ``get_continuous_result``).
+    def start_continuous_batching(self) -> None:
+        """Nothing to start (qwen3_engine.py:623-626 starts the batcher's thread)."""
+
+    def stop_continuous_batching(self) -> None:
+        """Nothing to stop (qwen3_engine.py:628-631)."""
+
+    def add_continuous_request(self, prompt, max_tokens: int = 50, **kwargs) -> str:
+        """Queue a request and return at once (qwen3_engine.py:633-649). ``prompt``: a string (with a tokenizer in the
+        model folder) or a list of token ids. The id is of the reference's form."""
+        import time
+        as_text = isinstance(prompt, str)
+        if as_text and self.tokenizer is None:
+            raise ValueError("the model folder has no tokenizer; pass the prompt as a list of token ids")
+        ids = self.tokenizer(prompt)["input_ids"] if as_text else list(prompt)
+        ignore_eos = bool(kwargs.pop("ignore_eos", False))
+        base = self.engine.sampler.config.merged(kwargs)
+        request_id = f"req_{id(prompt)}_{int(time.time() * 1000)}_{len(self._continuous)}"
+        self.engine.add_request(ids, max_tokens, base, eos_token_ids=self._eos_ids(), ignore_eos=ignore_eos, req_id=request_id)
+        self._continuous[request_id] = (prompt, time.time())
+        return request_id
+
+    def get_continuous_result(self, request_id: str):
+        """The finished request as the reference's dictionary (continuous_batching.py:286-293), or None while it is
+        not finished; a call that finds it unfinished runs one step of the engine first."""
+        import time
+        if request_id not in self._continuous:
+            raise KeyError(f"no continuous request {request_id!r}")
+        request = self.engine._requests[request_id]
+        if request.status != "finished":
+            self.engine.step()
+            if request.status != "finished":
+                return None
+        prompt, started = self._continuous[request_id]
+        finished = self._continuous_done.setdefault(request_id, time.time())
+        text = self.tokenizer.decode(request.output, skip_special_tokens=True) if self.tokenizer is not None else ""
+        return {"request_id": request_id, "prompt": prompt, "generated_text": text, "generated_tokens": list(request.output),
+                "latency_ms": (finished - started) * 1000, "tokens_generated": len(request.output),
+                "finish_reason": request.finish_reason}
+
+    def get_continuous_stats(self):
+        """Counters of scheduler and cache (the reference's batcher counts the same things, continuous_batching.py:448-463)."""
+        return self.engine.stats()
+
+    def get_kv_cache_stats(self):
+        """Pages free, used, at most used and used again per group; live requests (qwen3_engine.py:614-616)."""
+        return self.engine.cache.stats()
+
+    def clear_kv_cache(self) -> None:
+        """Give every page back: whatever is queued or running is aborted (qwen3_engine.py:618-621)."""
+        self.cleanup()
+
+    def get_optimization_stats(self):
+        """The reference's switches (qwen3_engine.py:672-695) as they are here: always on, or not built."""
+        runner = self.engine.runner
+        return {"torch_compile_enabled": False, "cuda_graphs_enabled": bool(runner.use_graphs),
+                "paged_attention_enabled": True, "flash_attention_enabled": False, "prefix_caching_enabled": False,
+                "tensor_parallel_enabled": False, "one_step_ahead": bool(self.engine.lookahead),
+                "cuda_graphs": {"num_graphs": len(runner._graphs), "replays": runner.graph_replays},
+                "paged_attention": self.engine.cache.stats()}
+
+    def get_model_info(self):
+        """Sizes and parameter counts from the model's configuration (models/qwen3/factory.py:132-166)."""
+        c = self.model_config
+        info = {"model_type": getattr(c, "model_type", "qwen3"), "vocab_size": c.vocab_size, "hidden_size": c.hidden_size,
+                "num_layers": c.num_hidden_layers, "num_attention_heads": c.num_attention_heads,
+                "num_key_value_heads": c.num_key_value_heads, "intermediate_size": c.intermediate_size,
+                "max_position_embeddings": c.max_position_embeddings, "head_dim": c.head_dim,
+                "torch_dtype": str(self.engine.dtype), "use_cache": True, "tie_word_embeddings": bool(c.tie_word_embeddings)}
+        info.update(c.parameter_counts())
+        return info
+
+    def estimate_memory_usage(self):
+        """Bytes of the weights in the engine's type and the reference's rule of thumb for the GPU
+        (models/qwen3/factory.py:168-211), with what a token of context costs in this engine's cache."""
+        info = self.get_model_info()
+        bytes_per_param = 4 if self.engine.dtype == torch.float32 else 2
+        memory_mb = info["total_parameters"] * bytes_per_param / (1024 * 1024)
+        memory_gb = memory_mb / 1024
+        from .cache import CacheManager
+        per_page = sum(CacheManager.bytes_per_page(self.engine.model.cache_specs(), self.engine.cache.page_size, self.engine.dtype))
+        return {**{k: v for k, v in info.items() if k.endswith("parameters") or k.endswith("_per_layer")},
+                "memory_mb": memory_mb, "memory_gb": memory_gb, "model_memory_mb": memory_mb, "model_memory_gb": memory_gb,
+                "bytes_per_param": bytes_per_param, "dtype": str(self.engine.dtype),
+                "recommended_gpu_memory_gb": max(memory_gb * 1.5, memory_gb + 1.0),
+                "kv_cache_bytes_per_token": per_page // self.engine.cache.page_size}
+
     def cleanup(self) -> None:
         """Abort whatever is still queued or running and give its pages back."""
         for request in list(self.engine.scheduler.running) + list(self.engine.scheduler.waiting):
@@ -207,3 +298,5 @@ class Qwen3InferenceEngine:
             self.engine.abort(req_id)                        # requests whose last token is still on its way
         self.engine.drain()
         self.engine._requests.clear()
+        self._continuous.clear()
+        self._continuous_done.clear()

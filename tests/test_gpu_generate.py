@@ -400,3 +400,45 @@ def test_requests_that_arrive_and_are_aborted_while_the_engine_is_a_step_ahead(t
     for one, other in zip(*outs):
         assert one == other or "abort" in (one[1], other[1])
     assert any(reason == "abort" for _tokens, reason in outs[1]) and any(reason == "length" for _tokens, reason in outs[1])
+
+
+def test_the_references_calls_around_its_batcher_and_caches(tmp_path):
+    """qwen3_engine.py:614-712 under their names: requests that are added without waiting and asked for later, the
+    counters of cache and scheduler, the switches, the model's sizes and parameter counts, the memory estimate."""
+    tiny = plain.TINY_A
+    folder, weights = H.make_case(tmp_path, tiny, 0, torch.float32, std=0.08)
+    engine = engine_for(folder, torch.float32)
+    engine.start_continuous_batching()
+    prompts = [H.random_tokens(256, 9, 71), H.random_tokens(256, 21, 72)]
+    ids = [engine.add_continuous_request(p, max_tokens=6, temperature=0.0) for p in prompts]
+    assert len(set(ids)) == 2 and all(i.startswith("req_") for i in ids)
+    results, polls = {}, 0
+    while len(results) < 2:
+        for i in ids:
+            if i not in results:
+                result = engine.get_continuous_result(i)
+                if result is not None:
+                    results[i] = result
+        polls += 1
+        assert polls < 200
+    assert polls > 2                                            # the first questions found them unfinished
+    for i, prompt in zip(ids, prompts):
+        assert results[i]["generated_tokens"] == plain.greedy_generate(tiny, weights, prompt, 6)
+        assert results[i]["tokens_generated"] == 6 and results[i]["prompt"] == prompt and results[i]["latency_ms"] > 0
+        assert engine.get_continuous_result(i)["latency_ms"] == results[i]["latency_ms"]
+    with pytest.raises(KeyError):
+        engine.get_continuous_result("req_nobody")
+    engine.stop_continuous_batching()
+    assert engine.get_continuous_stats()["finished"] == 2 and engine.get_kv_cache_stats()["live_requests"] == 0
+    switches = engine.get_optimization_stats()
+    assert switches["paged_attention_enabled"] and switches["cuda_graphs_enabled"] and not switches["tensor_parallel_enabled"]
+    info = engine.get_model_info()
+    assert info["total_parameters"] == sum(t.numel() for t in weights.values()) and info["num_layers"] == tiny["num_hidden_layers"]
+    memory = engine.estimate_memory_usage()
+    assert memory["bytes_per_param"] == 4 and abs(memory["memory_mb"] - info["total_parameters"] * 4 / 2 ** 20) < 1e-9
+    layers, kv_heads, head_dim = tiny["num_hidden_layers"], tiny["num_key_value_heads"], info["head_dim"]
+    assert memory["kv_cache_bytes_per_token"] == layers * 2 * kv_heads * head_dim * 4
+    engine.add_continuous_request(prompts[0], max_tokens=40)
+    engine.engine.step()
+    engine.clear_kv_cache()
+    assert engine.get_kv_cache_stats()["live_requests"] == 0 and not engine.engine.has_unfinished()
