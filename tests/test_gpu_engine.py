@@ -279,6 +279,9 @@ def test_prompt_portions_whose_products_add_themselves_into_the_residual(tmp_pat
     H.assert_close(H.replay(runner, H.cut_portions(requests, (20, 5, 16, 31))), want, tol, "accumulate portions")
     H.assert_close(H.replay(runner, H.cut_mixed(requests, (18, 3, 40, 16), max_live=3)), want, tol, "accumulate mixed")
     assert len(calls) > whole and min(calls) >= 16
+    # where the library's call cannot be had (it answers False), the product is taken and added as everywhere else
+    monkeypatch.setattr(kernels, "library_add_product", lambda r, x, w: False)
+    H.assert_close(H.replay(runner, H.cut_whole(requests)), want, tol, "accumulate refused")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
